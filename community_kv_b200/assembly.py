@@ -1,0 +1,179 @@
+"""Host/torch assembly of the decode state from community labels.
+
+Produces the layout the decode kernels consume - per-community member lists in
+recency-descending order, e4m3 mean-key centroids with decode headroom, and the
+retrieval-head -> (graph, KV head) maps - with the semantics of the reference's
+``build_member_csr``, ``compute_centroids`` and ``aggregation_mappings``
+(``community_kv/graph/partition.py:71-94, 382-492``).  Plain torch ops that run
+on CPU or GPU tensors; the Leiden partition that produces the labels stays on
+the host and is not part of this package.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from community_kv_b200.config import GraphAggregation
+
+FP8_MAX = 448.0
+
+
+def aggregation_mappings(
+    aggregation: GraphAggregation | str,
+    *,
+    query_heads: int,
+    kv_heads: int,
+    device: torch.device | str = "cpu",
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(retrieval_to_graph, retrieval_to_kv)`` int32 vectors for an aggregation mode."""
+
+    aggregation = GraphAggregation(aggregation)
+    heads = aggregation.retrieval_head_count(query_heads=query_heads, kv_heads=kv_heads)
+    index = torch.arange(heads, dtype=torch.int32, device=device)
+    if aggregation is GraphAggregation.PER_QUERY_HEAD:
+        return index, index // (query_heads // kv_heads)
+    if aggregation is GraphAggregation.QUERY_GROUP:
+        return index, index.clone()
+    return torch.zeros_like(index), index
+
+
+def build_member_csr(
+    community_ids: torch.Tensor,
+    community_counts: torch.Tensor,
+    *,
+    num_sink: int,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """CSR of non-sink positions by community; members sorted newest first."""
+
+    graphs, length = community_ids.shape
+    widest = int(community_counts.max())
+    labels = community_ids[:, num_sink:].long()
+    where = torch.arange(num_sink, length, device=community_ids.device).expand(graphs, -1)
+    order = (labels * length + (length - 1 - where)).argsort(dim=1)
+    member_positions = where.gather(1, order).to(torch.int32)
+    histogram = torch.zeros((graphs, widest), dtype=torch.int64, device=community_ids.device)
+    histogram.scatter_add_(1, labels, torch.ones_like(labels))
+    offsets = torch.zeros((graphs, widest + 1), dtype=torch.int32, device=community_ids.device)
+    offsets[:, 1:] = histogram.cumsum(1).to(torch.int32)
+    return offsets, member_positions
+
+
+def compute_centroids(
+    community_ids: torch.Tensor,
+    community_counts: torch.Tensor,
+    keys: torch.Tensor,
+    *,
+    retrieval_to_graph: torch.Tensor | None = None,
+    retrieval_to_kv: torch.Tensor | None = None,
+    num_sink: int,
+    max_decode_tokens: int,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-retrieval-head e4m3 mean keys ``[R, max count + headroom, D]`` and sizes."""
+
+    graphs, length = community_ids.shape
+    if keys.ndim != 3 or keys.shape[1] != length:
+        raise ValueError("keys must have shape [KV heads, sequence, head dim]")
+    if retrieval_to_graph is None or retrieval_to_kv is None:
+        if keys.shape[0] != graphs:
+            raise ValueError("aggregation mappings are required when graph and KV counts differ")
+        retrieval_to_graph = torch.arange(graphs, dtype=torch.int32, device=community_ids.device)
+        retrieval_to_kv = retrieval_to_graph
+    heads = retrieval_to_graph.numel()
+    live = int(community_counts.max())
+    capacity = live + max_decode_tokens
+    dim = keys.shape[-1]
+    labels = community_ids[retrieval_to_graph.long(), num_sink:].long()
+    rows = keys[retrieval_to_kv.long(), num_sink:].float()
+    sums = torch.zeros((heads, capacity, dim), dtype=torch.float32, device=keys.device)
+    sums.scatter_add_(1, labels.unsqueeze(-1).expand(-1, -1, dim), rows)
+    sizes = torch.zeros((heads, capacity), dtype=torch.int32, device=keys.device)
+    sizes.scatter_add_(1, labels, torch.ones_like(labels, dtype=torch.int32))
+    sums[:, :live] /= sizes[:, :live].float().clamp_min(1).unsqueeze(-1)
+    return sums.clamp_(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), sizes
+
+
+@dataclass(slots=True)
+class AssembledLayer:
+    """Everything ``DecodeRuntime.prepare_layer`` takes, built from labels and keys."""
+
+    member_offsets: torch.Tensor
+    member_positions: torch.Tensor
+    num_communities: torch.Tensor
+    centroids: torch.Tensor
+    community_sizes: torch.Tensor
+    community_weight: torch.Tensor
+    total_weight: torch.Tensor
+    token_communities: torch.Tensor
+    retrieval_to_graph: torch.Tensor
+    retrieval_to_kv: torch.Tensor
+
+
+def assemble_layer(
+    community_ids: torch.Tensor,
+    keys: torch.Tensor,
+    *,
+    aggregation: GraphAggregation | str,
+    query_heads: int,
+    num_sink: int,
+    max_decode_tokens: int,
+    community_weight: torch.Tensor | None = None,
+    total_weight: torch.Tensor | None = None,
+) -> AssembledLayer:
+    """Decode state of one layer from dense labels ``[graphs, S]`` and keys ``[Hkv, S, D]``.
+
+    Sink positions must carry labels of their own (size-zero communities after
+    the sink exclusion), like the reference's isolated-vertex fill.  Modularity
+    weights default to the community sizes (a unit-weight star per member),
+    which keeps the online rule well defined for synthetic labels.
+    """
+
+    graphs, length = community_ids.shape
+    kv_heads = keys.shape[0]
+    counts = (community_ids.amax(dim=1) + 1).to(torch.int32)
+    to_graph, to_kv = aggregation_mappings(
+        aggregation, query_heads=query_heads, kv_heads=kv_heads, device=keys.device
+    )
+    centroids, sizes = compute_centroids(
+        community_ids,
+        counts,
+        keys,
+        retrieval_to_graph=to_graph,
+        retrieval_to_kv=to_kv,
+        num_sink=num_sink,
+        max_decode_tokens=max_decode_tokens,
+    )
+    offsets, positions = build_member_csr(community_ids, counts, num_sink=num_sink)
+    capacity = centroids.shape[1]
+    if community_weight is None:
+        community_weight = torch.zeros((graphs, capacity), dtype=torch.float32, device=keys.device)
+        leaders = torch.unique(to_graph.long())
+        community_weight[:] = sizes[leaders].float() if leaders.numel() == graphs else 0.0
+    if total_weight is None:
+        total_weight = community_weight.sum(dim=1)
+    labels = torch.full(
+        (graphs, length + max_decode_tokens), -1, dtype=torch.int32, device=keys.device
+    )
+    labels[:, :length] = community_ids
+    return AssembledLayer(
+        member_offsets=offsets,
+        member_positions=positions,
+        num_communities=counts,
+        centroids=centroids,
+        community_sizes=sizes,
+        community_weight=community_weight,
+        total_weight=total_weight,
+        token_communities=labels,
+        retrieval_to_graph=to_graph,
+        retrieval_to_kv=to_kv,
+    )
+
+
+__all__ = [
+    "AssembledLayer",
+    "aggregation_mappings",
+    "assemble_layer",
+    "build_member_csr",
+    "compute_centroids",
+]

@@ -1,0 +1,73 @@
+"""Public configuration objects, same names and meaning as the reference's.
+
+Mirrors ``community_kv/config.py:9-70`` of the reference project: how query-head
+edge lists are aggregated into graphs, the per-request decode settings, and the
+prefill partition scheduling settings.
+"""
+
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass
+
+
+class GraphAggregation(str, enum.Enum):
+    """Which query heads share one token graph."""
+
+    PER_QUERY_HEAD = "per_query_head"
+    QUERY_GROUP = "query_group"
+    LAYER_WISE = "layer_wise"
+
+    def graph_count(self, *, query_heads: int, kv_heads: int) -> int:
+        if min(query_heads, kv_heads) <= 0 or query_heads % kv_heads != 0:
+            raise ValueError("query heads must divide evenly into KV-head groups")
+        return {
+            GraphAggregation.PER_QUERY_HEAD: query_heads,
+            GraphAggregation.QUERY_GROUP: kv_heads,
+            GraphAggregation.LAYER_WISE: 1,
+        }[self]
+
+    def retrieval_head_count(self, *, query_heads: int, kv_heads: int) -> int:
+        graphs = self.graph_count(query_heads=query_heads, kv_heads=kv_heads)
+        return graphs if graphs > kv_heads else kv_heads
+
+
+@dataclass(frozen=True, slots=True)
+class CommunityKVConfig:
+    """Settings that stay fixed for the lifetime of one request."""
+
+    token_budget: int = 4096
+    num_sink: int = 10
+    lam: float = 0.5
+    aggregation: GraphAggregation = GraphAggregation.PER_QUERY_HEAD
+    leiden_resolution: float = 1.0
+    leiden_seed: int = 0
+
+    def __post_init__(self) -> None:
+        object.__setattr__(self, "aggregation", GraphAggregation(self.aggregation))
+        problems = []
+        if self.token_budget <= 0 or self.token_budget % 64 != 0:
+            problems.append("token_budget must be a positive multiple of 64")
+        elif self.num_sink < 0 or self.num_sink + 1 >= self.token_budget:
+            problems.append("num_sink leaves no selected-token capacity")
+        if not (0.0 <= self.lam <= 1.0):
+            problems.append("lam must be in [0, 1]")
+        if self.leiden_resolution <= 0:
+            problems.append("leiden_resolution must be positive")
+        if problems:
+            raise ValueError(problems[0])
+
+
+@dataclass(frozen=True, slots=True)
+class PartitionConfig:
+    """Where and how wide the host-side prefill partition jobs run."""
+
+    devices: tuple[str, ...] = ()
+    workers_per_device: int = 2
+
+    def __post_init__(self) -> None:
+        if self.workers_per_device <= 0:
+            raise ValueError("workers_per_device must be positive")
+
+
+__all__ = ["CommunityKVConfig", "GraphAggregation", "PartitionConfig"]

@@ -1,0 +1,159 @@
+// C ABI of the sparse-decode path: argument validation and kernel sequencing.
+
+#include "ckv_device.cuh"
+
+namespace ckv {
+cudaError_t launch_score(const ckv_layer_args& a, cudaStream_t stream);
+cudaError_t launch_select(const ckv_layer_args& a, cudaStream_t stream);
+cudaError_t launch_resolve(const ckv_layer_args& a, cudaStream_t stream);
+cudaError_t launch_attention(const ckv_layer_args& a, cudaStream_t stream);
+cudaError_t launch_merge_update(const ckv_layer_args& a, cudaStream_t stream);
+int attention_smem_bytes();
+
+namespace {
+
+enum Need { kNeedScore = 1, kNeedSelect = 2, kNeedAttention = 4 };
+
+int check_common(const ckv_layer_args* a) {
+  if (a == nullptr) return CKV_ERR_NULL;
+  if (a->batch <= 0 || a->retrieval_heads <= 0 || a->graphs <= 0) return CKV_ERR_SHAPE;
+  if (a->group_size < 1 || a->group_size > 16) return CKV_ERR_SHAPE;
+  if (a->community_capacity <= 0) return CKV_ERR_SHAPE;
+  if (a->token_budget <= 0 || a->token_budget % CKV_TILE) return CKV_ERR_SHAPE;
+  if (a->num_sink < 0 || a->num_sink + 1 >= a->token_budget) return CKV_ERR_SHAPE;
+  if (static_cast<int64_t>(a->batch) * a->retrieval_heads > 65535) return CKV_ERR_CAPACITY;
+  if (a->retrieval_to_graph == nullptr || a->retrieval_to_kv == nullptr) return CKV_ERR_NULL;
+  return CKV_OK;
+}
+
+int check(const ckv_layer_args* a, int need) {
+  const int common = check_common(a);
+  if (common != CKV_OK) return common;
+  if (need & kNeedScore) {
+    if (!a->query || !a->centroids || !a->community_sizes || !a->community_counts || !a->scores)
+      return CKV_ERR_NULL;
+  }
+  if (need & kNeedSelect) {
+    if (!a->scores || !a->community_sizes || !a->community_counts || !a->communities ||
+        !a->cumulative_ends || !a->descriptor_counts || !a->tile_descriptors || !a->positions)
+      return CKV_ERR_NULL;
+    if (a->descriptor_capacity < a->token_budget - a->num_sink - 1) return CKV_ERR_SHAPE;
+    if (a->max_communities < 0) return CKV_ERR_SHAPE;
+  }
+  if (need & (kNeedSelect | kNeedAttention)) {
+    if (!a->member_offsets || !a->member_positions || !a->current_position ||
+        !a->delta_positions || !a->chunk_start || !a->chunk_size || !a->chunk_previous ||
+        !a->community_tail || !a->delta_sizes)
+      return CKV_ERR_NULL;
+    if (a->num_sink > 0 && !a->sink_positions) return CKV_ERR_NULL;
+    if (a->member_capacity <= 0 || a->chunks_per_graph <= 0 || a->delta_position_capacity <= 0)
+      return CKV_ERR_SHAPE;
+  }
+  if (need & kNeedAttention) {
+    if (!a->query || !a->key || !a->value || !a->positions || !a->partials || !a->partial_topk ||
+        !a->output || !a->lse || !a->topk_scores || !a->topk_positions || !a->communities ||
+        !a->cumulative_ends || !a->descriptor_counts)
+      return CKV_ERR_NULL;
+    if (a->splits <= 0 || a->splits > 32 || a->token_budget % (CKV_TILE * a->splits))
+      return CKV_ERR_SHAPE;
+    if (a->sequence_capacity <= 0 || a->token_capacity <= 0) return CKV_ERR_SHAPE;
+    if ((a->key_row_stride % 8) || (a->value_row_stride % 8) || (a->key_head_stride % 8) ||
+        (a->value_head_stride % 8) || (a->key_batch_stride % 8) || (a->value_batch_stride % 8) ||
+        (reinterpret_cast<uintptr_t>(a->key) % 16) || (reinterpret_cast<uintptr_t>(a->value) % 16))
+      return CKV_ERR_ALIGN;
+    if (a->key_row_stride < CKV_HEAD_DIM || a->value_row_stride < CKV_HEAD_DIM)
+      return CKV_ERR_SHAPE;
+    if (!(a->flags & CKV_FLAG_SKIP_UPDATE)) {
+      if (!a->centroids || !a->community_sizes || !a->community_counts || !a->community_weight ||
+          !a->total_weight || !a->token_communities || !a->chunk_capacity || !a->chunk_next ||
+          !a->community_head || !a->next_free_chunk || !a->next_free_position || !a->assigned ||
+          !a->overflow)
+        return CKV_ERR_NULL;
+    }
+  }
+  return CKV_OK;
+}
+
+int select_device(const ckv_layer_args* a) {
+  int current = -1;
+  if (cudaGetDevice(&current) != cudaSuccess) return CKV_ERR_DEVICE;
+  if (current != a->device) {
+    if (cudaSetDevice(a->device) != cudaSuccess) return CKV_ERR_DEVICE;
+  }
+  return CKV_OK;
+}
+
+int launched(cudaError_t err) { return err == cudaSuccess ? CKV_OK : CKV_ERR_LAUNCH; }
+
+}  // namespace
+}  // namespace ckv
+
+extern "C" {
+
+int ckv_version(void) { return 100; }
+
+const char* ckv_status_string(int status) {
+  switch (status) {
+    case CKV_OK: return "ok";
+    case CKV_ERR_NULL: return "a required pointer is null";
+    case CKV_ERR_SHAPE: return "a size or stride is out of range";
+    case CKV_ERR_ALIGN: return "K/V rows must be 16-byte aligned";
+    case CKV_ERR_LAUNCH: return "the CUDA runtime rejected a kernel launch";
+    case CKV_ERR_DEVICE: return "the CUDA device cannot be selected";
+    case CKV_ERR_UNSUPPORTED: return "unsupported configuration";
+    case CKV_ERR_CAPACITY: return "a size exceeds a fixed built-in maximum";
+    default: return "unknown status";
+  }
+}
+
+int ckv_attention_smem_bytes(int group_size) {
+  (void)group_size;
+  return ckv::attention_smem_bytes();
+}
+
+int ckv_score_centroids(const ckv_layer_args* args, void* cuda_stream) {
+  int status = ckv::check(args, ckv::kNeedScore);
+  if (status != CKV_OK) return status;
+  status = ckv::select_device(args);
+  if (status != CKV_OK) return status;
+  return ckv::launched(ckv::launch_score(*args, static_cast<cudaStream_t>(cuda_stream)));
+}
+
+int ckv_select_descriptors(const ckv_layer_args* args, void* cuda_stream) {
+  int status = ckv::check(args, ckv::kNeedSelect);
+  if (status != CKV_OK) return status;
+  status = ckv::select_device(args);
+  if (status != CKV_OK) return status;
+  return ckv::launched(ckv::launch_select(*args, static_cast<cudaStream_t>(cuda_stream)));
+}
+
+int ckv_segmented_attention(const ckv_layer_args* args, void* cuda_stream) {
+  int status = ckv::check(args, ckv::kNeedAttention);
+  if (status != CKV_OK) return status;
+  status = ckv::select_device(args);
+  if (status != CKV_OK) return status;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  status = ckv::launched(ckv::launch_resolve(*args, stream));
+  if (status != CKV_OK) return status;
+  status = ckv::launched(ckv::launch_attention(*args, stream));
+  if (status != CKV_OK) return status;
+  return ckv::launched(ckv::launch_merge_update(*args, stream));
+}
+
+int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream) {
+  int status =
+      ckv::check(args, ckv::kNeedScore | ckv::kNeedSelect | ckv::kNeedAttention);
+  if (status != CKV_OK) return status;
+  status = ckv::select_device(args);
+  if (status != CKV_OK) return status;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  status = ckv::launched(ckv::launch_score(*args, stream));
+  if (status != CKV_OK) return status;
+  status = ckv::launched(ckv::launch_select(*args, stream));
+  if (status != CKV_OK) return status;
+  status = ckv::launched(ckv::launch_attention(*args, stream));
+  if (status != CKV_OK) return status;
+  return ckv::launched(ckv::launch_merge_update(*args, stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,220 @@
+// Device-side helpers shared by the sparse-decode kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ckv_b200.h"
+
+namespace ckv {
+
+constexpr int kHeadDim = CKV_HEAD_DIM;
+constexpr int kTile = CKV_TILE;
+constexpr int kKappa = CKV_KAPPA;
+constexpr int kPartialStride = CKV_PARTIAL_STRIDE;
+constexpr int kMaxDeltaWalk = 32;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// One launch covers `batch * retrieval_heads` independent units.
+struct Unit {
+  int batch;
+  int head;
+  int graph;
+  int kv;
+};
+
+__device__ __forceinline__ Unit make_unit(const ckv_layer_args& a, int flat) {
+  Unit u;
+  u.batch = flat / a.retrieval_heads;
+  u.head = flat - u.batch * a.retrieval_heads;
+  u.graph = a.retrieval_to_graph[u.head];
+  u.kv = a.retrieval_to_kv[u.head];
+  return u;
+}
+
+__device__ __forceinline__ uint16_t ordered_key16(uint16_t bits) {
+  return bits ^ ((bits & 0x8000u) ? 0xffffu : 0x8000u);
+}
+
+__device__ __forceinline__ uint32_t ordered_key32(float value) {
+  const uint32_t bits = __float_as_uint(value);
+  return (bits & 0x80000000u) ? ~bits : (bits ^ 0x80000000u);
+}
+
+__device__ __forceinline__ float key32_to_float(uint32_t ordered) {
+  const uint32_t bits = (ordered & 0x80000000u) ? (ordered ^ 0x80000000u) : ~ordered;
+  return __uint_as_float(bits);
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t packed) {
+  return __uint_as_float(packed << 16);
+}
+__device__ __forceinline__ float bf16_hi(uint32_t packed) {
+  return __uint_as_float(packed & 0xffff0000u);
+}
+
+// Four e4m3 bytes -> four fp32 values (exact).
+__device__ __forceinline__ void fp8x4_to_float(uint32_t word, float* out) {
+  const __half2_raw lo =
+      __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(word & 0xffffu), __NV_E4M3);
+  const __half2_raw hi =
+      __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(word >> 16), __NV_E4M3);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+  out[0] = a.x;
+  out[1] = a.y;
+  out[2] = b.x;
+  out[3] = b.y;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* pointer) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
+}
+
+// ---- mbarrier + bulk async copy (TMA engine, 1-D, no multicast) ----
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait: gives up after `limit` polls and reports false.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit) {
+  for (uint32_t poll = 0; poll < limit; ++poll) {
+    if (mbar_try_wait(bar, parity)) {
+      return true;
+    }
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                              uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ---- warp-level tensor-core helpers (legacy mma path; the decode tiles are
+// 16 x 8 and HBM-bound, far below a tcgen05 tile) ----
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                            uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1,
+                                                  uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float low, float high) {
+  const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+  return *reinterpret_cast<const uint32_t*>(&pair);
+}
+
+__device__ __forceinline__ uint64_t shfl_xor_u64(uint64_t value, int mask) {
+  const uint32_t lo = __shfl_xor_sync(0xffffffffu, static_cast<uint32_t>(value), mask);
+  const uint32_t hi = __shfl_xor_sync(0xffffffffu, static_cast<uint32_t>(value >> 32), mask);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+__device__ __forceinline__ uint64_t warp_max_u64(uint64_t value) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    const uint64_t other = shfl_xor_u64(value, offset);
+    value = other > value ? other : value;
+  }
+  return value;
+}
+
+// Newest-first member of a community's decode-delta chain, or 0 when the chain
+// ends early (the same default the reference's masked load yields).
+__device__ __forceinline__ int delta_member_position(const ckv_layer_args& a, int64_t graph_slot,
+                                                     int community, int member) {
+  const int64_t chunk_base = graph_slot * a.chunks_per_graph;
+  int chunk = a.community_tail[graph_slot * a.community_capacity + community];
+  int remaining = member;
+  for (int step = 0; step < kMaxDeltaWalk && chunk >= 0; ++step) {
+    const int size = a.chunk_size[chunk_base + chunk];
+    if (remaining < size) {
+      const int start = a.chunk_start[chunk_base + chunk];
+      return a.delta_positions[graph_slot * a.delta_position_capacity + start + size - 1 -
+                               remaining];
+    }
+    remaining -= size;
+    chunk = a.chunk_previous[chunk_base + chunk];
+  }
+  return 0;
+}
+
+// Cache row of logical token `logical` (0..T-1) of one unit, -1 when masked.
+__device__ __forceinline__ int resolve_token(const ckv_layer_args& a, const Unit& u, int flat_unit,
+                                             int logical, int descriptor_count) {
+  const int64_t graph_slot = static_cast<int64_t>(u.batch) * a.graphs + u.graph;
+  if (logical < a.num_sink) {
+    return a.sink_positions[logical];
+  }
+  if (logical == a.token_budget - 1) {
+    return a.current_position[graph_slot];
+  }
+  const int offset = logical - a.num_sink;
+  const int32_t* ends = a.cumulative_ends + static_cast<int64_t>(flat_unit) * a.descriptor_capacity;
+  int low = 0;
+  int high = descriptor_count;
+  while (low < high) {
+    const int middle = (low + high) >> 1;
+    if (ends[middle] <= offset) {
+      low = middle + 1;
+    } else {
+      high = middle;
+    }
+  }
+  if (low >= descriptor_count) {
+    return -1;  // budget under-filled: nothing selected for this slot
+  }
+  const int previous_end = low > 0 ? ends[low - 1] : 0;
+  const int member = offset - previous_end;
+  const int community =
+      a.communities[static_cast<int64_t>(flat_unit) * a.descriptor_capacity + low];
+  const int delta_count = a.delta_sizes[graph_slot * a.community_capacity + community];
+  if (member < delta_count) {
+    return delta_member_position(a, graph_slot, community, member);
+  }
+  const int start = a.member_offsets[graph_slot * (a.community_capacity + 1) + community];
+  return a.member_positions[graph_slot * a.member_capacity + start + member - delta_count];
+}
+
+}  // namespace ckv

@@ -1,0 +1,178 @@
+"""ctypes binding of ``libckv_b200.so`` (the C ABI declared in ``include/ckv_b200.h``).
+
+There is no fallback: if the library is missing or an entry point reports an
+error the call raises.  The library is built in-tree by
+``community_kv_b200.build``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import functools
+from typing import Any
+
+import torch
+
+from community_kv_b200.build import LIBRARY_PATH
+
+_i32 = ctypes.c_int32
+_i64 = ctypes.c_int64
+_f32 = ctypes.c_float
+_ptr = ctypes.c_void_p
+
+
+class LayerArgs(ctypes.Structure):
+    """Field-for-field mirror of ``struct ckv_layer_args``."""
+
+    _fields_ = [
+        ("device", _i32),
+        ("batch", _i32),
+        ("retrieval_heads", _i32),
+        ("graphs", _i32),
+        ("group_size", _i32),
+        ("community_capacity", _i32),
+        ("token_budget", _i32),
+        ("num_sink", _i32),
+        ("sequence_capacity", _i32),
+        ("token_capacity", _i32),
+        ("member_capacity", _i32),
+        ("chunks_per_graph", _i32),
+        ("delta_position_capacity", _i32),
+        ("descriptor_capacity", _i32),
+        ("max_communities", _i32),
+        ("splits", _i32),
+        ("flags", _i32),
+        ("softmax_scale", _f32),
+        ("lam", _f32),
+        ("key_batch_stride", _i64),
+        ("key_head_stride", _i64),
+        ("key_row_stride", _i64),
+        ("value_batch_stride", _i64),
+        ("value_head_stride", _i64),
+        ("value_row_stride", _i64),
+        ("key", _ptr),
+        ("value", _ptr),
+        ("query", _ptr),
+        ("sink_positions", _ptr),
+        ("retrieval_to_graph", _ptr),
+        ("retrieval_to_kv", _ptr),
+        ("score_cover", _ptr),
+        ("member_offsets", _ptr),
+        ("member_positions", _ptr),
+        ("centroids", _ptr),
+        ("community_sizes", _ptr),
+        ("community_counts", _ptr),
+        ("community_weight", _ptr),
+        ("total_weight", _ptr),
+        ("token_communities", _ptr),
+        ("current_position", _ptr),
+        ("delta_positions", _ptr),
+        ("chunk_start", _ptr),
+        ("chunk_capacity", _ptr),
+        ("chunk_size", _ptr),
+        ("chunk_next", _ptr),
+        ("chunk_previous", _ptr),
+        ("community_head", _ptr),
+        ("community_tail", _ptr),
+        ("delta_sizes", _ptr),
+        ("next_free_chunk", _ptr),
+        ("next_free_position", _ptr),
+        ("scores", _ptr),
+        ("communities", _ptr),
+        ("cumulative_ends", _ptr),
+        ("descriptor_counts", _ptr),
+        ("tile_descriptors", _ptr),
+        ("threshold_state", _ptr),
+        ("positions", _ptr),
+        ("partials", _ptr),
+        ("partial_topk", _ptr),
+        ("output", _ptr),
+        ("lse", _ptr),
+        ("topk_scores", _ptr),
+        ("topk_positions", _ptr),
+        ("assigned", _ptr),
+        ("overflow", _ptr),
+        ("status", _ptr),
+    ]
+
+
+FLAG_SKIP_UPDATE = 1
+DEV_WAIT_TIMEOUT = 1
+PARTIAL_STRIDE = 130
+
+ENTRY_POINTS = (
+    "ckv_version",
+    "ckv_status_string",
+    "ckv_score_centroids",
+    "ckv_select_descriptors",
+    "ckv_segmented_attention",
+    "ckv_decode_layer",
+    "ckv_attention_smem_bytes",
+)
+
+
+class NativeError(RuntimeError):
+    """An entry point of the CUDA library returned a negative status."""
+
+
+@functools.cache
+def library() -> ctypes.CDLL:
+    if not LIBRARY_PATH.exists():
+        raise ImportError(
+            f"{LIBRARY_PATH} is missing: build it with `python -m community_kv_b200.build`; "
+            "this package has no CPU or framework fallback"
+        )
+    lib = ctypes.CDLL(str(LIBRARY_PATH))
+    lib.ckv_version.restype = ctypes.c_int
+    lib.ckv_status_string.restype = ctypes.c_char_p
+    lib.ckv_status_string.argtypes = [ctypes.c_int]
+    lib.ckv_attention_smem_bytes.restype = ctypes.c_int
+    lib.ckv_attention_smem_bytes.argtypes = [ctypes.c_int]
+    for name in (
+        "ckv_score_centroids",
+        "ckv_select_descriptors",
+        "ckv_segmented_attention",
+        "ckv_decode_layer",
+    ):
+        function = getattr(lib, name)
+        function.restype = ctypes.c_int
+        function.argtypes = [ctypes.POINTER(LayerArgs), ctypes.c_void_p]
+    return lib
+
+
+def pointer(tensor: torch.Tensor | None) -> int | None:
+    if tensor is None:
+        return None
+    return tensor.data_ptr()
+
+
+def current_stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def call(name: str, args: LayerArgs, stream: int) -> None:
+    status = getattr(library(), name)(ctypes.byref(args), ctypes.c_void_p(stream))
+    if status != 0:
+        message = library().ckv_status_string(status).decode()
+        raise NativeError(f"{name} failed with status {status}: {message}")
+
+
+def fill(args: LayerArgs, **values: Any) -> LayerArgs:
+    for key, value in values.items():
+        setattr(args, key, value)
+    return args
+
+
+__all__ = [
+    "DEV_WAIT_TIMEOUT",
+    "ENTRY_POINTS",
+    "FLAG_SKIP_UPDATE",
+    "LayerArgs",
+    "NativeError",
+    "PARTIAL_STRIDE",
+    "call",
+    "current_stream",
+    "fill",
+    "library",
+    "pointer",
+]

@@ -1,0 +1,506 @@
+"""Decode-path operators: same call signatures as the reference's kernel launchers.
+
+``score_centroids``, ``select_weighted_descriptors_*``, ``score_and_select``
+(reference ``community_kv/attention/kernels/centroid_selection.py:330-556``),
+``segmented_attention`` / ``triton_segmented_attention``
+(``segmented_attention.py:1016-1273``) and ``decode_layer``
+(``community_kv/attention/decode.py:67-111``).  Each one validates its tensors
+like the reference does and then makes exactly one call into the CUDA library.
+Tensors may carry a leading batch axis (see ``community_kv_b200.state``).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from community_kv_b200 import native
+from community_kv_b200.state import (
+    ATTENTION_TILE,
+    HEAD_DIM,
+    CentroidSelectionWorkspace,
+    DecodeDeltaChunks,
+    DecodeLayerWorkspace,
+    MutableGraphState,
+    OnlineUpdateWorkspace,
+    PackedSegments,
+    PrefillCSR,
+    SegmentedAttentionWorkspace,
+)
+
+
+def _require_cuda(*tensors: torch.Tensor) -> torch.device:
+    device = tensors[0].device
+    if device.type != "cuda":
+        raise RuntimeError(
+            "community_kv_b200 operators run only on CUDA tensors; there is no CPU path"
+        )
+    if any(tensor.device != device for tensor in tensors):
+        raise ValueError("all operator tensors must share one device")
+    return device
+
+
+def _contiguous(name: str, tensor: torch.Tensor) -> torch.Tensor:
+    if not tensor.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return tensor
+
+
+def _score_args(
+    args: native.LayerArgs,
+    *,
+    query: torch.Tensor,
+    centroids: torch.Tensor,
+    community_sizes: torch.Tensor,
+    community_counts: torch.Tensor,
+    workspace: CentroidSelectionWorkspace,
+) -> None:
+    batched = centroids.ndim == 4
+    heads = workspace.kv_heads
+    if query.ndim != (3 if batched else 2) or query.shape[-1] != HEAD_DIM or query.shape[-2] % heads:
+        raise ValueError("query heads must divide into [KV head, group, 128]")
+    group = query.shape[-2] // heads
+    if not 1 <= group <= 16:
+        raise ValueError("GQA group size must be in [1, 16]")
+    lead = tuple(centroids.shape[:-3])
+    if tuple(centroids.shape[-3:]) != (heads, workspace.community_capacity, HEAD_DIM) or tuple(
+        workspace.scores.shape[:-2]
+    ) != lead:
+        raise ValueError("centroids have the wrong fixed capacity")
+    if community_sizes.shape != centroids.shape[:-1]:
+        raise ValueError("community_sizes must match centroid rows")
+    if community_counts.shape != lead + (heads,):
+        raise ValueError("community_counts must have one entry per KV head")
+    if query.dtype != torch.bfloat16:
+        raise TypeError("query must use BF16")
+    if centroids.dtype != torch.float8_e4m3fn:
+        raise TypeError("centroids must use FP8 E4M3")
+    if community_sizes.dtype != torch.int32:
+        raise TypeError("community_sizes must use int32")
+    if community_counts.dtype != torch.int32:
+        raise TypeError("community_counts must use int32")
+    native.fill(
+        args,
+        batch=lead[0] if lead else 1,
+        retrieval_heads=heads,
+        group_size=group,
+        community_capacity=workspace.community_capacity,
+        token_budget=workspace.token_budget,
+        num_sink=workspace.num_sink,
+        max_communities=workspace.max_communities,
+        descriptor_capacity=workspace.communities.shape[-1],
+        query=native.pointer(_contiguous("query", query)),
+        centroids=native.pointer(_contiguous("centroids", centroids)),
+        community_sizes=native.pointer(_contiguous("community_sizes", community_sizes)),
+        community_counts=native.pointer(_contiguous("community_counts", community_counts)),
+        score_cover=native.pointer(workspace.score_cover),
+        scores=native.pointer(workspace.scores),
+        communities=native.pointer(workspace.communities),
+        cumulative_ends=native.pointer(workspace.cumulative_ends),
+        descriptor_counts=native.pointer(workspace.descriptor_counts),
+        tile_descriptors=native.pointer(workspace.tile_descriptors),
+        threshold_state=native.pointer(workspace.native_threshold),
+        positions=native.pointer(workspace.positions),
+    )
+
+
+def _graph_args(
+    args: native.LayerArgs,
+    *,
+    csr: PrefillCSR,
+    state: MutableGraphState,
+    sink_positions: torch.Tensor,
+    current_position: torch.Tensor,
+) -> None:
+    deltas = state.deltas
+    if sink_positions.dtype != torch.int32 or current_position.dtype != torch.int32:
+        raise TypeError("sink_positions and current_position must use int32")
+    native.fill(
+        args,
+        graphs=state.graph_count,
+        retrieval_heads=state.retrieval_head_count,
+        community_capacity=state.community_capacity,
+        token_capacity=state.token_communities.shape[-1],
+        member_capacity=csr.member_positions.shape[-1],
+        chunks_per_graph=deltas.chunk_capacity_per_graph,
+        delta_position_capacity=deltas.position_capacity,
+        sink_positions=native.pointer(sink_positions),
+        retrieval_to_graph=native.pointer(state.retrieval_to_graph),
+        retrieval_to_kv=native.pointer(state.retrieval_to_kv),
+        member_offsets=native.pointer(_contiguous("member_offsets", csr.member_offsets)),
+        member_positions=native.pointer(_contiguous("member_positions", csr.member_positions)),
+        centroids=native.pointer(state.centroids),
+        community_sizes=native.pointer(state.community_sizes),
+        community_counts=native.pointer(state.community_counts),
+        community_weight=native.pointer(state.community_weight),
+        total_weight=native.pointer(state.total_weight),
+        token_communities=native.pointer(state.token_communities),
+        current_position=native.pointer(current_position),
+        delta_positions=native.pointer(deltas.positions),
+        chunk_start=native.pointer(deltas.chunk_start),
+        chunk_capacity=native.pointer(deltas.chunk_capacity),
+        chunk_size=native.pointer(deltas.chunk_size),
+        chunk_next=native.pointer(deltas.chunk_next),
+        chunk_previous=native.pointer(deltas.chunk_previous),
+        community_head=native.pointer(deltas.community_head),
+        community_tail=native.pointer(deltas.community_tail),
+        delta_sizes=native.pointer(deltas.community_sizes),
+        next_free_chunk=native.pointer(deltas.next_free_chunk),
+        next_free_position=native.pointer(deltas.next_free_position),
+    )
+
+
+def _attention_args(
+    args: native.LayerArgs,
+    *,
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    softmax_scale: float,
+    lam: float,
+    workspace: SegmentedAttentionWorkspace,
+    update: OnlineUpdateWorkspace | None,
+    token_budget: int,
+) -> None:
+    batched = key.ndim == 4
+    if key.ndim not in (3, 4) or value.shape != key.shape or key.shape[-1] != HEAD_DIM:
+        raise ValueError("key and value must have shape [Hkv, S, 128]")
+    if query.dtype != torch.bfloat16 or key.dtype != query.dtype or value.dtype != query.dtype:
+        raise TypeError("query, key, and value must use BF16")
+    if token_budget % ATTENTION_TILE:
+        raise ValueError("token budget must be a multiple of 64")
+    if key.stride(-1) != 1 or value.stride(-1) != 1:
+        raise ValueError("key and value rows must be contiguous")
+    if not 0.0 <= lam <= 1.0:
+        raise ValueError("update_lam must be in [0, 1]")
+    native.fill(
+        args,
+        group_size=workspace.group_size,
+        splits=workspace.splits,
+        token_budget=token_budget,
+        sequence_capacity=key.shape[-2],
+        softmax_scale=float(softmax_scale),
+        lam=float(lam),
+        key=native.pointer(key),
+        value=native.pointer(value),
+        key_batch_stride=key.stride(0) if batched else 0,
+        key_head_stride=key.stride(-3),
+        key_row_stride=key.stride(-2),
+        value_batch_stride=value.stride(0) if batched else 0,
+        value_head_stride=value.stride(-3),
+        value_row_stride=value.stride(-2),
+        query=native.pointer(_contiguous("query", query)),
+        partials=native.pointer(workspace.partials),
+        partial_topk=native.pointer(workspace.partial_topk_packed),
+        output=native.pointer(workspace.output),
+        lse=native.pointer(workspace.lse),
+        topk_scores=native.pointer(workspace.topk_scores),
+        topk_positions=native.pointer(workspace.topk_positions),
+        status=native.pointer(workspace.status),
+        flags=0 if update is not None else native.FLAG_SKIP_UPDATE,
+        assigned=native.pointer(update.assigned_communities) if update is not None else None,
+        overflow=native.pointer(update.overflow) if update is not None else None,
+    )
+
+
+def score_centroids(
+    *,
+    query: torch.Tensor,
+    centroids: torch.Tensor,
+    community_sizes: torch.Tensor,
+    community_counts: torch.Tensor,
+    workspace: CentroidSelectionWorkspace,
+) -> torch.Tensor:
+    """Score each contiguous query group against its centroid table (fp16 out)."""
+
+    args = native.LayerArgs()
+    _score_args(
+        args,
+        query=query,
+        centroids=centroids,
+        community_sizes=community_sizes,
+        community_counts=community_counts,
+        workspace=workspace,
+    )
+    device = _require_cuda(query, centroids, community_sizes, community_counts, workspace.scores)
+    # identity mappings are not read by the scoring kernel beyond make_unit()
+    mapping = torch.arange(workspace.kv_heads, dtype=torch.int32, device=device)
+    native.fill(
+        args,
+        device=device.index or 0,
+        graphs=workspace.kv_heads,
+        retrieval_to_graph=native.pointer(mapping),
+        retrieval_to_kv=native.pointer(mapping),
+    )
+    native.call("ckv_score_centroids", args, native.current_stream(device))
+    return workspace.scores
+
+
+def _select(
+    *,
+    community_sizes: torch.Tensor,
+    community_counts: torch.Tensor,
+    workspace: CentroidSelectionWorkspace,
+    csr: PrefillCSR,
+    state: MutableGraphState,
+    sink_positions: torch.Tensor,
+    current_position: torch.Tensor,
+) -> PackedSegments:
+    if community_sizes.shape != workspace.scores.shape:
+        raise ValueError("community_sizes must match the score capacity")
+    if community_sizes.dtype != torch.int32:
+        raise TypeError("community_sizes must use int32")
+    if community_counts.shape != workspace.scores.shape[:-1]:
+        raise ValueError("community_counts must have one entry per KV head")
+    if community_counts.dtype != torch.int32:
+        raise TypeError("community_counts must use int32")
+    device = _require_cuda(workspace.scores, community_sizes, community_counts)
+    args = native.LayerArgs()
+    _graph_args(
+        args, csr=csr, state=state, sink_positions=sink_positions, current_position=current_position
+    )
+    native.fill(
+        args,
+        device=device.index or 0,
+        batch=workspace.batch or 1,
+        group_size=1,
+        token_budget=workspace.token_budget,
+        num_sink=workspace.num_sink,
+        max_communities=workspace.max_communities,
+        descriptor_capacity=workspace.communities.shape[-1],
+        community_sizes=native.pointer(community_sizes),
+        community_counts=native.pointer(community_counts),
+        scores=native.pointer(workspace.scores),
+        communities=native.pointer(workspace.communities),
+        cumulative_ends=native.pointer(workspace.cumulative_ends),
+        descriptor_counts=native.pointer(workspace.descriptor_counts),
+        tile_descriptors=native.pointer(workspace.tile_descriptors),
+        threshold_state=native.pointer(workspace.native_threshold),
+        positions=native.pointer(workspace.positions),
+    )
+    native.call("ckv_select_descriptors", args, native.current_stream(device))
+    return workspace.packed_segments()
+
+
+def select_weighted_descriptors_native(**kwargs) -> PackedSegments:
+    """Exact budgeted selection from the fp16 scores already in the workspace.
+
+    Besides the reference's ``community_sizes``, ``community_counts`` and
+    ``workspace`` it needs ``csr``, ``state``, ``sink_positions`` and
+    ``current_position`` because the same kernel also resolves the selected
+    members to cache rows.
+    """
+
+    return _select(**kwargs)
+
+
+select_weighted_descriptors_cluster = select_weighted_descriptors_native
+select_weighted_descriptors_auto = select_weighted_descriptors_native
+
+
+def score_and_select(
+    *,
+    query: torch.Tensor,
+    centroids: torch.Tensor,
+    community_sizes: torch.Tensor,
+    community_counts: torch.Tensor,
+    workspace: CentroidSelectionWorkspace,
+    csr: PrefillCSR,
+    state: MutableGraphState,
+    sink_positions: torch.Tensor,
+    current_position: torch.Tensor,
+) -> PackedSegments:
+    score_centroids(
+        query=query,
+        centroids=centroids,
+        community_sizes=community_sizes,
+        community_counts=community_counts,
+        workspace=workspace,
+    )
+    return _select(
+        community_sizes=community_sizes,
+        community_counts=community_counts,
+        workspace=workspace,
+        csr=csr,
+        state=state,
+        sink_positions=sink_positions,
+        current_position=current_position,
+    )
+
+
+def _check_update(state: MutableGraphState, deltas: DecodeDeltaChunks, csr: PrefillCSR) -> None:
+    if state.deltas is not deltas:
+        raise ValueError("fused update must mutate the attention delta store")
+    if deltas.community_capacity != csr.community_capacity:
+        raise ValueError("delta chunks must match CSR community capacity")
+    if state.head_dim != HEAD_DIM:
+        raise ValueError("update state must use head_dim=128")
+
+
+def segmented_attention(
+    *,
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    csr: PrefillCSR,
+    deltas: DecodeDeltaChunks,
+    segments: PackedSegments,
+    sink_positions: torch.Tensor,
+    current_position: torch.Tensor,
+    softmax_scale: float,
+    workspace: SegmentedAttentionWorkspace,
+    update_state: MutableGraphState,
+    update_workspace: OnlineUpdateWorkspace | None,
+    update_lam: float,
+    positions: torch.Tensor | None = None,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gather the selected members' K/V rows and run exact split attention.
+
+    ``update_workspace=None`` skips the online assignment (attention only).
+    Returns ``(output, lse, topk_scores, topk_positions)``, aliases of the
+    workspace tensors.
+    """
+
+    _check_update(update_state, deltas, csr)
+    device = _require_cuda(query, key, value, segments.communities)
+    heads = update_state.retrieval_head_count
+    if query.shape[-2:] != (heads * workspace.group_size, HEAD_DIM):
+        raise ValueError(
+            f"query must have {workspace.group_size} [128] heads per retrieval head"
+        )
+    if positions is None:
+        positions = torch.empty(
+            segments.communities.shape[:-1] + (segments.token_budget,),
+            dtype=torch.int32,
+            device=device,
+        )
+    args = native.LayerArgs()
+    _graph_args(
+        args,
+        csr=csr,
+        state=update_state,
+        sink_positions=sink_positions,
+        current_position=current_position,
+    )
+    _attention_args(
+        args,
+        query=query,
+        key=key,
+        value=value,
+        softmax_scale=softmax_scale,
+        lam=update_lam,
+        workspace=workspace,
+        update=update_workspace,
+        token_budget=segments.token_budget,
+    )
+    native.fill(
+        args,
+        device=device.index or 0,
+        batch=key.shape[0] if key.ndim == 4 else 1,
+        num_sink=segments.num_sink,
+        descriptor_capacity=segments.communities.shape[-1],
+        communities=native.pointer(segments.communities),
+        cumulative_ends=native.pointer(segments.cumulative_ends),
+        descriptor_counts=native.pointer(segments.descriptor_counts),
+        tile_descriptors=native.pointer(segments.tile_descriptors),
+        positions=native.pointer(positions),
+    )
+    native.call("ckv_segmented_attention", args, native.current_stream(device))
+    return workspace.output, workspace.lse, workspace.topk_scores, workspace.topk_positions
+
+
+triton_segmented_attention = segmented_attention
+
+
+def build_layer_args(
+    *,
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    csr: PrefillCSR,
+    state: MutableGraphState,
+    sink_positions: torch.Tensor,
+    current_position: torch.Tensor,
+    softmax_scale: float,
+    lam: float,
+    workspace: DecodeLayerWorkspace,
+) -> native.LayerArgs:
+    """Validate one layer's tensors and pack them for ``ckv_decode_layer``."""
+
+    device = _require_cuda(query, key, value, state.centroids)
+    _check_update(state, state.deltas, csr)
+    args = native.LayerArgs()
+    _score_args(
+        args,
+        query=query,
+        centroids=state.centroids,
+        community_sizes=state.community_sizes,
+        community_counts=state.community_counts,
+        workspace=workspace.selection,
+    )
+    _graph_args(
+        args, csr=csr, state=state, sink_positions=sink_positions, current_position=current_position
+    )
+    _attention_args(
+        args,
+        query=query,
+        key=key,
+        value=value,
+        softmax_scale=softmax_scale,
+        lam=lam,
+        workspace=workspace.attention,
+        update=workspace.update,
+        token_budget=workspace.selection.token_budget,
+    )
+    native.fill(args, device=device.index or 0)
+    return args
+
+
+def decode_layer(
+    *,
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    csr: PrefillCSR,
+    state: MutableGraphState,
+    sink_positions: torch.Tensor,
+    current_position: torch.Tensor,
+    softmax_scale: float,
+    lam: float,
+    workspace: DecodeLayerWorkspace,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Run one complete layer transition: score, select, attend, assign."""
+
+    args = build_layer_args(
+        query=query,
+        key=key,
+        value=value,
+        csr=csr,
+        state=state,
+        sink_positions=sink_positions,
+        current_position=current_position,
+        softmax_scale=softmax_scale,
+        lam=lam,
+        workspace=workspace,
+    )
+    native.call("ckv_decode_layer", args, native.current_stream(query.device))
+    attention = workspace.attention
+    return (
+        attention.output,
+        attention.lse,
+        attention.topk_scores,
+        attention.topk_positions,
+        workspace.update.assigned_communities,
+    )
+
+
+__all__ = [
+    "build_layer_args",
+    "decode_layer",
+    "score_and_select",
+    "score_centroids",
+    "segmented_attention",
+    "select_weighted_descriptors_auto",
+    "select_weighted_descriptors_cluster",
+    "select_weighted_descriptors_native",
+    "triton_segmented_attention",
+]

@@ -1,0 +1,189 @@
+"""Seeded synthetic decode workloads with the shapes of the benchmark configurations.
+
+No dataset is involved: keys are planted Gaussian clusters (or plain Gaussian
+rows with Zipf-sized random communities), labels are the cluster ids, and the
+decode state is assembled from them exactly like a partitioned prefill would be
+(``community_kv_b200.assembly``).  Used by the tests, the smoke check and the
+benchmark to build inputs; it is not on the decode path.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from community_kv_b200.assembly import AssembledLayer, aggregation_mappings, assemble_layer
+from community_kv_b200.config import GraphAggregation
+
+HEAD_DIM = 128
+
+
+@dataclass(slots=True)
+class SyntheticLayer:
+    """One layer of one sequence: cache, labels, assembled decode state."""
+
+    key: torch.Tensor  # [Hkv, S_cap, 128] bf16
+    value: torch.Tensor
+    labels: torch.Tensor  # [graphs, S] int32
+    assembled: AssembledLayer
+    prefill_seq_len: int
+    max_decode_tokens: int
+    group_size: int
+    query_heads: int
+    kv_heads: int
+    aggregation: GraphAggregation
+
+    def prepare_kwargs(self) -> dict:
+        """Keyword arguments for ``DecodeRuntime.prepare_layer`` / ``convert_prefill_tensors``."""
+
+        a = self.assembled
+        return dict(
+            member_offsets=a.member_offsets,
+            member_positions=a.member_positions,
+            num_communities=a.num_communities,
+            centroids=a.centroids,
+            community_sizes=a.community_sizes,
+            community_weight=a.community_weight,
+            total_weight=a.total_weight,
+            token_communities=a.token_communities,
+            retrieval_to_graph=a.retrieval_to_graph,
+            retrieval_to_kv=a.retrieval_to_kv,
+            prefill_seq_len=self.prefill_seq_len,
+            max_decode_tokens=self.max_decode_tokens,
+            group_size=self.group_size,
+            aggregation=self.aggregation,
+            query_heads=self.query_heads,
+            kv_heads=self.kv_heads,
+        )
+
+    def to(self, device: torch.device | str) -> "SyntheticLayer":
+        a = self.assembled
+        moved = AssembledLayer(**{name: getattr(a, name).to(device) for name in a.__slots__})
+        return SyntheticLayer(
+            key=self.key.to(device),
+            value=self.value.to(device),
+            labels=self.labels.to(device),
+            assembled=moved,
+            prefill_seq_len=self.prefill_seq_len,
+            max_decode_tokens=self.max_decode_tokens,
+            group_size=self.group_size,
+            query_heads=self.query_heads,
+            kv_heads=self.kv_heads,
+            aggregation=self.aggregation,
+        )
+
+
+def zipf_sizes(total: int, communities: int, exponent: float, generator: torch.Generator) -> torch.Tensor:
+    """Positive integer sizes summing to ``total``, proportional to rank**-exponent."""
+
+    rank = torch.arange(1, communities + 1, dtype=torch.float64)
+    share = rank.pow(-exponent)
+    share = share / share.sum()
+    sizes = torch.floor(share * (total - communities)).long() + 1
+    shortfall = total - int(sizes.sum())
+    if shortfall > 0:
+        extra = torch.multinomial(share, shortfall, replacement=True, generator=generator)
+        sizes += torch.bincount(extra, minlength=communities)
+    return sizes[torch.randperm(communities, generator=generator)]
+
+
+def make_layer(
+    *,
+    seed: int,
+    kv_heads: int = 8,
+    group_size: int = 4,
+    seq_len: int = 8192,
+    communities: int = 64,
+    sigma: float = 0.3,
+    num_sink: int = 10,
+    max_decode_tokens: int = 16,
+    aggregation: GraphAggregation | str = GraphAggregation.QUERY_GROUP,
+    zipf_exponent: float | None = None,
+    integer_valued: bool = False,
+) -> SyntheticLayer:
+    """Planted-cluster layer on the CPU.
+
+    ``zipf_exponent=None``: keys are ``centre + sigma * noise`` with multinomial
+    cluster sizes, labels are the cluster ids.  With an exponent: keys are plain
+    Gaussian rows and labels are random with Zipf-distributed community sizes.
+    ``integer_valued`` draws small integers for every operand so that all fp32
+    sums are exact whatever their order.
+    """
+
+    aggregation = GraphAggregation(aggregation)
+    generator = torch.Generator().manual_seed(seed)
+    query_heads = kv_heads * group_size
+    rows = seq_len + max_decode_tokens + 1
+    to_graph, _ = aggregation_mappings(aggregation, query_heads=query_heads, kv_heads=kv_heads)
+    graphs = int(to_graph.max()) + 1
+    heads_per_graph = {GraphAggregation.PER_QUERY_HEAD: group_size}.get(aggregation, 1)
+
+    kv_labels = torch.empty((kv_heads, seq_len), dtype=torch.int64)
+    if zipf_exponent is None:
+        centres = torch.randn((kv_heads, communities, HEAD_DIM), generator=generator)
+        for head in range(kv_heads):
+            kv_labels[head] = torch.multinomial(
+                torch.ones(communities), seq_len, replacement=True, generator=generator
+            )
+            kv_labels[head, :communities] = torch.randperm(communities, generator=generator)
+        noise = torch.randn((kv_heads, rows, HEAD_DIM), generator=generator) * sigma
+        padded = torch.cat(
+            (kv_labels, torch.randint(0, communities, (kv_heads, rows - seq_len), generator=generator)),
+            dim=1,
+        )
+        key = torch.gather(centres, 1, padded.unsqueeze(-1).expand(-1, -1, HEAD_DIM)) + noise
+    else:
+        for head in range(kv_heads):
+            sizes = zipf_sizes(seq_len, communities, zipf_exponent, generator)
+            ids = torch.repeat_interleave(torch.arange(communities), sizes)
+            kv_labels[head] = ids[torch.randperm(seq_len, generator=generator)]
+        key = torch.randn((kv_heads, rows, HEAD_DIM), generator=generator)
+    value = torch.randn((kv_heads, rows, HEAD_DIM), generator=generator)
+    if integer_valued:
+        key = torch.randint(-3, 4, key.shape, generator=generator).float()
+        value = torch.randint(-3, 4, value.shape, generator=generator).float()
+    else:
+        key = key / HEAD_DIM**0.5
+        value = value / HEAD_DIM**0.5
+    key = key.to(torch.bfloat16)
+    value = value.to(torch.bfloat16)
+
+    if aggregation is GraphAggregation.LAYER_WISE:
+        labels = kv_labels[:1]
+    elif aggregation is GraphAggregation.QUERY_GROUP:
+        labels = kv_labels
+    else:
+        labels = kv_labels.repeat_interleave(heads_per_graph, dim=0)
+    labels = labels.to(torch.int32).contiguous()
+    assert labels.shape[0] == graphs
+    assembled = assemble_layer(
+        labels,
+        key[:, :seq_len],
+        aggregation=aggregation,
+        query_heads=query_heads,
+        num_sink=num_sink,
+        max_decode_tokens=max_decode_tokens,
+    )
+    return SyntheticLayer(
+        key=key,
+        value=value,
+        labels=labels,
+        assembled=assembled,
+        prefill_seq_len=seq_len,
+        max_decode_tokens=max_decode_tokens,
+        group_size=query_heads // assembled.retrieval_to_graph.numel(),
+        query_heads=query_heads,
+        kv_heads=kv_heads,
+        aggregation=aggregation,
+    )
+
+
+def make_query(*, seed: int, query_heads: int, integer_valued: bool = False) -> torch.Tensor:
+    generator = torch.Generator().manual_seed(seed)
+    if integer_valued:
+        return torch.randint(-2, 3, (query_heads, HEAD_DIM), generator=generator).to(torch.bfloat16)
+    return torch.randn((query_heads, HEAD_DIM), generator=generator).to(torch.bfloat16)
+
+
+__all__ = ["SyntheticLayer", "make_layer", "make_query", "zipf_sizes"]

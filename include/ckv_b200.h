@@ -1,0 +1,161 @@
+/*
+ * ckv_b200.h - C ABI of the B200 (sm_100a) CommunityKV sparse-decode hot path.
+ *
+ * Every entry point takes plain pointers and sizes (no framework types), never
+ * allocates, never synchronises, and enqueues its kernels on the CUDA stream it
+ * is given.  The return value is 0 on success or a negative ckv_status code.
+ * Device-side trouble that cannot be known on the host (a bounded wait that ran
+ * out) is reported by OR-ing bits into the optional `status` word.
+ *
+ * All per-sequence tensors carry a leading `batch` dimension and are stored
+ * batch-major and contiguous: element [b, ...] lives at b * (product of the
+ * remaining extents).  `batch` is the number of independent sequence slots in
+ * one launch; with batch == 1 the layouts are exactly the reference's per-layer
+ * tensors.  The K/V cache alone uses explicit strides because it belongs to the
+ * host framework's cache object.
+ *
+ * Reference interfaces these entry points stand in for (paths inside the
+ * reference project):
+ *   ckv_score_centroids      score_centroids(), the Triton launcher
+ *                            community_kv/attention/kernels/centroid_selection.py:330-445
+ *   ckv_select_descriptors   _selection_native.select_weighted_descriptors
+ *                            community_kv/attention/kernels/_csrc/bindings.cpp:3-22
+ *                            (descriptor_selection.cu:852-1189)
+ *   ckv_segmented_attention  triton_segmented_attention()
+ *                            community_kv/attention/kernels/segmented_attention.py:1016-1273
+ *   ckv_decode_layer         decode_layer()  community_kv/attention/decode.py:67-111
+ *   ckv_prefill_topk         torch.ops.flash_attn_3.fwd(..., exclude_sink_tokens=n)
+ *                            community_kv/attention/flash_attention.py:23-51
+ *                            (third_party/flash_attention/community-kv.patch)
+ */
+#ifndef CKV_B200_H_
+#define CKV_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CKV_HEAD_DIM 128
+#define CKV_TILE 64
+#define CKV_KAPPA 8
+#define CKV_PARTIAL_STRIDE 130 /* floats per (split, head): max, sum, acc[128] */
+
+typedef enum ckv_status {
+  CKV_OK = 0,
+  CKV_ERR_NULL = -1,      /* a required pointer is null */
+  CKV_ERR_SHAPE = -2,     /* a size or stride is out of range */
+  CKV_ERR_ALIGN = -3,     /* K/V rows are not 16-byte aligned */
+  CKV_ERR_LAUNCH = -4,    /* the CUDA runtime rejected a launch */
+  CKV_ERR_DEVICE = -5,    /* the device index cannot be selected */
+  CKV_ERR_UNSUPPORTED = -6,
+  CKV_ERR_CAPACITY = -7   /* a size exceeds a fixed built-in maximum */
+} ckv_status;
+
+/* bits OR-ed into *status by the kernels */
+#define CKV_DEV_WAIT_TIMEOUT 1u /* a bounded mbarrier wait gave up */
+
+/* flags */
+#define CKV_FLAG_SKIP_UPDATE 1 /* attention only: leave the graph state untouched */
+
+typedef struct ckv_layer_args {
+  /* ---- geometry ---- */
+  int32_t device;             /* CUDA device ordinal that owns every pointer */
+  int32_t batch;              /* independent sequence slots in this launch */
+  int32_t retrieval_heads;    /* R */
+  int32_t graphs;             /* number of graphs (R, or 1 when one graph is shared) */
+  int32_t group_size;         /* query heads per retrieval head, 1..16 */
+  int32_t community_capacity; /* centroid rows per retrieval head */
+  int32_t token_budget;       /* T, multiple of 64 */
+  int32_t num_sink;
+  int32_t sequence_capacity;  /* rows per head in the K/V cache */
+  int32_t token_capacity;     /* width of token_communities */
+  int32_t member_capacity;    /* width of member_positions */
+  int32_t chunks_per_graph;
+  int32_t delta_position_capacity;
+  int32_t descriptor_capacity; /* width of communities / cumulative_ends, >= T - num_sink - 1 */
+  int32_t max_communities;    /* 0: fill the token budget (reference behaviour); k>0: at most k communities */
+  int32_t splits;             /* attention CTAs per retrieval head; T % (64*splits) == 0 */
+  int32_t flags;
+  float softmax_scale;
+  float lam;
+  /* ---- K/V cache, bf16, element strides; a row is 128 contiguous elements ---- */
+  int64_t key_batch_stride, key_head_stride, key_row_stride;
+  int64_t value_batch_stride, value_head_stride, value_row_stride;
+  const void* key;
+  const void* value;
+  /* ---- per-call inputs ---- */
+  const void* query;                 /* bf16 [batch, R*G, 128] */
+  const int32_t* sink_positions;     /* [num_sink], shared by the batch */
+  const int32_t* retrieval_to_graph; /* [R], shared by the batch */
+  const int32_t* retrieval_to_kv;    /* [R], shared by the batch */
+  const int32_t* score_cover;        /* [batch, R] or null: score only rows below ceil64(min(capacity, cover)) */
+  /* ---- immutable prefill CSR ---- */
+  const int32_t* member_offsets;   /* [batch, graphs, capacity+1] */
+  const int32_t* member_positions; /* [batch, graphs, member_capacity] */
+  /* ---- mutable graph state ---- */
+  void* centroids;             /* e4m3 [batch, R, capacity, 128] */
+  int32_t* community_sizes;    /* [batch, R, capacity] */
+  int32_t* community_counts;   /* [batch, R] */
+  float* community_weight;     /* [batch, graphs, capacity] */
+  float* total_weight;         /* [batch, graphs] */
+  int32_t* token_communities;  /* [batch, graphs, token_capacity] */
+  int32_t* current_position;   /* [batch, graphs] */
+  int32_t* delta_positions;    /* [batch, graphs, delta_position_capacity] */
+  int32_t* chunk_start;        /* [batch, graphs, chunks_per_graph] (and the four below) */
+  int32_t* chunk_capacity;
+  int32_t* chunk_size;
+  int32_t* chunk_next;
+  int32_t* chunk_previous;
+  int32_t* community_head;     /* [batch, graphs, capacity] (and the two below) */
+  int32_t* community_tail;
+  int32_t* delta_sizes;
+  int32_t* next_free_chunk;    /* [batch, graphs] */
+  int32_t* next_free_position; /* [batch, graphs] */
+  /* ---- selection workspace ---- */
+  void* scores;                /* fp16 [batch, R, capacity] */
+  int32_t* communities;        /* [batch, R, descriptor_capacity] */
+  int32_t* cumulative_ends;    /* [batch, R, descriptor_capacity] */
+  int32_t* descriptor_counts;  /* [batch, R] */
+  int32_t* tile_descriptors;   /* [batch, R, T/64] */
+  int32_t* threshold_state;    /* [batch, R, 4]; slot 0 receives the threshold key */
+  /* ---- attention workspace ---- */
+  int32_t* positions;          /* [batch, R, T] resolved cache rows, -1 = masked */
+  float* partials;             /* [batch, R, splits, G, 130] */
+  uint64_t* partial_topk;      /* [batch, R, splits, 8] */
+  void* output;                /* bf16 [batch, R*G, 128] */
+  float* lse;                  /* [batch, R*G] */
+  float* topk_scores;          /* [batch, R, 8] */
+  int32_t* topk_positions;     /* [batch, R, 8] */
+  int32_t* assigned;           /* [batch, graphs] */
+  int32_t* overflow;           /* [batch, graphs] */
+  uint32_t* status;            /* one device word, may be null */
+} ckv_layer_args;
+
+/* Library version: major*10000 + minor*100 + patch. */
+int ckv_version(void);
+const char* ckv_status_string(int status);
+
+/* A1.  scores[b,r,c] = fp16(max_g q . centroid); -inf if c >= count or size <= 0. */
+int ckv_score_centroids(const ckv_layer_args* args, void* cuda_stream);
+
+/* A2.  Exact weighted threshold selection; fills communities, cumulative_ends,
+ * descriptor_counts, tile_descriptors and the resolved `positions`. */
+int ckv_select_descriptors(const ckv_layer_args* args, void* cuda_stream);
+
+/* A3+A4+A5.  Resolves positions from the packed descriptors already in the
+ * workspace, gathers K/V rows, runs split attention, merges, and (unless
+ * CKV_FLAG_SKIP_UPDATE) performs the online assignment and state update. */
+int ckv_segmented_attention(const ckv_layer_args* args, void* cuda_stream);
+
+/* A1..A5 back to back: the whole per-layer decode transition. */
+int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream);
+
+/* Bytes of dynamic shared memory the attention kernel asks for (for diagnostics). */
+int ckv_attention_smem_bytes(int group_size);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CKV_B200_H_ */

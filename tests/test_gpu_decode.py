@@ -1,0 +1,253 @@
+"""Parity of the CUDA decode path (through the C ABI) against the CPU oracle."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from community_kv_b200 import ops
+from community_kv_b200.batched import BatchedDecodeRuntime
+from community_kv_b200.config import CommunityKVConfig, GraphAggregation
+from community_kv_b200.runtime import DecodeRuntime, convert_prefill_tensors
+from community_kv_b200.state import DecodeLayerWorkspace
+from community_kv_b200.synthetic import make_layer, make_query
+from tests.helpers import OracleLayer, assert_state_equal, assert_step_equal
+
+pytestmark = pytest.mark.gpu
+SCALE = 128 ** -0.5
+
+
+def _cover(converted):
+    capacity = converted.mutable.community_capacity
+    return [min(capacity, c + converted.decode_capacity) for c in converted.initial_community_counts]
+
+
+def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None):
+    device = torch.device("cuda", 0)
+    runtime = DecodeRuntime(config, splits=splits)
+    state = runtime.prepare_layer(0, **layer.to(device).prepare_kwargs())
+    twin = OracleLayer(
+        state.converted.csr,
+        state.converted.mutable,
+        state.converted.current_position,
+        token_budget=state.workspace.selection.token_budget,
+        num_sink=config.num_sink,
+        cover=_cover(state.converted),
+    )
+    key = layer.key.to(device)[None]
+    value = layer.value.to(device)[None]
+    for step in range(steps):
+        query = make_query(seed=seed + step, query_heads=layer.query_heads, integer_valued=integer)
+        out = runtime.decode(
+            layer_idx=0,
+            query=query.to(device)[None, :, None, :],
+            key=key,
+            value=value,
+            softmax_scale=SCALE,
+        )
+        assert out.shape == (1, 1, layer.query_heads, 128)
+        want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=config.lam)
+        where = f"step {step}"
+        assert_step_equal(
+            selection=state.workspace.selection,
+            attention=state.workspace.attention,
+            update=state.workspace.update,
+            result=want,
+            where=where,
+        )
+        assert_state_equal(state.converted.mutable, twin.state, where)
+        assert torch.equal(state.converted.current_position.cpu(), twin.current), where
+    runtime.assert_no_overflow()
+    return state, twin
+
+
+@pytest.mark.parametrize(
+    "aggregation", [GraphAggregation.QUERY_GROUP, GraphAggregation.PER_QUERY_HEAD, GraphAggregation.LAYER_WISE]
+)
+def test_single_layer_config0_parity(aggregation):
+    """BASELINE config 1: ctx 8192, 32/8 heads, 64 planted clusters, budget 1024."""
+
+    layer = make_layer(seed=0, seq_len=8192, communities=64, max_decode_tokens=8, aggregation=aggregation)
+    config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation=aggregation)
+    _run_sequence(layer, config, steps=4, seed=100)
+
+
+def test_many_small_communities_and_delta_chains():
+    """Mean community size ~16 (the tuned regime): many descriptors, decode deltas get re-selected."""
+
+    layer = make_layer(seed=1, kv_heads=2, seq_len=4096, communities=256, max_decode_tokens=24)
+    config = CommunityKVConfig(token_budget=512, num_sink=4, lam=0.5, aggregation="query_group")
+    state, twin = _run_sequence(layer, config, steps=24, seed=200, splits=4)
+    assert int(state.converted.mutable.deltas.community_sizes.sum()) == 24 * 2
+
+
+def test_integer_fixture_is_exact_end_to_end():
+    """Small-integer operands: every fp32 sum is exact, so even the bf16 output must match closely."""
+
+    layer = make_layer(seed=2, kv_heads=2, seq_len=2048, communities=32, max_decode_tokens=6, integer_valued=True)
+    config = CommunityKVConfig(token_budget=256, num_sink=2, lam=0.25, aggregation="query_group")
+    _run_sequence(layer, config, steps=6, seed=300, integer=True, splits=2)
+
+
+@pytest.mark.parametrize("group_size,kv_heads", [(1, 4), (2, 4), (5, 2), (8, 2), (12, 1), (16, 1)])
+def test_group_sizes(group_size, kv_heads):
+    layer = make_layer(seed=3 + group_size, kv_heads=kv_heads, group_size=group_size, seq_len=2048,
+                       communities=48, max_decode_tokens=4)
+    config = CommunityKVConfig(token_budget=256, num_sink=3, lam=0.5, aggregation="query_group")
+    _run_sequence(layer, config, steps=2, seed=400 + group_size, splits=1)
+
+
+def test_zipf_communities_full_context_unit():
+    """BASELINE config 4 shape for one sequence-layer: ctx 131072, 4096 Zipf communities, budget 2048."""
+
+    layer = make_layer(seed=5, seq_len=131072, communities=4096, max_decode_tokens=4, zipf_exponent=1.1)
+    config = CommunityKVConfig(token_budget=2048, num_sink=10, lam=0.5, aggregation="query_group")
+    _run_sequence(layer, config, steps=2, seed=500)
+
+
+def test_batched_sequences_match_per_sequence_oracle():
+    device = torch.device("cuda", 0)
+    config = CommunityKVConfig(token_budget=512, num_sink=10, lam=0.5, aggregation="query_group")
+    layers = [
+        make_layer(seed=10 + b, kv_heads=4, seq_len=4096, communities=96 + 16 * b, max_decode_tokens=6,
+                   zipf_exponent=1.1 if b % 2 else None)
+        for b in range(3)
+    ]
+    runtime = BatchedDecodeRuntime(config, splits=2)
+    converted = [convert_prefill_tensors(**layer.to(device).prepare_kwargs()) for layer in layers]
+    state = runtime.prepare_layer(0, converted)
+    twins = []
+    for b in range(3):
+        csr, mutable, current = state.sequence_view(b)
+        twins.append(
+            OracleLayer(csr, mutable, current, token_budget=state.token_budget, num_sink=config.num_sink,
+                        cover=state.workspace.selection.score_cover[b].cpu().tolist())
+        )
+    key = torch.stack([layer.key for layer in layers]).to(device)
+    value = torch.stack([layer.value for layer in layers]).to(device)
+    for step in range(5):
+        queries = torch.stack([make_query(seed=600 + 10 * step + b, query_heads=16) for b in range(3)])
+        out = runtime.decode(layer_idx=0, query=queries.to(device), key=key, value=value, softmax_scale=SCALE)
+        assert out.shape == (3, 16, 128)
+        for b in range(3):
+            want = twins[b].step(query=queries[b], key=layers[b].key, value=layers[b].value,
+                                 softmax_scale=SCALE, lam=config.lam)
+            ws = state.workspace
+            view = lambda obj, names: type("V", (), {n: getattr(obj, n)[b] for n in names})
+            assert_step_equal(
+                selection=view(ws.selection, ["scores", "descriptor_counts", "communities", "cumulative_ends",
+                                               "tile_descriptors", "positions"]),
+                attention=view(ws.attention, ["output", "lse", "topk_positions", "topk_scores"]),
+                update=view(ws.update, ["assigned_communities", "overflow"]),
+                result=want,
+                where=f"step {step} seq {b}",
+            )
+            _, mutable, current = state.sequence_view(b)
+            assert_state_equal(mutable, twins[b].state, f"step {step} seq {b}")
+            assert torch.equal(current.cpu(), twins[b].current)
+    runtime.assert_no_overflow()
+
+
+def test_standalone_entry_points_and_skip_update():
+    """score -> select -> attention as three separate C-ABI calls, without the online update."""
+
+    device = torch.device("cuda", 0)
+    layer = make_layer(seed=20, kv_heads=2, seq_len=2048, communities=40, max_decode_tokens=4)
+    config = CommunityKVConfig(token_budget=256, num_sink=5, lam=0.5, aggregation="query_group")
+    converted = convert_prefill_tensors(**layer.to(device).prepare_kwargs())
+    ws = DecodeLayerWorkspace.allocate(
+        retrieval_head_count=2, graph_count=2, group_size=4, community_capacity=converted.mutable.community_capacity,
+        token_budget=256, num_sink=5, dtype=torch.bfloat16, device=device, splits=2,
+    )
+    sinks = torch.arange(5, dtype=torch.int32, device=device)
+    twin = OracleLayer(converted.csr, converted.mutable, converted.current_position, token_budget=256,
+                       num_sink=5, cover=None)
+    query = make_query(seed=21, query_heads=8)
+    mutable = converted.mutable
+    ops.score_centroids(query=query.to(device), centroids=mutable.centroids,
+                        community_sizes=mutable.community_sizes, community_counts=mutable.community_counts,
+                        workspace=ws.selection)
+    segments = ops.select_weighted_descriptors_auto(
+        community_sizes=mutable.community_sizes, community_counts=mutable.community_counts,
+        workspace=ws.selection, csr=converted.csr, state=mutable, sink_positions=sinks,
+        current_position=converted.current_position)
+    ws.selection.positions.fill_(-7)  # the attention entry point must resolve positions itself
+    ops.segmented_attention(
+        query=query.to(device), key=layer.key.to(device), value=layer.value.to(device), csr=converted.csr,
+        deltas=mutable.deltas, segments=segments, sink_positions=sinks,
+        current_position=converted.current_position, softmax_scale=SCALE, workspace=ws.attention,
+        update_state=mutable, update_workspace=None, update_lam=0.5, positions=ws.selection.positions)
+    want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=0.5, update=False)
+    assert_step_equal(selection=ws.selection, attention=ws.attention, update=ws.update, result=want,
+                      check_update=False)
+    assert_state_equal(mutable, twin.state, "skip-update leaves the state untouched")
+    assert int(converted.current_position[0]) == 2048
+
+
+def test_topk_communities_mode_and_underfill():
+    """Extension (BASELINE config 1 wording): at most k communities; unfilled slots are masked."""
+
+    device = torch.device("cuda", 0)
+    config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation="query_group")
+    layer = make_layer(seed=30, kv_heads=4, seq_len=8192, communities=64, max_decode_tokens=4)
+    converted = [convert_prefill_tensors(**layer.to(device).prepare_kwargs())]
+    runtime = BatchedDecodeRuntime(config)
+    state = runtime.prepare_layer(0, converted, max_communities=5)
+    csr, mutable, current = state.sequence_view(0)
+    twin = OracleLayer(csr, mutable, current, token_budget=1024, num_sink=10,
+                       cover=state.workspace.selection.score_cover[0].cpu().tolist(), max_communities=5)
+    key = layer.key.to(device)[None]
+    value = layer.value.to(device)[None]
+    for step in range(3):
+        query = make_query(seed=700 + step, query_heads=16)
+        runtime.decode(layer_idx=0, query=query.to(device)[None], key=key, value=value, softmax_scale=SCALE)
+        want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=0.5)
+        ws = state.workspace
+        view = lambda obj, names: type("V", (), {n: getattr(obj, n)[0] for n in names})
+        assert int(ws.selection.descriptor_counts.max()) <= 5
+        assert int((ws.selection.positions == -1).sum()) > 0  # 5 of 64 clusters cannot fill 1013 slots
+        assert_step_equal(
+            selection=view(ws.selection, ["scores", "descriptor_counts", "communities", "cumulative_ends",
+                                           "tile_descriptors", "positions"]),
+            attention=view(ws.attention, ["output", "lse", "topk_positions", "topk_scores"]),
+            update=view(ws.update, ["assigned_communities", "overflow"]),
+            result=want, where=f"step {step}")
+        assert_state_equal(state.sequence_view(0)[1], twin.state, f"step {step}")
+
+
+def test_overflow_flags_stop_the_cursor():
+    """Exhaust the decode-delta pools on purpose: flags are raised, the cursor stops, nothing faults."""
+
+    layer = make_layer(seed=40, kv_heads=1, seq_len=1024, communities=16, max_decode_tokens=2)
+    config = CommunityKVConfig(token_budget=128, num_sink=2, lam=0.5, aggregation="query_group")
+    device = torch.device("cuda", 0)
+    runtime = DecodeRuntime(config, splits=1)
+    state = runtime.prepare_layer(0, **layer.to(device).prepare_kwargs())
+    twin = OracleLayer(state.converted.csr, state.converted.mutable, state.converted.current_position,
+                       token_budget=128, num_sink=2, cover=_cover(state.converted))
+    key, value = layer.key.to(device)[None], layer.value.to(device)[None]
+    for step in range(4):
+        query = make_query(seed=800 + step, query_heads=4)
+        runtime.decode(layer_idx=0, query=query.to(device)[None, :, None, :], key=key, value=value,
+                       softmax_scale=SCALE)
+        want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=0.5)
+        assert torch.equal(state.workspace.update.overflow.cpu(), want.overflow), step
+        assert_state_equal(state.converted.mutable, twin.state, f"step {step}")
+        assert torch.equal(state.converted.current_position.cpu(), twin.current)
+    with pytest.raises(RuntimeError, match="overflow"):
+        runtime.assert_no_overflow()
+
+
+def test_shape_errors_are_reported_before_launch():
+    device = torch.device("cuda", 0)
+    layer = make_layer(seed=50, kv_heads=1, seq_len=1024, communities=16, max_decode_tokens=2)
+    config = CommunityKVConfig(token_budget=128, num_sink=2)
+    runtime = DecodeRuntime(config)
+    runtime.prepare_layer(0, **layer.to(device).prepare_kwargs())
+    with pytest.raises(ValueError, match="query shape"):
+        runtime.decode(layer_idx=0, query=torch.zeros((1, 4, 2, 128), device=device, dtype=torch.bfloat16),
+                       key=layer.key.to(device)[None], value=layer.value.to(device)[None], softmax_scale=SCALE)
+    with pytest.raises(RuntimeError, match="not prepared"):
+        runtime.decode(layer_idx=3, query=torch.zeros((1, 4, 1, 128), device=device, dtype=torch.bfloat16),
+                       key=layer.key.to(device)[None], value=layer.value.to(device)[None], softmax_scale=SCALE)
