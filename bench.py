@@ -1,0 +1,513 @@
+"""Benchmark of the sparse-decode attention path at 128K context.
+
+Workload (the reference's long-context batched decode configuration): a
+Qwen3-8B-shaped decoder - 36 layers, 32 query / 8 KV heads, head_dim 128 - at
+131072 tokens of context per sequence, 1024-4096 communities per (layer, KV
+head) with Zipf(1.1) sizes, 2048-token retrieval budget, bf16 K/V.  One "step"
+is one decode step of the attention path: for every layer, every sequence and
+every KV head, centroid scoring -> budgeted community selection -> gather +
+segmented attention -> merge -> online assignment.  Layers run one after the
+other (a real decoder's layers depend on each other); all sequences and heads of
+a layer share one library call.  KV heads are sharded across the GPUs, each GPU
+keeps 8/N heads of ``--batch-per-gpu * N`` sequences (weak scaling), and every
+layer's head outputs are all-gathered.
+
+Prints one JSON line (rank 0).  ``--impl reference`` times the CPU restatement of
+the reference's algorithm on the host cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from concurrent.futures import ProcessPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+LAYERS = 36
+QUERY_HEADS = 32
+KV_HEADS = 8
+HEAD_DIM = 128
+CONTEXT = 131072
+BUDGET = 2048
+NUM_SINK = 10
+COMMUNITIES = (1024, 4096)
+ZIPF = 1.1
+SCALE = HEAD_DIM**-0.5
+METRIC = "sparse decode tokens/sec at 128K ctx (attention path, all 36 layers)"
+
+
+def parse_args() -> argparse.Namespace:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    parser.add_argument("--batch-per-gpu", type=int, default=0, help="0: largest of 8/4/2/1 that fits")
+    parser.add_argument("--layers", type=int, default=LAYERS)
+    parser.add_argument("--context", type=int, default=CONTEXT)
+    parser.add_argument("--splits", type=int, default=8)
+    parser.add_argument("--layers-per-launch", type=int, default=1)
+    parser.add_argument("--cpu-seconds", type=float, default=15.0)
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--seed", type=int, default=0)
+    return parser.parse_args()
+
+
+# --------------------------------------------------------------------------- #
+# CPU arm: the oracle port on the host cores
+# --------------------------------------------------------------------------- #
+def _cpu_worker(task: tuple[int, int, float]) -> tuple[int, float]:
+    """Time oracle layer transitions of one (sequence, layer, KV head) unit."""
+
+    seed, context, seconds = task
+    import torch
+
+    torch.set_num_threads(1)
+    from community_kv_b200.runtime import convert_prefill_tensors
+    from community_kv_b200.synthetic import make_layer, make_query
+    from oracle import decode_oracle
+
+    generator = torch.Generator().manual_seed(seed)
+    count = int(torch.randint(COMMUNITIES[0], COMMUNITIES[1] + 1, (1,), generator=generator))
+    layer = make_layer(
+        seed=seed, kv_heads=1, group_size=4, seq_len=context, communities=count,
+        num_sink=NUM_SINK, max_decode_tokens=64, zipf_exponent=ZIPF,
+    )
+    converted = convert_prefill_tensors(**layer.prepare_kwargs())
+    sinks = torch.arange(NUM_SINK, dtype=torch.int32)
+    done = 0
+    begin = time.perf_counter()
+    while True:
+        decode_oracle.decode_layer(
+            query=make_query(seed=seed * 131 + done, query_heads=4),
+            key=layer.key,
+            value=layer.value,
+            csr=converted.csr,
+            state=converted.mutable,
+            sink_positions=sinks,
+            current_position=converted.current_position,
+            softmax_scale=SCALE,
+            lam=0.5,
+            token_budget=BUDGET,
+            num_sink=NUM_SINK,
+            exact=False,
+        )
+        done += 1
+        elapsed = time.perf_counter() - begin
+        if elapsed >= seconds or done >= 60:
+            return done, elapsed
+
+
+def cpu_baseline(seconds: float, context: int, layers: int, seed: int = 0) -> dict:
+    """Whole-host throughput of the CPU restatement on a bounded sample of the workload."""
+
+    import multiprocessing
+
+    cores = os.cpu_count() or 1
+    context_for_sample = context
+    tasks = [(seed * 1000 + worker, context_for_sample, seconds) for worker in range(cores)]
+    with ProcessPoolExecutor(max_workers=cores, mp_context=multiprocessing.get_context("spawn")) as pool:
+        results = list(pool.map(_cpu_worker, tasks))
+    unit_rate = sum(done / elapsed for done, elapsed in results)
+    units_per_token = layers * KV_HEADS
+    return {
+        "value": unit_rate / units_per_token,
+        "unit": "tokens/s",
+        "cores": cores,
+        "kind": "port",
+        "sample": (
+            f"{cores} processes x one (sequence, layer, KV head) unit each at ctx {context_for_sample}, "
+            f"{sum(d for d, _ in results)} unit-steps in ~{seconds:.0f}s; a token = {units_per_token} units"
+        ),
+    }
+
+
+def run_reference(args: argparse.Namespace) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_step = []
+    total_steps = args.warmup + args.steps
+    seconds = max(2.0, min(args.cpu_seconds, 150.0 / max(total_steps, 1)))
+    last = None
+    for step in range(total_steps):
+        last = cpu_baseline(seconds, args.context, args.layers, seed=step)
+        if step >= args.warmup:
+            per_step.append(last["value"])
+    value = statistics.mean(per_step)
+    line = {
+        "impl": "reference",
+        "metric": METRIC,
+        "value": value,
+        "unit": "tokens/s",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": 1000.0 / value,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": workload_config(args, batch=1, world=1),
+        "cpu_baseline": {**last, "value": value},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args: argparse.Namespace, *, batch: int, world: int) -> dict:
+    return {
+        "workload": (
+            "batched long-context decode (Qwen3-8B attention shapes): "
+            f"{args.layers} layers x {batch} sequences x {KV_HEADS} KV heads, ctx {args.context}, "
+            f"{COMMUNITIES[0]}-{COMMUNITIES[1]} Zipf({ZIPF}) communities per head, budget {BUDGET}"
+        ),
+        "global_batch": batch,
+        "context": args.context,
+        "token_budget": BUDGET,
+        "parallelism": f"kv-head shard x{world}",
+        "layers_per_launch": args.layers_per_launch,
+        "splits": args.splits,
+        "l2": "inputs larger than L2 (each step gathers rows scattered over the whole KV cache)",
+    }
+
+
+# --------------------------------------------------------------------------- #
+# clocks
+# --------------------------------------------------------------------------- #
+class ClockSampler:
+    FIELDS = (
+        "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+        "clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.samples: list[list[str]] = []
+        self.process: subprocess.Popen | None = None
+        self.thread: threading.Thread | None = None
+
+    def start(self) -> None:
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self) -> None:
+        assert self.process is not None and self.process.stdout is not None
+        for line in self.process.stdout:
+            self.samples.append([part.strip() for part in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.process is not None:
+            self.process.terminate()
+            try:
+                self.process.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+        clocks, maxima, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for sample in self.samples:
+            if len(sample) < 7:
+                continue
+            try:
+                clocks.append(float(sample[0]))
+                maxima.append(float(sample[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, sample[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": max(maxima) if maxima else None,
+            "samples": len(clocks),
+            "reasons": sorted(reasons),
+        }
+
+
+# --------------------------------------------------------------------------- #
+# GPU arm
+# --------------------------------------------------------------------------- #
+def pick_batch(requested: int, args: argparse.Namespace, heads_local: int, torch) -> int:
+    if requested > 0:
+        return requested
+    free, _ = torch.cuda.mem_get_info()
+    rows = args.context + 512
+    per_sequence = args.layers * heads_local * rows * HEAD_DIM * 2 * 2
+    per_sequence += args.layers * heads_local * (args.context * 12 + 5000 * 140)
+    for candidate in (8, 4, 2, 1):
+        if candidate * per_sequence < 0.86 * free:
+            return candidate
+    return 1
+
+
+def run_b200(args: argparse.Namespace) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from community_kv_b200 import native
+    from community_kv_b200.workload import build_decode_workload
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if KV_HEADS % world:
+        raise SystemExit("the number of GPUs must divide the 8 KV heads")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    heads_local = KV_HEADS // world
+    query_local = heads_local * (QUERY_HEADS // KV_HEADS)
+    per_gpu = pick_batch(args.batch_per_gpu, args, KV_HEADS, torch)
+    batch = per_gpu * world
+    total_steps = args.warmup + args.steps
+    e2e_steps = max(3, min(args.steps, 10))
+    extra_steps = 4 + e2e_steps + 3
+    max_decode = total_steps + extra_steps + 8
+
+    build_begin = time.perf_counter()
+    work = build_decode_workload(
+        layers=args.layers, batch=batch, kv_heads=heads_local, group_size=QUERY_HEADS // KV_HEADS,
+        seq_len=args.context, communities=COMMUNITIES, token_budget=BUDGET, num_sink=NUM_SINK,
+        max_decode_tokens=max_decode, device=device, seed=args.seed, zipf_exponent=ZIPF,
+        head_offset=rank * heads_local, layers_per_launch=args.layers_per_launch, splits=args.splits,
+    )
+    torch.cuda.synchronize()
+    build_seconds = time.perf_counter() - build_begin
+    launches, slots = work.launches, work.slots
+
+    # One contiguous output arena so that a step's result is a single tensor.
+    out_local = torch.zeros((launches, slots, query_local, HEAD_DIM), dtype=torch.bfloat16, device=device)
+    out_full = (
+        torch.zeros((launches, world, slots, query_local, HEAD_DIM), dtype=torch.bfloat16, device=device)
+        if world > 1 else None
+    )
+    q_cur = torch.zeros((launches, slots, query_local, HEAD_DIM), dtype=torch.bfloat16, device=device)
+    generator = torch.Generator(device=device).manual_seed(args.seed + 17 + rank)
+    stream = torch.cuda.Stream(device)
+    packed = []
+    with torch.cuda.stream(stream):
+        for launch in range(launches):
+            state = work.state(launch)
+            state.workspace.attention.output = out_local[launch]
+            packed.append(
+                work.runtime.pack(launch, query=q_cur[launch], key=work.key[launch],
+                                  value=work.value[launch], softmax_scale=SCALE)
+            )
+
+    def enqueue_step() -> None:
+        handle = stream.cuda_stream
+        for launch in range(launches):
+            native.call("ckv_decode_layer", packed[launch], handle)
+            if world > 1:
+                dist.all_gather_into_tensor(out_full[launch], out_local[launch])
+
+    def new_queries(count: int) -> "torch.Tensor":
+        return torch.randn((count, launches, slots, query_local, HEAD_DIM), generator=generator,
+                           device=device, dtype=torch.float32).to(torch.bfloat16)
+
+    def barrier() -> None:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up (direct launches), then capture one step in a CUDA graph ----
+    q_all = new_queries(total_steps)
+    with torch.cuda.stream(stream):
+        for step in range(args.warmup):
+            q_cur.copy_(q_all[step])
+            enqueue_step()
+    barrier()
+    graph = torch.cuda.CUDAGraph()
+    use_graph = True
+    try:
+        with torch.cuda.graph(graph, stream=stream):
+            enqueue_step()
+        # the capture itself does not execute; state is untouched
+    except Exception as error:  # pragma: no cover - depends on NCCL capture support
+        use_graph = False
+        if rank == 0:
+            print(f"[bench] graph capture unavailable ({type(error).__name__}); direct launches", file=sys.stderr)
+    barrier()
+
+    def run_step() -> None:
+        if use_graph:
+            graph.replay()
+        else:
+            enqueue_step()
+
+    # ---- timed region: K steps, CUDA events on the launching stream ----
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with torch.cuda.stream(stream):
+        begin.record()
+        for step in range(args.warmup, total_steps):
+            q_cur.copy_(q_all[step])
+            run_step()
+        end.record()
+    barrier()
+    elapsed_ms = torch.tensor([begin.elapsed_time(end)], device=device)
+    if world > 1:
+        dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(elapsed_ms) / args.steps
+    work.runtime.assert_no_overflow()
+
+    # ---- dominant kernel alone: gather + segmented attention, per-launch events ----
+    attn_args = []
+    for launch in range(launches):
+        clone = native.LayerArgs.from_buffer_copy(packed[launch])
+        clone.flags = native.FLAG_ATTENTION_ONLY | native.FLAG_SKIP_UPDATE
+        attn_args.append(clone)
+    kernel_ms = []
+    with torch.cuda.stream(stream):
+        for repeat in range(3):
+            events = []
+            for launch in range(launches):
+                first, second = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                first.record()
+                native.call("ckv_segmented_attention", attn_args[launch], stream.cuda_stream)
+                second.record()
+                events.append((first, second))
+            stream.synchronize()
+            if repeat > 0:
+                kernel_ms.extend(a.elapsed_time(b) for a, b in events)
+    attention_ms = statistics.mean(kernel_ms)
+    clocks = sampler.stop() if rank == 0 else {}
+
+    # ---- end to end: host queries and new K/V rows in, head outputs out, every step ----
+    pinned_q = torch.randn((e2e_steps, launches, slots, query_local, HEAD_DIM)).to(torch.bfloat16).pin_memory()
+    pinned_kv = (torch.randn((e2e_steps, 2, launches, slots, heads_local, HEAD_DIM)) * SCALE).to(torch.bfloat16).pin_memory()
+    pinned_out = torch.empty((launches, world, slots, query_local, HEAD_DIM), dtype=torch.bfloat16).pin_memory()
+    new_kv = torch.empty((2, launches, slots, heads_local, HEAD_DIM), dtype=torch.bfloat16, device=device)
+    cursor = int(work.state(0).current_position.max())
+    result = out_full if world > 1 else out_local
+    barrier()
+    e2e_begin, e2e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e2e_begin.record()
+        for step in range(e2e_steps):
+            q_cur.copy_(pinned_q[step], non_blocking=True)
+            new_kv.copy_(pinned_kv[step], non_blocking=True)
+            work.key[:, :, :, cursor + step].copy_(new_kv[0])
+            work.value[:, :, :, cursor + step].copy_(new_kv[1])
+            run_step()
+            pinned_out.view(result.shape).copy_(result, non_blocking=True)
+            stream.synchronize()  # the caller reads the step's output before the next token
+        e2e_end.record()
+    barrier()
+    e2e_ms = torch.tensor([e2e_begin.elapsed_time(e2e_end)], device=device)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_ms_per_step = float(e2e_ms) / e2e_steps
+    work.runtime.assert_no_overflow()
+
+    # ---- roofline ----
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    if peaks_path.exists():
+        peak = float(json.loads(peaks_path.read_text())["hbm_gbs"])
+        peak_source = "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_source = 6650.0, "fallback"
+    units_per_launch = slots * heads_local
+    kv_bytes_per_unit = 2 * BUDGET * HEAD_DIM * 2
+    attention_gbs = units_per_launch * kv_bytes_per_unit / (attention_ms * 1e-3) / 1e9
+    centroid_bytes = sum(work.community_counts) * HEAD_DIM
+    step_bytes = centroid_bytes + launches * units_per_launch * kv_bytes_per_unit
+    step_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    line = {
+        "metric": METRIC,
+        "value": batch / (ms_per_step * 1e-3),
+        "unit": "tokens/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_per_step,
+        "us_per_step": ms_per_step * 1e3,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": workload_config(args, batch=batch, world=world),
+        "roofline": {
+            "kernel": "attention_kernel (KV gather + segmented flash-decode)",
+            "bound": "hbm",
+            "achieved": attention_gbs,
+            "peak": peak,
+            "unit": "GB/s",
+            "frac": attention_gbs / peak,
+            "peak_source": peak_source,
+            "traffic": None,
+            "algorithmic_bytes_per_launch": units_per_launch * kv_bytes_per_unit,
+            "launch_ms": attention_ms,
+        },
+        "step_roofline": {
+            "bytes_per_step_per_gpu": step_bytes,
+            "achieved": step_gbs,
+            "frac": step_gbs / peak,
+            "note": "centroids + selected KV of all layers / whole-step time",
+        },
+        "e2e": {
+            "value": batch / (e2e_ms_per_step * 1e-3),
+            "unit": "tokens/s",
+            "ms_per_step": e2e_ms_per_step,
+            "steps": e2e_steps,
+            "h2d_bytes_per_step": int(pinned_q[0].numel() * 2 + pinned_kv[0].numel() * 2),
+            "d2h_bytes_per_step": int(pinned_out.numel() * 2),
+        },
+        "gpu_launches": args.steps * launches * 4,
+        "cuda_graph": use_graph,
+        "clocks": clocks,
+        "build_seconds": build_seconds,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        del work
+        torch.cuda.empty_cache()
+        line["cpu_baseline"] = cpu_baseline(args.cpu_seconds, args.context, args.layers)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -133,6 +133,9 @@ int ckv_segmented_attention(const ckv_layer_args* args, void* cuda_stream) {
   status = ckv::select_device(args);
   if (status != CKV_OK) return status;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (args->flags & CKV_FLAG_ATTENTION_ONLY) {
+    return ckv::launched(ckv::launch_attention(*args, stream));
+  }
   status = ckv::launched(ckv::launch_resolve(*args, stream));
   if (status != CKV_OK) return status;
   status = ckv::launched(ckv::launch_attention(*args, stream));

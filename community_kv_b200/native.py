@@ -97,6 +97,7 @@ class LayerArgs(ctypes.Structure):
 
 
 FLAG_SKIP_UPDATE = 1
+FLAG_ATTENTION_ONLY = 2
 DEV_WAIT_TIMEOUT = 1
 PARTIAL_STRIDE = 130
 
@@ -166,6 +167,7 @@ def fill(args: LayerArgs, **values: Any) -> LayerArgs:
 __all__ = [
     "DEV_WAIT_TIMEOUT",
     "ENTRY_POINTS",
+    "FLAG_ATTENTION_ONLY",
     "FLAG_SKIP_UPDATE",
     "LayerArgs",
     "NativeError",

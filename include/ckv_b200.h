@@ -57,7 +57,10 @@ typedef enum ckv_status {
 #define CKV_DEV_WAIT_TIMEOUT 1u /* a bounded mbarrier wait gave up */
 
 /* flags */
-#define CKV_FLAG_SKIP_UPDATE 1 /* attention only: leave the graph state untouched */
+#define CKV_FLAG_SKIP_UPDATE 1    /* attention only: leave the graph state untouched */
+#define CKV_FLAG_ATTENTION_ONLY 2 /* ckv_segmented_attention: launch only the gather+attention
+                                     kernel on the positions already in the workspace (no
+                                     position resolution, no merge); for kernel timing */
 
 typedef struct ckv_layer_args {
   /* ---- geometry ---- */
