@@ -55,7 +55,7 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--batch-per-gpu", type=int, default=0, help="0: largest of 8/4/2/1 that fits")
     parser.add_argument("--layers", type=int, default=LAYERS)
     parser.add_argument("--context", type=int, default=CONTEXT)
-    parser.add_argument("--splits", type=int, default=8)
+    parser.add_argument("--splits", type=int, default=0, help="attention CTAs per head; 0: fill one wave")
     parser.add_argument("--layers-per-launch", type=int, default=1)
     parser.add_argument("--cpu-seconds", type=float, default=15.0)
     parser.add_argument("--no-cpu-baseline", action="store_true")
@@ -293,7 +293,7 @@ def run_b200(args: argparse.Namespace) -> None:
         layers=args.layers, batch=batch, kv_heads=heads_local, group_size=QUERY_HEADS // KV_HEADS,
         seq_len=args.context, communities=COMMUNITIES, token_budget=BUDGET, num_sink=NUM_SINK,
         max_decode_tokens=max_decode, device=device, seed=args.seed, zipf_exponent=ZIPF,
-        head_offset=rank * heads_local, layers_per_launch=args.layers_per_launch, splits=args.splits,
+        head_offset=rank * heads_local, layers_per_launch=args.layers_per_launch, splits=args.splits or None,
     )
     torch.cuda.synchronize()
     build_seconds = time.perf_counter() - build_begin

@@ -54,7 +54,7 @@ int check(const ckv_layer_args* a, int need) {
         !a->output || !a->lse || !a->topk_scores || !a->topk_positions || !a->communities ||
         !a->cumulative_ends || !a->descriptor_counts)
       return CKV_ERR_NULL;
-    if (a->splits <= 0 || a->splits > 32 || a->token_budget % (CKV_TILE * a->splits))
+    if (a->splits <= 0 || a->splits > 32 || a->splits > a->token_budget / 16)
       return CKV_ERR_SHAPE;
     if (a->sequence_capacity <= 0 || a->token_capacity <= 0) return CKV_ERR_SHAPE;
     if ((a->key_row_stride % 8) || (a->value_row_stride % 8) || (a->key_head_stride % 8) ||

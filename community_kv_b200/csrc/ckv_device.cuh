@@ -114,6 +114,18 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
       ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
       : "memory");
 }
+// 16-byte asynchronous global -> shared copy (L2 only); src_bytes 0 zero-fills.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -181,7 +193,9 @@ __device__ __forceinline__ int delta_member_position(const ckv_layer_args& a, in
 }
 
 // Cache row of logical token `logical` (0..T-1) of one unit, -1 when masked.
-__device__ __forceinline__ int resolve_token(const ckv_layer_args& a, const Unit& u, int flat_unit,
+// `ends` / `comms` are the unit's descriptor arrays (global or shared memory).
+__device__ __forceinline__ int resolve_token(const ckv_layer_args& a, const Unit& u,
+                                             const int32_t* ends, const int32_t* comms,
                                              int logical, int descriptor_count) {
   const int64_t graph_slot = static_cast<int64_t>(u.batch) * a.graphs + u.graph;
   if (logical < a.num_sink) {
@@ -191,7 +205,6 @@ __device__ __forceinline__ int resolve_token(const ckv_layer_args& a, const Unit
     return a.current_position[graph_slot];
   }
   const int offset = logical - a.num_sink;
-  const int32_t* ends = a.cumulative_ends + static_cast<int64_t>(flat_unit) * a.descriptor_capacity;
   int low = 0;
   int high = descriptor_count;
   while (low < high) {
@@ -207,8 +220,7 @@ __device__ __forceinline__ int resolve_token(const ckv_layer_args& a, const Unit
   }
   const int previous_end = low > 0 ? ends[low - 1] : 0;
   const int member = offset - previous_end;
-  const int community =
-      a.communities[static_cast<int64_t>(flat_unit) * a.descriptor_capacity + low];
+  const int community = comms[low];
   const int delta_count = a.delta_sizes[graph_slot * a.community_capacity + community];
   if (member < delta_count) {
     return delta_member_position(a, graph_slot, community, member);

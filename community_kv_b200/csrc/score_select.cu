@@ -17,98 +17,189 @@
 namespace ckv {
 
 constexpr int kScoreThreads = 256;
-constexpr int kScoreRowsPerBlock = 128;  // 8 warps x 16 rows
 constexpr int kSelectThreads = 1024;
 constexpr int kStash = 4608;  // communities whose keys/sizes are staged in shared memory
+constexpr int kDescStash = 2048;  // descriptors kept in shared memory for the position search
 
-__global__ void __launch_bounds__(kScoreThreads) score_kernel(const ckv_layer_args a) {
-  __shared__ __align__(16) float q_s[16 * kHeadDim];
-  const int flat = blockIdx.y;
-  const Unit u = make_unit(a, flat);
-  const int group = a.group_size;
-  const __nv_bfloat16* query = reinterpret_cast<const __nv_bfloat16*>(a.query) +
-                               (static_cast<int64_t>(u.batch) * a.retrieval_heads + u.head) *
-                                   group * kHeadDim;
-  for (int i = threadIdx.x; i < group * kHeadDim; i += kScoreThreads) {
-    q_s[i] = __bfloat162float(query[i]);
+// Work is counted in 16-row groups.  The groups of all units of the launch are
+// laid end to end and every CTA takes an equal contiguous share, so units with
+// many communities do not become stragglers.  Inside its share a CTA's eight
+// warps stride over the groups and keep the next group's loads in flight while
+// they compute the current one.
+constexpr int kScoreMaxUnits = 4096;  // units whose group counts fit the shared prefix table
+
+__device__ __forceinline__ void load_group(const uint8_t* table, int row_base, int quad, int slice,
+                                           int capacity, uint4 (&raw)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = min(row_base + quad + 4 * i, capacity - 1);
+    raw[i] = __ldg(reinterpret_cast<const uint4*>(table + static_cast<int64_t>(row) * kHeadDim) + slice);
   }
-  __syncthreads();
+}
 
+__device__ __forceinline__ int score_limit(const ckv_layer_args& a, int flat) {
   const int capacity = a.community_capacity;
-  int limit = capacity;
-  if (a.score_cover != nullptr) {
-    const int cover = min(capacity, a.score_cover[flat]);
-    limit = min(capacity, ((cover + kTile - 1) / kTile) * kTile);
+  if (a.score_cover == nullptr) {
+    return capacity;
   }
+  const int cover = min(capacity, a.score_cover[flat]);
+  return min(capacity, ((cover + kTile - 1) / kTile) * kTile);
+}
+
+__global__ void __launch_bounds__(kScoreThreads, 2) score_kernel(const ckv_layer_args a) {
+  // query group as fp32, laid out [head][k][slice][4] so that the eight slices
+  // of one 16-byte read fall into different banks
+  __shared__ __align__(16) float q_s[16 * kHeadDim];
+  __shared__ int prefix[kScoreMaxUnits + 1];
+  const int units = a.batch * a.retrieval_heads;
+  const int group = a.group_size;
+  const int capacity = a.community_capacity;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int slice = lane & 7;   // which 16 of the 128 dimensions
   const int quad = lane >> 3;   // row inside a group of four consecutive rows
-  const int row_base = blockIdx.x * kScoreRowsPerBlock + warp * 16;
-  if (row_base >= limit) {
+
+  // inclusive prefix of the per-unit group counts
+  for (int unit = threadIdx.x; unit < units; unit += kScoreThreads) {
+    prefix[unit + 1] = (score_limit(a, unit) + 15) / 16;
+  }
+  if (threadIdx.x == 0) {
+    prefix[0] = 0;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int per_lane = (units + 31) / 32;
+    const int lo = min(units, lane * per_lane);
+    const int hi = min(units, lo + per_lane);
+    int running = 0;
+    for (int unit = lo; unit < hi; ++unit) {
+      running += prefix[unit + 1];
+      prefix[unit + 1] = running;
+    }
+    int offset = running;
+#pragma unroll
+    for (int delta = 1; delta < 32; delta <<= 1) {
+      const int other = __shfl_up_sync(0xffffffffu, offset, delta);
+      if (lane >= delta) {
+        offset += other;
+      }
+    }
+    offset -= running;
+    for (int unit = lo; unit < hi; ++unit) {
+      prefix[unit + 1] += offset;
+    }
+  }
+  __syncthreads();
+  const int total = prefix[units];
+  const int my_begin = static_cast<int>(static_cast<int64_t>(blockIdx.x) * total / gridDim.x);
+  const int my_end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * total / gridDim.x);
+  if (my_begin >= my_end) {
     return;
   }
-  const int count = a.community_counts[flat];
-  const uint8_t* table =
-      reinterpret_cast<const uint8_t*>(a.centroids) + static_cast<int64_t>(flat) * capacity * kHeadDim;
-
-  float x[4][16];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int row = min(row_base + quad + 4 * i, capacity - 1);
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(table + static_cast<int64_t>(row) * kHeadDim) + slice);
-    fp8x4_to_float(raw.x, x[i] + 0);
-    fp8x4_to_float(raw.y, x[i] + 4);
-    fp8x4_to_float(raw.z, x[i] + 8);
-    fp8x4_to_float(raw.w, x[i] + 12);
+  int flat = 0;
+  {
+    int low = 0, high = units - 1;  // last unit whose prefix is <= my_begin
+    while (low < high) {
+      const int middle = (low + high + 1) >> 1;
+      if (prefix[middle] <= my_begin) {
+        low = middle;
+      } else {
+        high = middle - 1;
+      }
+    }
+    flat = low;
   }
-
   const bool up_a = (slice & 4) != 0;
   const bool up_b = (slice & 2) != 0;
-  float best = -INFINITY;
-  for (int g = 0; g < group; ++g) {
-    float qv[16];
-    const float4* qp = reinterpret_cast<const float4*>(q_s + g * kHeadDim + slice * 16);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float4 v = qp[k];
-      qv[4 * k + 0] = v.x;
-      qv[4 * k + 1] = v.y;
-      qv[4 * k + 2] = v.z;
-      qv[4 * k + 3] = v.w;
-    }
-    float p[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float acc = __fmul_rn(x[i][0], qv[0]);
-#pragma unroll
-      for (int k = 1; k < 16; ++k) {
-        acc = __fmaf_rn(x[i][k], qv[k], acc);
-      }
-      p[i] = acc;
-    }
-    // Sum the eight slices of each row: (j, j^4), then (j, j^2), then (j, j^1),
-    // folding the four rows onto the lanes on the way (a transposing butterfly).
-    float keep0 = up_a ? p[2] : p[0];
-    float keep1 = up_a ? p[3] : p[1];
-    const float send0 = up_a ? p[0] : p[2];
-    const float send1 = up_a ? p[1] : p[3];
-    keep0 = __fadd_rn(keep0, __shfl_xor_sync(0xffffffffu, send0, 4));
-    keep1 = __fadd_rn(keep1, __shfl_xor_sync(0xffffffffu, send1, 4));
-    float keep = up_b ? keep1 : keep0;
-    const float send = up_b ? keep0 : keep1;
-    keep = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 2));
-    keep = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, keep, 1));
-    best = fmaxf(best, keep);
-  }
+  const int my_row_in_group = quad + 4 * ((up_a ? 2 : 0) + (up_b ? 1 : 0));
 
-  if ((slice & 1) == 0) {
-    const int row = row_base + quad + 4 * ((up_a ? 2 : 0) + (up_b ? 1 : 0));
-    if (row < limit) {
-      const bool live =
-          row < count && a.community_sizes[static_cast<int64_t>(flat) * capacity + row] > 0;
-      __half* out = reinterpret_cast<__half*>(a.scores) + static_cast<int64_t>(flat) * capacity;
-      out[row] = __float2half_rn(live ? best : -INFINITY);
+  for (; flat < units && prefix[flat] < my_end; ++flat) {
+    const int first_group = max(my_begin, prefix[flat]) - prefix[flat];
+    const int last_group = min(my_end, prefix[flat + 1]) - prefix[flat];
+    if (first_group >= last_group) {
+      continue;
+    }
+    const int limit = score_limit(a, flat);
+    const uint8_t* table = reinterpret_cast<const uint8_t*>(a.centroids) +
+                           static_cast<int64_t>(flat) * capacity * kHeadDim;
+    uint4 raw[4];
+    int current = first_group + warp;
+    if (current < last_group) {
+      load_group(table, current * 16, quad, slice, capacity, raw);
+    }
+    const __nv_bfloat16* query =
+        reinterpret_cast<const __nv_bfloat16*>(a.query) + static_cast<int64_t>(flat) * group * kHeadDim;
+    __syncthreads();  // the previous unit's query is no longer read
+    for (int i = threadIdx.x; i < group * kHeadDim; i += kScoreThreads) {
+      const int g = i >> 7;
+      const int dim = i & 127;
+      q_s[((g * 4 + ((dim >> 2) & 3)) * 8 + (dim >> 4)) * 4 + (dim & 3)] = __bfloat162float(query[i]);
+    }
+    __syncthreads();
+
+    const int count = a.community_counts[flat];
+    const int32_t* sizes = a.community_sizes + static_cast<int64_t>(flat) * capacity;
+    __half* out = reinterpret_cast<__half*>(a.scores) + static_cast<int64_t>(flat) * capacity;
+
+    for (; current < last_group; current += kScoreThreads / 32) {
+      float x[4][16];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        fp8x4_to_float(raw[i].x, x[i] + 0);
+        fp8x4_to_float(raw[i].y, x[i] + 4);
+        fp8x4_to_float(raw[i].z, x[i] + 8);
+        fp8x4_to_float(raw[i].w, x[i] + 12);
+      }
+      const int next = current + kScoreThreads / 32;
+      if (next < last_group) {
+        load_group(table, next * 16, quad, slice, capacity, raw);
+      }
+      const int row = current * 16 + my_row_in_group;
+      int size = 0;
+      if ((slice & 1) == 0 && row < limit) {
+        size = __ldg(sizes + row);
+      }
+
+      float best = -INFINITY;
+      for (int g = 0; g < group; ++g) {
+        float qv[16];
+        const float4* qp = reinterpret_cast<const float4*>(q_s) + g * 32 + slice;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float4 v = qp[k * 8];
+          qv[4 * k + 0] = v.x;
+          qv[4 * k + 1] = v.y;
+          qv[4 * k + 2] = v.z;
+          qv[4 * k + 3] = v.w;
+        }
+        float p[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float acc = __fmul_rn(x[i][0], qv[0]);
+#pragma unroll
+          for (int k = 1; k < 16; ++k) {
+            acc = __fmaf_rn(x[i][k], qv[k], acc);
+          }
+          p[i] = acc;
+        }
+        // Sum the eight slices of each row: (j, j^4), then (j, j^2), then (j, j^1),
+        // folding the four rows onto the lanes on the way (a transposing butterfly).
+        float keep0 = up_a ? p[2] : p[0];
+        float keep1 = up_a ? p[3] : p[1];
+        const float send0 = up_a ? p[0] : p[2];
+        const float send1 = up_a ? p[1] : p[3];
+        keep0 = __fadd_rn(keep0, __shfl_xor_sync(0xffffffffu, send0, 4));
+        keep1 = __fadd_rn(keep1, __shfl_xor_sync(0xffffffffu, send1, 4));
+        float keep = up_b ? keep1 : keep0;
+        const float send = up_b ? keep0 : keep1;
+        keep = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 2));
+        keep = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, keep, 1));
+        best = fmaxf(best, keep);
+      }
+      if ((slice & 1) == 0 && row < limit) {
+        const bool live = row < count && size > 0;
+        out[row] = __float2half_rn(live ? best : -INFINITY);
+      }
     }
   }
 }
@@ -232,7 +323,7 @@ __device__ __forceinline__ void find_threshold_bin(const int* hist_mass, const i
   }
 }
 
-__global__ void __launch_bounds__(kSelectThreads) select_kernel(const ckv_layer_args a) {
+__global__ void __launch_bounds__(kSelectThreads, 1) select_kernel(const ckv_layer_args a) {
   __shared__ uint16_t stash_key[kStash];
   __shared__ int stash_size[kStash];
   __shared__ int hist_mass[256];
@@ -240,6 +331,8 @@ __global__ void __launch_bounds__(kSelectThreads) select_kernel(const ckv_layer_
   __shared__ Quad scan_scratch[32];
   __shared__ Quad scan_total;
   __shared__ int s_bin, s_mass, s_count, s_stored_equal, s_descriptors;
+  __shared__ int32_t desc_comm[kDescStash];
+  __shared__ int32_t desc_end[kDescStash];
 
   const int flat = blockIdx.x;
   const Unit u = make_unit(a, flat);
@@ -262,10 +355,12 @@ __global__ void __launch_bounds__(kSelectThreads) select_kernel(const ckv_layer_
     s_stored_equal = 0;
   }
   if (stashed) {
+#pragma unroll 5
     for (int c = tid; c < active; c += kSelectThreads) {
-      const int size = sizes[c];
+      const int size = __ldg(sizes + c);
+      const uint16_t bits = score_bits[c];  // unconditional: both loads are in flight together
       stash_size[c] = size > 0 ? size : 0;
-      stash_key[c] = size > 0 ? ordered_key16(score_bits[c]) : 0;
+      stash_key[c] = size > 0 ? ordered_key16(bits) : 0;
     }
   }
   __syncthreads();
@@ -361,6 +456,10 @@ __global__ void __launch_bounds__(kSelectThreads) select_kernel(const ckv_layer_
       if (descriptor < a.descriptor_capacity) {
         out_comm[descriptor] = c;
         out_ends[descriptor] = prefix.high_mass;
+        if (descriptor < kDescStash) {
+          desc_comm[descriptor] = c;
+          desc_end[descriptor] = prefix.high_mass;
+        }
       }
     } else if (key == threshold) {
       const int start = total_high_mass + prefix.equal_mass;
@@ -372,6 +471,10 @@ __global__ void __launch_bounds__(kSelectThreads) select_kernel(const ckv_layer_
         if (rank < a.descriptor_capacity) {
           out_comm[rank] = c;
           out_ends[rank] = min(budget, start + size);
+          if (rank < kDescStash) {
+            desc_comm[rank] = c;
+            desc_end[rank] = min(budget, start + size);
+          }
         }
         stored_equal += 1;
       }
@@ -391,6 +494,9 @@ __global__ void __launch_bounds__(kSelectThreads) select_kernel(const ckv_layer_
   }
   __syncthreads();
   const int descriptors = s_descriptors;
+  const bool in_smem = descriptors <= kDescStash;
+  const int32_t* search_ends = in_smem ? desc_end : out_ends;
+  const int32_t* search_comm = in_smem ? desc_comm : out_comm;
 
   // First descriptor of every 64-token tile.
   for (int tile = tid; tile < tile_count; tile += kSelectThreads) {
@@ -399,7 +505,7 @@ __global__ void __launch_bounds__(kSelectThreads) select_kernel(const ckv_layer_
     int high = descriptors;
     while (low < high) {
       const int middle = (low + high) >> 1;
-      if (out_ends[middle] <= offset) {
+      if (search_ends[middle] <= offset) {
         low = middle + 1;
       } else {
         high = middle;
@@ -410,9 +516,70 @@ __global__ void __launch_bounds__(kSelectThreads) select_kernel(const ckv_layer_
   }
 
   // Resolve every logical token of the budget to its cache row.
+  // Two logical tokens per thread and pass, so that the two dependent global
+  // reads of each (community tables, then the member list) overlap.
   int32_t* positions = a.positions + static_cast<int64_t>(flat) * a.token_budget;
-  for (int logical = tid; logical < a.token_budget; logical += kSelectThreads) {
-    positions[logical] = resolve_token(a, u, flat, logical, descriptors);
+  const int64_t graph_slot = static_cast<int64_t>(u.batch) * a.graphs + u.graph;
+  const int32_t* delta_sizes = a.delta_sizes + graph_slot * capacity;
+  const int32_t* offsets = a.member_offsets + graph_slot * (capacity + 1);
+  const int32_t* members = a.member_positions + graph_slot * a.member_capacity;
+  for (int base = 0; base < a.token_budget; base += 2 * kSelectThreads) {
+    int logical[2], community[2], member[2], direct[2];
+    bool lookup[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      logical[i] = base + i * kSelectThreads + tid;
+      lookup[i] = false;
+      direct[i] = -1;
+      community[i] = 0;
+      member[i] = 0;
+      if (logical[i] >= a.token_budget) {
+        continue;
+      }
+      if (logical[i] < a.num_sink) {
+        direct[i] = a.sink_positions[logical[i]];
+      } else if (logical[i] == a.token_budget - 1) {
+        direct[i] = a.current_position[graph_slot];
+      } else {
+        const int offset = logical[i] - a.num_sink;
+        int low = 0;
+        int high = descriptors;
+        while (low < high) {
+          const int middle = (low + high) >> 1;
+          if (search_ends[middle] <= offset) {
+            low = middle + 1;
+          } else {
+            high = middle;
+          }
+        }
+        if (low < descriptors) {
+          lookup[i] = true;
+          community[i] = search_comm[low];
+          member[i] = offset - (low > 0 ? search_ends[low - 1] : 0);
+        }
+      }
+    }
+    int delta_count[2], start[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      delta_count[i] = lookup[i] ? delta_sizes[community[i]] : 0;
+      start[i] = lookup[i] ? offsets[community[i]] : 0;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (lookup[i] && member[i] >= delta_count[i]) {
+        direct[i] = members[start[i] + member[i] - delta_count[i]];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (lookup[i] && member[i] < delta_count[i]) {
+        direct[i] = delta_member_position(a, graph_slot, community[i], member[i]);
+      }
+      if (logical[i] < a.token_budget) {
+        positions[logical[i]] = direct[i];
+      }
+    }
   }
 }
 
@@ -425,13 +592,20 @@ __global__ void __launch_bounds__(256) resolve_kernel(const ckv_layer_args a) {
     return;
   }
   const int descriptors = min(a.descriptor_capacity, max(0, a.descriptor_counts[flat]));
+  const int64_t base = static_cast<int64_t>(flat) * a.descriptor_capacity;
   a.positions[static_cast<int64_t>(flat) * a.token_budget + logical] =
-      resolve_token(a, u, flat, logical, descriptors);
+      resolve_token(a, u, a.cumulative_ends + base, a.communities + base, logical, descriptors);
 }
 
 cudaError_t launch_score(const ckv_layer_args& a, cudaStream_t stream) {
-  const dim3 grid((a.community_capacity + kScoreRowsPerBlock - 1) / kScoreRowsPerBlock,
-                  a.batch * a.retrieval_heads);
+  // two CTAs per SM are resident: one wave, but never finer than eight 16-row
+  // groups (one per warp) per CTA
+  const int units = a.batch * a.retrieval_heads;
+  if (units > kScoreMaxUnits) {
+    return cudaErrorInvalidConfiguration;
+  }
+  const long long finest = static_cast<long long>(units) * ((a.community_capacity + 127) / 128);
+  const int grid = finest < 1 ? 1 : (finest > 2 * 148 ? 2 * 148 : static_cast<int>(finest));
   score_kernel<<<grid, kScoreThreads, 0, stream>>>(a);
   return cudaGetLastError();
 }

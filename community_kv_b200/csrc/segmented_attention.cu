@@ -1,17 +1,23 @@
 // Gather + segmented flash-decode attention over the resolved cache rows (sm_100a).
 //
-// Grid (splits, batch*R), 128 threads.  A CTA owns T/splits logical tokens of
-// one retrieval head; each of its four warps owns a contiguous quarter and runs
-// its own pipeline, 16 tokens per step:
-//   * lane i (<16) asks the TMA engine for K row i, lane 16+i for V row i: one
-//     256-byte cp.async.bulk per lane per step, completion counted on a per-warp
-//     mbarrier (three stages in flight per warp, no multicast, bounded waits);
-//   * rows land in shared memory at a 272-byte pitch so ldmatrix is conflict
-//     free; Q K^T and P V run on mma.m16n8k16 (bf16 in, fp32 accumulate) with the
-//     query group on the M axis;
-//   * the first head of the group is additionally scored on the CUDA cores in
-//     the fixed fp32 order shared with the CPU oracle; those scores feed the
-//     top-8 neighbour candidates, so the online labels are reproducible;
+// Grid (splits, batch*R), 128 threads, three CTAs per SM.  The T logical tokens of
+// one retrieval head are cut into 16-token steps; CTA `split` owns a contiguous
+// run of steps and each of its four warps a contiguous quarter of that run.  Every
+// warp runs its own two-stage pipeline:
+//   * the 16 K rows and 16 V rows of a step (256 bytes each, anywhere in the
+//     cache) are fetched with 16-byte cp.async copies, a half-warp per row, so
+//     every request is a full coalesced row; completion is tracked with
+//     cp.async groups (no barrier objects, nothing to spin on); masked slots are
+//     zero-filled without touching memory;
+//   * rows land in shared memory at a 272-byte pitch so ldmatrix is conflict free;
+//   * S^T = K Q^T and O^T = V^T P^T run on mma.m16n8k16 (bf16 in, fp32 accumulate)
+//     with the 16 tokens on the M axis and up to eight query heads on the N axis
+//     (two head blocks when the group is larger than eight), P^T moves from the
+//     accumulator layout to the operand layout with movmatrix;
+//   * the first head of the group is additionally scored on the CUDA cores in the
+//     fixed fp32 order shared with the CPU oracle (mixed-precision fma: bf16
+//     operands, fp32 accumulate, one rounding); those scores feed the top-8
+//     neighbour candidates, so the online labels are reproducible bit for bit;
 //   * running (max, sum, acc) per warp, merged across the four warps at the end
 //     and written as one partial per (split, head).
 
@@ -21,35 +27,60 @@ namespace ckv {
 
 constexpr int kAttnThreads = 128;
 constexpr int kAttnWarps = 4;
-constexpr int kStages = 3;
-constexpr int kRowPitch = 272;                       // bytes between staged rows
-constexpr int kStageBytes = 32 * kRowPitch;          // 16 K rows + 16 V rows
-constexpr int kWarpBytes = kStages * kStageBytes;    // 26112
-constexpr uint32_t kWaitPolls = 1u << 22;
+constexpr int kStages = 2;
+constexpr int kStepTokens = 16;
+constexpr int kRowPitch = 272;                     // bytes between staged rows
+constexpr int kStageBytes = 32 * kRowPitch;        // 16 K rows + 16 V rows
+constexpr int kWarpBytes = kStages * kStageBytes;  // 17408
 
 struct AttnSmem {
-  // dynamic layout: [warp][stage][32 rows x 272 B], then q_rep, then barriers
-  static constexpr int kRowsBytes = kAttnWarps * kWarpBytes;        // 104448
-  static constexpr int kQrepOffset = kRowsBytes;                    // 128 floats
-  static constexpr int kBarOffset = kQrepOffset + kHeadDim * 4;     // 12 x 8 B
-  static constexpr int kTopOffset = kBarOffset + kAttnWarps * kStages * 8;  // 4 x 8 u64
+  static constexpr int kRowsBytes = kAttnWarps * kWarpBytes;              // 69632
+  static constexpr int kQrepOffset = kRowsBytes;                          // 128 bf16
+  static constexpr int kTopOffset = kQrepOffset + kHeadDim * 2;           // 4 x 8 u64
   static constexpr int kTotal = kTopOffset + kAttnWarps * kKappa * 8;
 };
 
-__device__ __forceinline__ void top_insert(uint64_t (&list)[kKappa], uint64_t candidate) {
-  if (candidate > list[kKappa - 1]) {
-#pragma unroll
-    for (int k = 0; k < kKappa; ++k) {
-      const uint64_t resident = list[k];
-      const bool greater = candidate > resident;
-      list[k] = greater ? candidate : resident;
-      candidate = greater ? resident : candidate;
-    }
-  }
+// acc += a.lo*b.lo ; acc += a.hi*b.hi  with bf16 operands, fp32 accumulate, each
+// step rounded once (the product of two bf16 values is exact in fp32).
+__device__ __forceinline__ float fma2_bf16(uint32_t a, uint32_t b, float acc) {
+  asm("{\n"
+      ".reg .b16 al, ah, bl, bh;\n"
+      "mov.b32 {al, ah}, %1;\n"
+      "mov.b32 {bl, bh}, %2;\n"
+      "fma.rn.f32.bf16 %0, al, bl, %0;\n"
+      "fma.rn.f32.bf16 %0, ah, bh, %0;\n"
+      "}\n"
+      : "+f"(acc)
+      : "r"(a), "r"(b));
+  return acc;
 }
 
-template <bool kHigh>
-__global__ void __launch_bounds__(kAttnThreads) attention_kernel(const ckv_layer_args a) {
+__device__ __forceinline__ float dot16_bf16(const uint8_t* row, const uint8_t* q) {
+  const uint4 r0 = *reinterpret_cast<const uint4*>(row);
+  const uint4 r1 = *reinterpret_cast<const uint4*>(row + 16);
+  const uint4 q0 = *reinterpret_cast<const uint4*>(q);
+  const uint4 q1 = *reinterpret_cast<const uint4*>(q + 16);
+  float v = 0.f;
+  v = fma2_bf16(r0.x, q0.x, v);
+  v = fma2_bf16(r0.y, q0.y, v);
+  v = fma2_bf16(r0.z, q0.z, v);
+  v = fma2_bf16(r0.w, q0.w, v);
+  v = fma2_bf16(r1.x, q1.x, v);
+  v = fma2_bf16(r1.y, q1.y, v);
+  v = fma2_bf16(r1.z, q1.z, v);
+  v = fma2_bf16(r1.w, q1.w, v);
+  return v;
+}
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t value) {
+  uint32_t out;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(out) : "r"(value));
+  return out;
+}
+
+// kBlocks = number of 8-head blocks of the query group (1 for G <= 8, 2 for G <= 16).
+template <int kBlocks>
+__global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const ckv_layer_args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int flat = blockIdx.y;
   const int split = blockIdx.x;
@@ -57,26 +88,27 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const ckv_layer
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int group = a.group_size;
-  const int tokens_per_cta = a.token_budget / a.splits;
-  const int tokens_per_warp = tokens_per_cta / kAttnWarps;
-  const int steps = tokens_per_warp / 16;
-  const int warp_token0 = split * tokens_per_cta + warp * tokens_per_warp;
+
+  // contiguous runs of 16-token steps: CTA, then warp
+  const int steps_total = a.token_budget / kStepTokens;
+  const int cta_begin = static_cast<int>(static_cast<int64_t>(split) * steps_total / a.splits);
+  const int cta_end = static_cast<int>(static_cast<int64_t>(split + 1) * steps_total / a.splits);
+  const int cta_steps = cta_end - cta_begin;
+  const int warp_begin = cta_begin + warp * cta_steps / kAttnWarps;
+  const int warp_end = cta_begin + (warp + 1) * cta_steps / kAttnWarps;
+  const int steps = warp_end - warp_begin;
+  const int warp_token0 = warp_begin * kStepTokens;
 
   uint8_t* warp_rows = smem + warp * kWarpBytes;
-  float* q_rep = reinterpret_cast<float*>(smem + AttnSmem::kQrepOffset);
-  const uint32_t bar_base = smem_u32(smem + AttnSmem::kBarOffset) + warp * kStages * 8;
+  uint8_t* q_rep = smem + AttnSmem::kQrepOffset;
   uint64_t* top_s = reinterpret_cast<uint64_t*>(smem + AttnSmem::kTopOffset);
 
   const __nv_bfloat16* query = reinterpret_cast<const __nv_bfloat16*>(a.query) +
                                (static_cast<int64_t>(u.batch) * a.retrieval_heads + u.head) *
                                    group * kHeadDim;
-  q_rep[threadIdx.x] = __bfloat162float(query[threadIdx.x]);
-  if (lane == 0) {
-#pragma unroll
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar_base + s * 8, 1);
-    }
-    mbar_fence_init();
+  if (threadIdx.x < kHeadDim / 2) {
+    reinterpret_cast<uint32_t*>(q_rep)[threadIdx.x] =
+        reinterpret_cast<const uint32_t*>(query)[threadIdx.x];
   }
   __syncthreads();
 
@@ -86,284 +118,253 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const ckv_layer
   const __nv_bfloat16* value_head = reinterpret_cast<const __nv_bfloat16*>(a.value) +
                                     u.batch * a.value_batch_stride + u.kv * a.value_head_stride;
   const int token_lane = lane & 15;
-  const bool value_lane = lane >= 16;
   const uint32_t rows_u32 = smem_u32(warp_rows);
 
-  auto issue = [&](int step) {
-    const int stage = step % kStages;
-    const int pos = positions[warp_token0 + step * 16 + token_lane];
-    const int64_t row = pos > 0 ? pos : 0;
-    const __nv_bfloat16* src =
-        value_lane ? value_head + row * a.value_row_stride : key_head + row * a.key_row_stride;
-    const uint32_t bar = bar_base + stage * 8;
-    if (lane == 0) {
-      mbar_expect_tx(bar, 32 * kHeadDim * 2);
+  // One step = 32 rows.  Half-warp `lane >> 4` copies rows 2j + (lane >> 4), lane & 15
+  // picks the 16-byte piece of the row.  Every lane holds the position of token lane & 15.
+  const int piece = lane & 15;
+  const int row_half = lane >> 4;
+  auto issue = [&](int step, int pos) {
+    const uint32_t dst = rows_u32 + (step % kStages) * kStageBytes + piece * 16;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int row = 2 * j + row_half;
+      const int row_pos = __shfl_sync(0xffffffffu, pos, row);
+      const int64_t safe = row_pos > 0 ? row_pos : 0;
+      const uint32_t bytes = row_pos >= 0 ? 16u : 0u;  // 0: zero-fill, nothing is read
+      cp_async16(dst + row * kRowPitch, key_head + safe * a.key_row_stride + piece * 8, bytes);
+      cp_async16(dst + (16 + row) * kRowPitch, value_head + safe * a.value_row_stride + piece * 8,
+                 bytes);
     }
-    __syncwarp();
-    bulk_copy_g2s(rows_u32 + stage * kStageBytes + lane * kRowPitch, src, kHeadDim * 2, bar);
   };
 
-  const int prologue = steps < kStages ? steps : kStages;
-  for (int s = 0; s < prologue; ++s) {
-    issue(s);
+  // positions of the steps in flight (this lane's token) and of the next one
+  static_assert(kStages == 2, "the position ring below is written for two stages");
+  int pos_even = 0 < steps ? positions[warp_token0 + token_lane] : -1;
+  int pos_odd = 1 < steps ? positions[warp_token0 + kStepTokens + token_lane] : -1;
+  if (0 < steps) {
+    issue(0, pos_even);
   }
+  cp_async_commit();
+  if (1 < steps) {
+    issue(1, pos_odd);
+  }
+  cp_async_commit();
 
-  // A fragments of the query group: rows g (and g+8) of a 16 x 128 matrix.
+  // B fragments of Q^T: b0 = q[head g][16ks + 2t .. +1], b1 = the same + 8
   const int g_row = lane >> 2;
   const int t_col = lane & 3;
-  uint32_t qa[8][4];
+  uint32_t qb[kBlocks][8][2];
 #pragma unroll
-  for (int ks = 0; ks < 8; ++ks) {
-    const int col = ks * 16 + 2 * t_col;
-    qa[ks][0] = qa[ks][1] = qa[ks][2] = qa[ks][3] = 0u;
-    if (g_row < group) {
-      qa[ks][0] = *reinterpret_cast<const uint32_t*>(query + g_row * kHeadDim + col);
-      qa[ks][2] = *reinterpret_cast<const uint32_t*>(query + g_row * kHeadDim + col + 8);
-    }
-    if (kHigh && g_row + 8 < group) {
-      qa[ks][1] = *reinterpret_cast<const uint32_t*>(query + (g_row + 8) * kHeadDim + col);
-      qa[ks][3] = *reinterpret_cast<const uint32_t*>(query + (g_row + 8) * kHeadDim + col + 8);
+  for (int hb = 0; hb < kBlocks; ++hb) {
+    const int head = hb * 8 + g_row;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      qb[hb][ks][0] = qb[hb][ks][1] = 0u;
+      if (head < group) {
+        const __nv_bfloat16* src = query + head * kHeadDim + ks * 16 + 2 * t_col;
+        qb[hb][ks][0] = *reinterpret_cast<const uint32_t*>(src);
+        qb[hb][ks][1] = *reinterpret_cast<const uint32_t*>(src + 8);
+      }
     }
   }
 
-  float acc[16][4];
+  // O^T accumulators: acc[hb][mb] covers d = 16mb + g (+8), heads 8hb + 2t, +1
+  float acc[kBlocks][8][4];
+  float run_max[kBlocks][2], run_sum[kBlocks][2];
 #pragma unroll
-  for (int n = 0; n < 16; ++n) {
-    acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-  }
-  float run_max_lo = -INFINITY, run_max_hi = -INFINITY;
-  float run_sum_lo = 0.f, run_sum_hi = 0.f;
-  uint64_t top[kKappa];
+  for (int hb = 0; hb < kBlocks; ++hb) {
+    run_max[hb][0] = run_max[hb][1] = -INFINITY;
+    run_sum[hb][0] = run_sum[hb][1] = 0.f;
 #pragma unroll
-  for (int k = 0; k < kKappa; ++k) {
-    top[k] = 0ull;
+    for (int mb = 0; mb < 8; ++mb) {
+      acc[hb][mb][0] = acc[hb][mb][1] = acc[hb][mb][2] = acc[hb][mb][3] = 0.f;
+    }
   }
+  // warp-wide top-8 neighbour candidates: lane j (<8) holds the j-th best
+  uint64_t warp_top = 0ull;
+  uint64_t warp_floor = 0ull;  // current 8th best (0 while fewer than 8)
   const float scale = a.softmax_scale;
-  bool failed = false;
 
   for (int step = 0; step < steps; ++step) {
     const int stage = step % kStages;
-    const uint32_t parity = (step / kStages) & 1;
-    if (!mbar_wait_bounded(bar_base + stage * 8, parity, kWaitPolls)) {
-      failed = true;
-    }
-    if (__any_sync(0xffffffffu, failed)) {
-      failed = true;
-      break;
-    }
+    // position of the token this lane will fetch for step + kStages (prefetch now)
+    const int next_step = step + kStages;
+    const int next_pos =
+        next_step < steps ? positions[warp_token0 + next_step * kStepTokens + token_lane] : -1;
+    cp_async_wait<kStages - 1>();  // this step's group has landed (one younger group may be pending)
+    __syncwarp();
     const uint32_t k_u32 = rows_u32 + stage * kStageBytes;
     const uint32_t v_u32 = k_u32 + 16 * kRowPitch;
-    const int my_pos = positions[warp_token0 + step * 16 + token_lane];
+    const int my_pos = stage ? pos_odd : pos_even;
     const unsigned valid_bits = __ballot_sync(0xffffffffu, my_pos >= 0) & 0xffffu;
+    const bool ok_lo = (valid_bits >> g_row) & 1u;        // token g
+    const bool ok_hi = (valid_bits >> (g_row + 8)) & 1u;  // token g + 8
 
-    // ---- S = Q K^T for 16 tokens (two 8-token column blocks) ----
-    float s[2][4];
+    // ---- S^T = K Q^T : 16 tokens x 8 heads per block, two interleaved chains ----
+    float s[kBlocks][4];
+    {
+      float even[kBlocks][4], odd[kBlocks][4];
 #pragma unroll
-    for (int nb = 0; nb < 2; ++nb) {
-      s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+      for (int hb = 0; hb < kBlocks; ++hb) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        uint32_t b0, b1, b2, b3;
-        const uint32_t addr =
-            k_u32 + (nb * 8 + (lane & 7)) * kRowPitch + (kk * 4 + (lane >> 3)) * 16;
-        ldmatrix_x4(addr, b0, b1, b2, b3);
-        mma_bf16_16816(s[nb], qa[2 * kk][0], qa[2 * kk][1], qa[2 * kk][2], qa[2 * kk][3], b0, b1);
-        mma_bf16_16816(s[nb], qa[2 * kk + 1][0], qa[2 * kk + 1][1], qa[2 * kk + 1][2],
-                       qa[2 * kk + 1][3], b2, b3);
+        for (int e = 0; e < 4; ++e) {
+          even[hb][e] = 0.f;
+          odd[hb][e] = 0.f;
+        }
       }
-    }
-    // scale + mask; columns of s[nb][0..1] are tokens nb*8 + 2t, +1
-    float tile_max_lo = -INFINITY, tile_max_hi = -INFINITY;
+      const uint32_t a_base = k_u32 + ((lane & 7) + 8 * ((lane >> 3) & 1)) * kRowPitch + (lane >> 4) * 16;
 #pragma unroll
-    for (int nb = 0; nb < 2; ++nb) {
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t a0, a1, a2, a3;
+        ldmatrix_x4(a_base + ks * 32, a0, a1, a2, a3);
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int token = nb * 8 + 2 * t_col + e;
-        const bool ok = (valid_bits >> token) & 1u;
-        s[nb][e] = ok ? s[nb][e] * scale : -INFINITY;
-        s[nb][2 + e] = ok ? s[nb][2 + e] * scale : -INFINITY;
-        tile_max_lo = fmaxf(tile_max_lo, s[nb][e]);
-        tile_max_hi = fmaxf(tile_max_hi, s[nb][2 + e]);
+        for (int hb = 0; hb < kBlocks; ++hb) {
+          mma_bf16_16816((ks & 1) ? odd[hb] : even[hb], a0, a1, a2, a3, qb[hb][ks][0], qb[hb][ks][1]);
+        }
       }
-    }
-    tile_max_lo = fmaxf(tile_max_lo, __shfl_xor_sync(0xffffffffu, tile_max_lo, 1));
-    tile_max_lo = fmaxf(tile_max_lo, __shfl_xor_sync(0xffffffffu, tile_max_lo, 2));
-    if (kHigh) {
-      tile_max_hi = fmaxf(tile_max_hi, __shfl_xor_sync(0xffffffffu, tile_max_hi, 1));
-      tile_max_hi = fmaxf(tile_max_hi, __shfl_xor_sync(0xffffffffu, tile_max_hi, 2));
-    }
-    const float new_max_lo = fmaxf(run_max_lo, tile_max_lo);
-    const float safe_lo = new_max_lo == -INFINITY ? 0.f : new_max_lo;
-    const float corr_lo = exp2f((run_max_lo - safe_lo) * kLog2e);
-    run_max_lo = new_max_lo;
-    float corr_hi = 1.f, safe_hi = 0.f;
-    if (kHigh) {
-      const float new_max_hi = fmaxf(run_max_hi, tile_max_hi);
-      safe_hi = new_max_hi == -INFINITY ? 0.f : new_max_hi;
-      corr_hi = exp2f((run_max_hi - safe_hi) * kLog2e);
-      run_max_hi = new_max_hi;
-    }
-    float p[2][4];
-    float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
-    for (int nb = 0; nb < 2; ++nb) {
+      for (int hb = 0; hb < kBlocks; ++hb) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        p[nb][e] = exp2f((s[nb][e] - safe_lo) * kLog2e);
-        sum_lo += p[nb][e];
-        if (kHigh) {
-          p[nb][2 + e] = exp2f((s[nb][2 + e] - safe_hi) * kLog2e);
-          sum_hi += p[nb][2 + e];
-        } else {
-          p[nb][2 + e] = 0.f;
+        for (int e = 0; e < 4; ++e) {
+          s[hb][e] = even[hb][e] + odd[hb][e];
         }
       }
     }
-    run_sum_lo = run_sum_lo * corr_lo + sum_lo;
-    if (kHigh) {
-      run_sum_hi = run_sum_hi * corr_hi + sum_hi;
-    }
-    const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]);
-    const uint32_t pa2 = pack_bf16(p[1][0], p[1][1]);
-    const uint32_t pa1 = kHigh ? pack_bf16(p[0][2], p[0][3]) : 0u;
-    const uint32_t pa3 = kHigh ? pack_bf16(p[1][2], p[1][3]) : 0u;
 
-    // ---- O = O * corr + P V ----
+    // ---- online softmax per head (heads 2t, 2t+1 of each block live on this lane) ----
+    uint32_t pb[kBlocks][2];
+    bool rescale = false;
+    float corr[kBlocks][2];
 #pragma unroll
-    for (int dd = 0; dd < 8; ++dd) {
-      uint32_t b0, b1, b2, b3;
-      const uint32_t addr =
-          v_u32 + ((lane & 7) + 8 * ((lane >> 3) & 1)) * kRowPitch + (2 * dd + (lane >> 4)) * 16;
-      ldmatrix_x4_trans(addr, b0, b1, b2, b3);
+    for (int hb = 0; hb < kBlocks; ++hb) {
+      s[hb][0] = ok_lo ? s[hb][0] * scale : -INFINITY;
+      s[hb][1] = ok_lo ? s[hb][1] * scale : -INFINITY;
+      s[hb][2] = ok_hi ? s[hb][2] * scale : -INFINITY;
+      s[hb][3] = ok_hi ? s[hb][3] * scale : -INFINITY;
+      float p[4];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float* o = acc[2 * dd + half];
-        o[0] *= corr_lo;
-        o[1] *= corr_lo;
-        if (kHigh) {
-          o[2] *= corr_hi;
-          o[3] *= corr_hi;
+      for (int e = 0; e < 2; ++e) {
+        float tile_max = fmaxf(s[hb][e], s[hb][2 + e]);
+        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
+        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
+        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
+        const float new_max = fmaxf(run_max[hb][e], tile_max);
+        const float safe = new_max == -INFINITY ? 0.f : new_max;
+        corr[hb][e] = exp2f((run_max[hb][e] - safe) * kLog2e);
+        rescale = rescale || (new_max != run_max[hb][e]);
+        run_max[hb][e] = new_max;
+        p[e] = exp2f((s[hb][e] - safe) * kLog2e);
+        p[2 + e] = exp2f((s[hb][2 + e] - safe) * kLog2e);
+        run_sum[hb][e] = run_sum[hb][e] * corr[hb][e] + p[e] + p[2 + e];
+      }
+      // accumulator layout (token g | g+8, heads 2t,2t+1) -> operand layout
+      // (tokens 2t,2t+1 | +8, head g)
+      pb[hb][0] = movmatrix_trans(pack_bf16(p[0], p[1]));
+      pb[hb][1] = movmatrix_trans(pack_bf16(p[2], p[3]));
+    }
+    if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+      for (int hb = 0; hb < kBlocks; ++hb) {
+#pragma unroll
+        for (int mb = 0; mb < 8; ++mb) {
+          acc[hb][mb][0] *= corr[hb][0];
+          acc[hb][mb][1] *= corr[hb][1];
+          acc[hb][mb][2] *= corr[hb][0];
+          acc[hb][mb][3] *= corr[hb][1];
         }
       }
-      mma_bf16_16816(acc[2 * dd], pa0, pa1, pa2, pa3, b0, b1);
-      mma_bf16_16816(acc[2 * dd + 1], pa0, pa1, pa2, pa3, b2, b3);
+    }
+
+    // ---- O^T += V^T P^T ----
+    {
+      const uint32_t v_base = v_u32 + ((lane & 7) + 8 * (lane >> 4)) * kRowPitch + ((lane >> 3) & 1) * 16;
+#pragma unroll
+      for (int mb = 0; mb < 8; ++mb) {
+        uint32_t a0, a1, a2, a3;
+        ldmatrix_x4_trans(v_base + mb * 32, a0, a1, a2, a3);
+#pragma unroll
+        for (int hb = 0; hb < kBlocks; ++hb) {
+          mma_bf16_16816(acc[hb][mb], a0, a1, a2, a3, pb[hb][0], pb[hb][1]);
+        }
+      }
     }
 
     // ---- fixed-order fp32 score of the group's first head (neighbour candidates) ----
     {
       const int half = lane >> 4;  // 0: slices 0,4,2,6   1: slices 1,5,3,7
       const uint8_t* row = warp_rows + stage * kStageBytes + token_lane * kRowPitch;
-      float part[4];
-#pragma unroll
-      for (int idx = 0; idx < 4; ++idx) {
-        const int slice = (idx == 0 ? 0 : idx == 1 ? 4 : idx == 2 ? 2 : 6) + half;
-        const uint4 r0 = *reinterpret_cast<const uint4*>(row + slice * 32);
-        const uint4 r1 = *reinterpret_cast<const uint4*>(row + slice * 32 + 16);
-        const float4* qp = reinterpret_cast<const float4*>(q_rep + slice * 16);
-        const float4 q0 = qp[0], q1 = qp[1], q2 = qp[2], q3 = qp[3];
-        float v = __fmul_rn(bf16_lo(r0.x), q0.x);
-        v = __fmaf_rn(bf16_hi(r0.x), q0.y, v);
-        v = __fmaf_rn(bf16_lo(r0.y), q0.z, v);
-        v = __fmaf_rn(bf16_hi(r0.y), q0.w, v);
-        v = __fmaf_rn(bf16_lo(r0.z), q1.x, v);
-        v = __fmaf_rn(bf16_hi(r0.z), q1.y, v);
-        v = __fmaf_rn(bf16_lo(r0.w), q1.z, v);
-        v = __fmaf_rn(bf16_hi(r0.w), q1.w, v);
-        v = __fmaf_rn(bf16_lo(r1.x), q2.x, v);
-        v = __fmaf_rn(bf16_hi(r1.x), q2.y, v);
-        v = __fmaf_rn(bf16_lo(r1.y), q2.z, v);
-        v = __fmaf_rn(bf16_hi(r1.y), q2.w, v);
-        v = __fmaf_rn(bf16_lo(r1.z), q3.x, v);
-        v = __fmaf_rn(bf16_hi(r1.z), q3.y, v);
-        v = __fmaf_rn(bf16_lo(r1.w), q3.z, v);
-        v = __fmaf_rn(bf16_hi(r1.w), q3.w, v);
-        part[idx] = v;
-      }
-      float total = __fadd_rn(__fadd_rn(part[0], part[1]), __fadd_rn(part[2], part[3]));
+      const float p0 = dot16_bf16(row + (0 + half) * 32, q_rep + (0 + half) * 32);
+      const float p1 = dot16_bf16(row + (4 + half) * 32, q_rep + (4 + half) * 32);
+      const float p2 = dot16_bf16(row + (2 + half) * 32, q_rep + (2 + half) * 32);
+      const float p3 = dot16_bf16(row + (6 + half) * 32, q_rep + (6 + half) * 32);
+      float total = __fadd_rn(__fadd_rn(p0, p1), __fadd_rn(p2, p3));
       total = __fadd_rn(total, __shfl_xor_sync(0xffffffffu, total, 16));
+      uint64_t candidate = 0ull;
       if (lane < 16 && my_pos >= 0) {
-        const int logical = warp_token0 + step * 16 + token_lane;
-        const float candidate = logical < a.num_sink ? -INFINITY : __fmul_rn(total, scale);
-        const uint64_t packed = (static_cast<uint64_t>(ordered_key32(candidate)) << 32) |
-                                (0xffffffffu - static_cast<uint32_t>(my_pos));
-        top_insert(top, packed);
+        const int logical = warp_token0 + step * kStepTokens + token_lane;
+        const float score = logical < a.num_sink ? -INFINITY : __fmul_rn(total, scale);
+        candidate = (static_cast<uint64_t>(ordered_key32(score)) << 32) |
+                    (0xffffffffu - static_cast<uint32_t>(my_pos));
+      }
+      unsigned pending = __ballot_sync(0xffffffffu, candidate > warp_floor);
+      while (pending) {
+        const int src = __ffs(pending) - 1;
+        pending &= pending - 1;
+        const uint64_t c = (static_cast<uint64_t>(__shfl_sync(0xffffffffu, static_cast<uint32_t>(candidate >> 32), src)) << 32) |
+                           __shfl_sync(0xffffffffu, static_cast<uint32_t>(candidate), src);
+        const uint32_t up_hi = __shfl_up_sync(0xffffffffu, static_cast<uint32_t>(warp_top >> 32), 1);
+        const uint32_t up_lo = __shfl_up_sync(0xffffffffu, static_cast<uint32_t>(warp_top), 1);
+        const uint64_t above = (static_cast<uint64_t>(up_hi) << 32) | up_lo;
+        if (lane < kKappa && c > warp_top) {
+          warp_top = (lane > 0 && above < c) ? above : c;
+        }
+        warp_floor = (static_cast<uint64_t>(__shfl_sync(0xffffffffu, static_cast<uint32_t>(warp_top >> 32), kKappa - 1)) << 32) |
+                     __shfl_sync(0xffffffffu, static_cast<uint32_t>(warp_top), kKappa - 1);
       }
     }
 
     __syncwarp();
-    if (step + kStages < steps) {
-      fence_proxy_async();
-      issue(step + kStages);
-    }
-  }
-
-  if (failed) {
-    // Give the copies still in flight a bounded chance to land before the
-    // shared memory is released, then report and leave without writing.
-    for (int s = 0; s < kStages; ++s) {
-      mbar_wait_bounded(bar_base + s * 8, 0, 1u << 16);
-      mbar_wait_bounded(bar_base + s * 8, 1, 1u << 16);
-    }
-    if (lane == 0 && a.status != nullptr) {
-      atomicOr(a.status, CKV_DEV_WAIT_TIMEOUT);
-    }
-  }
-  const int any_failed = __syncthreads_or(failed ? 1 : 0);
-  if (any_failed) {
-    return;
-  }
-
-  // ---- per-warp epilogue: finish the row sums, park (max, sum, acc) in this
-  // warp's (now idle) staging area ----
-  run_sum_lo += __shfl_xor_sync(0xffffffffu, run_sum_lo, 1);
-  run_sum_lo += __shfl_xor_sync(0xffffffffu, run_sum_lo, 2);
-  if (kHigh) {
-    run_sum_hi += __shfl_xor_sync(0xffffffffu, run_sum_hi, 1);
-    run_sum_hi += __shfl_xor_sync(0xffffffffu, run_sum_hi, 2);
-  }
-  float* park = reinterpret_cast<float*>(warp_rows);  // [group][130]
-  if (g_row < group) {
-    float* dst = park + g_row * kPartialStride;
-    if (t_col == 0) {
-      dst[0] = run_max_lo;
-      dst[1] = run_sum_lo;
-    }
-#pragma unroll
-    for (int n = 0; n < 16; ++n) {
-      dst[2 + n * 8 + 2 * t_col] = acc[n][0];
-      dst[2 + n * 8 + 2 * t_col + 1] = acc[n][1];
-    }
-  }
-  if (kHigh && g_row + 8 < group) {
-    float* dst = park + (g_row + 8) * kPartialStride;
-    if (t_col == 0) {
-      dst[0] = run_max_hi;
-      dst[1] = run_sum_hi;
-    }
-#pragma unroll
-    for (int n = 0; n < 16; ++n) {
-      dst[2 + n * 8 + 2 * t_col] = acc[n][2];
-      dst[2 + n * 8 + 2 * t_col + 1] = acc[n][3];
-    }
-  }
-
-  // warp-level top-8 of the lanes' sorted lists
-  {
-    int cursor = 0;
-    for (int k = 0; k < kKappa; ++k) {
-      uint64_t head = 0ull;
-#pragma unroll
-      for (int slot = 0; slot < kKappa; ++slot) {
-        head = cursor == slot ? top[slot] : head;
+    if (next_step < steps) {
+      if (stage) {
+        pos_odd = next_pos;
+      } else {
+        pos_even = next_pos;
       }
-      const uint64_t best = warp_max_u64(head);
-      if (lane == 0) {
-        top_s[warp * kKappa + k] = best;
-      }
-      if (best != 0ull && head == best) {
-        ++cursor;
+      issue(next_step, next_pos);
+    }
+    cp_async_commit();
+  }
+  cp_async_wait<0>();
+
+  // ---- per-warp epilogue: finish the row sums, park (max, sum, acc) per head in
+  // this warp's (now idle) staging area ----
+  float* park = reinterpret_cast<float*>(warp_rows);  // [group][132]: acc[128], max, sum
+#pragma unroll
+  for (int hb = 0; hb < kBlocks; ++hb) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float sum = run_sum[hb][e];
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+      const int head = hb * 8 + 2 * t_col + e;
+      if (head < group) {
+        float* dst = park + head * kPartialStride;
+        if (g_row == 0) {
+          dst[kHeadDim] = run_max[hb][e];
+          dst[kHeadDim + 1] = sum;
+        }
+#pragma unroll
+        for (int mb = 0; mb < 8; ++mb) {
+          dst[mb * 16 + g_row] = acc[hb][mb][e];
+          dst[mb * 16 + g_row + 8] = acc[hb][mb][2 + e];
+        }
       }
     }
+  }
+  if (lane < kKappa) {
+    top_s[warp * kKappa + lane] = warp_top;
   }
   __syncthreads();
 
@@ -376,7 +377,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const ckv_layer
     float best = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kAttnWarps; ++w) {
-      m[w] = reinterpret_cast<const float*>(smem + w * kWarpBytes)[g * kPartialStride];
+      m[w] = reinterpret_cast<const float*>(smem + w * kWarpBytes)[g * kPartialStride + kHeadDim];
       best = fmaxf(best, m[w]);
     }
     const float safe = best == -INFINITY ? 0.f : best;
@@ -386,15 +387,15 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const ckv_layer
     for (int w = 0; w < kAttnWarps; ++w) {
       const float* src = reinterpret_cast<const float*>(smem + w * kWarpBytes) + g * kPartialStride;
       const float weight = exp2f((m[w] - safe) * kLog2e);
-      sum += src[1] * weight;
-      out += src[2 + d] * weight;
+      sum += src[kHeadDim + 1] * weight;
+      out += src[d] * weight;
     }
     float* dst = partial + g * kPartialStride;
     if (d == 0) {
-      dst[0] = best;
-      dst[1] = sum;
+      dst[kHeadDim] = best;
+      dst[kHeadDim + 1] = sum;
     }
-    dst[2 + d] = out;
+    dst[d] = out;
   }
   if (warp == 0) {
     uint64_t mine = top_s[lane];
@@ -417,20 +418,20 @@ cudaError_t launch_attention(const ckv_layer_args& a, cudaStream_t stream) {
   static bool configured[64] = {};
   const int device = a.device >= 0 && a.device < 64 ? a.device : 0;
   if (!configured[device]) {
-    cudaError_t err = cudaFuncSetAttribute(attention_kernel<false>,
+    cudaError_t err = cudaFuncSetAttribute(attention_kernel<1>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            AttnSmem::kTotal);
     if (err != cudaSuccess) return err;
-    err = cudaFuncSetAttribute(attention_kernel<true>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::kTotal);
+    err = cudaFuncSetAttribute(attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               AttnSmem::kTotal);
     if (err != cudaSuccess) return err;
     configured[device] = true;
   }
   const dim3 grid(a.splits, a.batch * a.retrieval_heads);
   if (a.group_size > 8) {
-    attention_kernel<true><<<grid, kAttnThreads, AttnSmem::kTotal, stream>>>(a);
+    attention_kernel<2><<<grid, kAttnThreads, AttnSmem::kTotal, stream>>>(a);
   } else {
-    attention_kernel<false><<<grid, kAttnThreads, AttnSmem::kTotal, stream>>>(a);
+    attention_kernel<1><<<grid, kAttnThreads, AttnSmem::kTotal, stream>>>(a);
   }
   return cudaGetLastError();
 }

@@ -99,7 +99,7 @@ class LayerArgs(ctypes.Structure):
 FLAG_SKIP_UPDATE = 1
 FLAG_ATTENTION_ONLY = 2
 DEV_WAIT_TIMEOUT = 1
-PARTIAL_STRIDE = 130
+PARTIAL_STRIDE = 132
 
 ENTRY_POINTS = (
     "ckv_version",

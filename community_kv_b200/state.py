@@ -20,7 +20,7 @@ import torch
 HEAD_DIM = 128
 ATTENTION_TILE = 64
 KAPPA = 8
-PARTIAL_STRIDE = 130
+PARTIAL_STRIDE = 132
 DEFAULT_SPLITS = 8
 
 
@@ -37,15 +37,19 @@ def _int32(name: str, tensor: torch.Tensor) -> None:
         raise TypeError(f"{name} must use torch.int32")
 
 
-def choose_splits(token_budget: int, requested: int = DEFAULT_SPLITS) -> int:
-    """Largest split count <= requested (and <= 32) that divides the tile count."""
+RESIDENT_ATTENTION_CTAS = 3 * 148  # three attention CTAs fit one SM; a B200 has 148 SMs
 
-    tiles = token_budget // ATTENTION_TILE
-    best = 1
-    for candidate in range(1, min(requested, 32, tiles) + 1):
-        if tiles % candidate == 0:
-            best = candidate
-    return best
+
+def choose_splits(token_budget: int, units: int, requested: int | None = None) -> int:
+    """Attention CTAs per retrieval head.
+
+    By default the (sequence, head) units of one launch share a single wave of
+    resident CTAs; a head's tokens are cut into 16-token steps, so at most
+    ``token_budget // 16`` (and never more than 32) CTAs can work on one head.
+    """
+
+    wanted = requested if requested else max(1, RESIDENT_ATTENTION_CTAS // max(units, 1))
+    return max(1, min(wanted, 32, token_budget // 16))
 
 
 @dataclass(slots=True)
@@ -461,7 +465,7 @@ class SegmentedAttentionWorkspace:
             raise ValueError("token_budget must be a positive multiple of 64")
         if dtype != torch.bfloat16:
             raise TypeError("the attention operator requires BF16 Q/K/V")
-        splits = choose_splits(token_budget, splits or DEFAULT_SPLITS)
+        splits = choose_splits(token_budget, (batch or 1) * kv_heads, splits)
         lead = _lead(batch)
         heads = lead + (kv_heads,)
         query_heads = lead + (kv_heads * group_size,)

@@ -40,7 +40,7 @@ extern "C" {
 #define CKV_HEAD_DIM 128
 #define CKV_TILE 64
 #define CKV_KAPPA 8
-#define CKV_PARTIAL_STRIDE 130 /* floats per (split, head): max, sum, acc[128] */
+#define CKV_PARTIAL_STRIDE 132 /* floats per (split, head): acc[128], max, sum, 2 pad */
 
 typedef enum ckv_status {
   CKV_OK = 0,
@@ -79,7 +79,7 @@ typedef struct ckv_layer_args {
   int32_t delta_position_capacity;
   int32_t descriptor_capacity; /* width of communities / cumulative_ends, >= T - num_sink - 1 */
   int32_t max_communities;    /* 0: fill the token budget (reference behaviour); k>0: at most k communities */
-  int32_t splits;             /* attention CTAs per retrieval head; T % (64*splits) == 0 */
+  int32_t splits;             /* attention CTAs per retrieval head, 1..32 */
   int32_t flags;
   float softmax_scale;
   float lam;
@@ -125,7 +125,7 @@ typedef struct ckv_layer_args {
   int32_t* threshold_state;    /* [batch, R, 4]; slot 0 receives the threshold key */
   /* ---- attention workspace ---- */
   int32_t* positions;          /* [batch, R, T] resolved cache rows, -1 = masked */
-  float* partials;             /* [batch, R, splits, G, 130] */
+  float* partials;             /* [batch, R, splits, G, 132] */
   uint64_t* partial_topk;      /* [batch, R, splits, 8] */
   void* output;                /* bf16 [batch, R*G, 128] */
   float* lse;                  /* [batch, R*G] */
