@@ -97,6 +97,10 @@ class LayerArgs(ctypes.Structure):
 
 
 FLAG_SKIP_UPDATE = 1
+STATIC_MAX_UNITS = 64
+STATIC_MAX_BUDGET = 4096
+STATIC_MAX_SPLITS = 8
+STATIC_MAX_GROUP = 8
 FLAG_ATTENTION_ONLY = 2
 DEV_WAIT_TIMEOUT = 1
 PARTIAL_STRIDE = 132
@@ -109,6 +113,7 @@ ENTRY_POINTS = (
     "ckv_segmented_attention",
     "ckv_decode_layer",
     "ckv_attention_smem_bytes",
+    "ckv_segmented_attention_static",
 )
 
 
@@ -134,6 +139,7 @@ def library() -> ctypes.CDLL:
         "ckv_select_descriptors",
         "ckv_segmented_attention",
         "ckv_decode_layer",
+        "ckv_segmented_attention_static",
     ):
         function = getattr(lib, name)
         function.restype = ctypes.c_int

@@ -411,6 +411,79 @@ def segmented_attention(
 triton_segmented_attention = segmented_attention
 
 
+def segmented_attention_static(
+    *,
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    csr: PrefillCSR,
+    deltas: DecodeDeltaChunks,
+    segments: PackedSegments,
+    sink_positions: torch.Tensor,
+    current_position: torch.Tensor,
+    softmax_scale: float,
+    workspace: SegmentedAttentionWorkspace,
+    update_state: MutableGraphState,
+    update_workspace: OnlineUpdateWorkspace | None,
+    update_lam: float,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``segmented_attention`` for hosts that must not allocate device memory.
+
+    Meant for callers that live inside a fixed memory budget - a serving process
+    whose pool is fully handed out, a plug-in running in memory it does not own -
+    and therefore cannot provide (or let this package provide) scratch tensors.
+    Only the outputs of ``workspace`` are used; the row positions, split partials
+    and candidate lists stay in a fixed array inside the CUDA library.  Limits:
+    at most 64 (sequence, head) units, budget 4096, 8 splits, group size 8
+    (``NativeError`` beyond).  Calls share that one array, so two calls that may
+    overlap on the GPU race; the first call on a device should come before any
+    stream capture.  Results are identical to ``segmented_attention``.
+    """
+
+    _check_update(update_state, deltas, csr)
+    device = _require_cuda(query, key, value, segments.communities)
+    heads = update_state.retrieval_head_count
+    if query.shape[-2:] != (heads * workspace.group_size, HEAD_DIM):
+        raise ValueError(
+            f"query must have {workspace.group_size} [128] heads per retrieval head"
+        )
+    args = native.LayerArgs()
+    _graph_args(
+        args,
+        csr=csr,
+        state=update_state,
+        sink_positions=sink_positions,
+        current_position=current_position,
+    )
+    _attention_args(
+        args,
+        query=query,
+        key=key,
+        value=value,
+        softmax_scale=softmax_scale,
+        lam=update_lam,
+        workspace=workspace,
+        update=update_workspace,
+        token_budget=segments.token_budget,
+    )
+    native.fill(
+        args,
+        device=device.index or 0,
+        batch=key.shape[0] if key.ndim == 4 else 1,
+        num_sink=segments.num_sink,
+        descriptor_capacity=segments.communities.shape[-1],
+        communities=native.pointer(segments.communities),
+        cumulative_ends=native.pointer(segments.cumulative_ends),
+        descriptor_counts=native.pointer(segments.descriptor_counts),
+        tile_descriptors=native.pointer(segments.tile_descriptors),
+        positions=None,
+        partials=None,
+        partial_topk=None,
+    )
+    native.call("ckv_segmented_attention_static", args, native.current_stream(device))
+    return workspace.output, workspace.lse, workspace.topk_scores, workspace.topk_positions
+
+
 def build_layer_args(
     *,
     query: torch.Tensor,
@@ -499,6 +572,7 @@ __all__ = [
     "score_and_select",
     "score_centroids",
     "segmented_attention",
+    "segmented_attention_static",
     "select_weighted_descriptors_auto",
     "select_weighted_descriptors_cluster",
     "select_weighted_descriptors_native",

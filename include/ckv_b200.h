@@ -155,6 +155,31 @@ int ckv_segmented_attention(const ckv_layer_args* args, void* cuda_stream);
 /* A1..A5 back to back: the whole per-layer decode transition. */
 int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream);
 
+/* Same operation and results as ckv_segmented_attention for callers that cannot
+ * allocate device memory (no counterpart in the reference: its Triton launcher
+ * always works on caller-allocated workspaces).  `positions`, `partials` and
+ * `partial_topk` of `args` are ignored; that scratch lives in a fixed array
+ * inside the library instead, CKV_STATIC_SCRATCH_BYTES (about 3.3 MB) on every
+ * GPU that loads the library, until the process exits.  Limits, checked up front
+ * (CKV_ERR_CAPACITY): batch * retrieval_heads <= CKV_STATIC_MAX_UNITS,
+ * token_budget <= CKV_STATIC_MAX_BUDGET, splits <= CKV_STATIC_MAX_SPLITS,
+ * group_size <= CKV_STATIC_MAX_GROUP.  Inputs, outputs and graph state are still
+ * the caller's.  The first call on a device looks up the array's device address;
+ * make that call before any stream capture begins.  All calls share the one
+ * array and it keeps the previous call's contents (every element that is read
+ * is rewritten first, nothing needs clearing): two calls whose kernels may
+ * overlap on the GPU - different streams, or different host threads - race. */
+#define CKV_STATIC_MAX_UNITS 64
+#define CKV_STATIC_MAX_BUDGET 4096
+#define CKV_STATIC_MAX_SPLITS 8
+#define CKV_STATIC_MAX_GROUP 8
+#define CKV_STATIC_SCRATCH_BYTES                                                        \
+  (4 * CKV_STATIC_MAX_UNITS * CKV_STATIC_MAX_BUDGET +                                   \
+   4 * CKV_STATIC_MAX_UNITS * CKV_STATIC_MAX_SPLITS * CKV_STATIC_MAX_GROUP *            \
+       CKV_PARTIAL_STRIDE +                                                             \
+   8 * CKV_STATIC_MAX_UNITS * CKV_STATIC_MAX_SPLITS * CKV_KAPPA)
+int ckv_segmented_attention_static(const ckv_layer_args* args, void* cuda_stream);
+
 /* Bytes of dynamic shared memory the attention kernel asks for (for diagnostics). */
 int ckv_attention_smem_bytes(int group_size);
 
