@@ -1,0 +1,135 @@
+"""Multi-GPU decomposition of the decode path: one process per GPU, NCCL for the exchange.
+
+The reference has no multi-GPU decode (its only cross-device traffic is
+``Tensor.to`` inside the partition workers, ``community_kv/graph/runtime.py:121-158``).
+Two decompositions follow from the independence of (sequence, layer, head) units:
+
+* **KV-head sharding** for whole-model decode: rank ``p`` of ``N`` owns KV heads
+  ``p*H/N .. (p+1)*H/N - 1`` with their cache slices, graph state and query
+  group; selection and the online update need no exchange at all, the head
+  outputs are all-gathered once per layer.
+* **Sequence sharding** for very long single-layer contexts: every rank scores
+  and selects identically (centroids and labels are replicated) but holds only
+  a contiguous slice of the K/V rows; it attends to the selected rows it owns
+  and the ranks combine their partial ``(max, sum, out)`` triples with the
+  log-sum-exp rule.
+
+Everything here is plain ``torch.distributed`` on tensors, so the logic also
+runs on CPU with the ``gloo`` backend (that is how it is tested without GPUs).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def head_shard(kv_heads: int, world: int, rank: int) -> range:
+    """KV heads owned by ``rank``: a contiguous block of ``kv_heads / world``."""
+
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError("rank must be in [0, world)")
+    if kv_heads % world:
+        raise ValueError("the number of ranks must divide the number of KV heads")
+    per_rank = kv_heads // world
+    return range(rank * per_rank, (rank + 1) * per_rank)
+
+
+def gather_head_outputs(
+    local: torch.Tensor,
+    *,
+    group: dist.ProcessGroup | None = None,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """All-gather ``local [B, Hq/N, D]`` into ``[B, Hq, D]`` in rank (= head) order."""
+
+    world = dist.get_world_size(group)
+    batch, heads, dim = local.shape
+    staged = (
+        out
+        if out is not None
+        else torch.empty((world, batch, heads, dim), dtype=local.dtype, device=local.device)
+    )
+    if staged.shape != (world, batch, heads, dim):
+        raise ValueError("out must have shape [world, B, Hq/N, D]")
+    dist.all_gather_into_tensor(staged.view(world * batch, heads, dim), local.contiguous(), group=group)
+    return staged.permute(1, 0, 2, 3).reshape(batch, world * heads, dim)
+
+
+def sequence_shard(length: int, world: int, rank: int) -> tuple[int, int]:
+    """Contiguous ``[begin, end)`` slice of the sequence held by ``rank``."""
+
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError("rank must be in [0, world)")
+    per_rank = -(-length // world)
+    return min(length, rank * per_rank), min(length, (rank + 1) * per_rank)
+
+
+def localize_positions(positions: torch.Tensor, begin: int, end: int) -> torch.Tensor:
+    """Map global cache rows to rows of this rank's slice; rows it does not hold become -1."""
+
+    owned = (positions >= begin) & (positions < end)
+    return torch.where(owned, positions - begin, torch.full_like(positions, -1))
+
+
+def combine_partials(
+    maxima: torch.Tensor,
+    sums: torch.Tensor,
+    accumulators: torch.Tensor,
+    *,
+    group: dist.ProcessGroup | None = None,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Exchange per-rank softmax partials and merge them.
+
+    ``maxima [H]``, ``sums [H]``, ``accumulators [H, D]`` (fp32, the accumulator
+    is not normalised).  One all-gather of the packed ``[H, D + 2]`` block per
+    rank; every rank then computes the same ``(output fp32 [H, D], lse [H])``.
+    A rank that holds none of the selected rows contributes ``max = -inf``.
+    """
+
+    world = dist.get_world_size(group)
+    packed = torch.cat((accumulators, maxima.unsqueeze(-1), sums.unsqueeze(-1)), dim=-1).contiguous()
+    gathered = torch.empty((world,) + packed.shape, dtype=packed.dtype, device=packed.device)
+    dist.all_gather_into_tensor(gathered.view((world * packed.shape[0],) + packed.shape[1:]), packed, group=group)
+    return merge_partials(gathered[..., -2], gathered[..., -1], gathered[..., :-2])
+
+
+def merge_partials(
+    maxima: torch.Tensor, sums: torch.Tensor, accumulators: torch.Tensor
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Log-sum-exp merge over the leading axis of stacked partials."""
+
+    top = maxima.amax(dim=0)
+    safe = torch.where(torch.isfinite(top), top, torch.zeros_like(top))
+    weight = torch.exp(maxima - safe)
+    weight = torch.where(torch.isfinite(maxima), weight, torch.zeros_like(weight))
+    denominator = (sums * weight).sum(dim=0)
+    output = (accumulators * weight.unsqueeze(-1)).sum(dim=0) / denominator.unsqueeze(-1)
+    return output, top + torch.log(denominator)
+
+
+def merge_topk(packed: torch.Tensor, k: int = 8) -> torch.Tensor:
+    """Global top-``k`` of per-rank packed (ordered score << 32 | ~position) candidates.
+
+    ``packed int64 [ranks, H, k]`` holding unsigned 64-bit keys; returns
+    ``int64 [H, k]`` in descending unsigned order.  Ties cannot occur between
+    ranks because a position lives on exactly one rank.
+    """
+
+    ranks, heads, width = packed.shape
+    flat = packed.permute(1, 0, 2).reshape(heads, ranks * width)
+    # order as unsigned: flip the sign bit, sort signed, flip back
+    flipped = flat ^ torch.tensor(-(2**63), dtype=torch.int64, device=packed.device)
+    top = torch.sort(flipped, dim=1, descending=True).values[:, :k]
+    return top ^ torch.tensor(-(2**63), dtype=torch.int64, device=packed.device)
+
+
+__all__ = [
+    "combine_partials",
+    "gather_head_outputs",
+    "head_shard",
+    "localize_positions",
+    "merge_partials",
+    "merge_topk",
+    "sequence_shard",
+]
