@@ -443,8 +443,7 @@ def run_b200(args: argparse.Namespace) -> None:
     step_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        finish(world, dist)
         return
     line = {
         "metric": METRIC,
@@ -497,8 +496,22 @@ def run_b200(args: argparse.Namespace) -> None:
         torch.cuda.empty_cache()
         line["cpu_baseline"] = cpu_baseline(args.cpu_seconds, args.context, args.layers)
     print(json.dumps(line), flush=True)
+    finish(world, dist)
+
+
+def finish(world: int, dist) -> None:
+    """Leave a multi-rank run without tearing NCCL down.
+
+    The process group is still referenced by the captured CUDA graph; destroying
+    it at this point can block for ever.  Everything has been measured and
+    printed, so the ranks meet at a barrier and exit directly.
+    """
+
     if world > 1:
-        dist.destroy_process_group()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main() -> None:
