@@ -9,6 +9,7 @@ cudaError_t launch_resolve(const ckv_layer_args& a, cudaStream_t stream);
 cudaError_t launch_attention(const ckv_layer_args& a, cudaStream_t stream);
 cudaError_t launch_merge_update(const ckv_layer_args& a, cudaStream_t stream);
 int attention_smem_bytes();
+cudaError_t launch_prefill(const ckv_prefill_args& a, cudaStream_t stream);
 
 namespace {
 
@@ -157,6 +158,40 @@ int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream) {
   status = ckv::launched(ckv::launch_attention(*args, stream));
   if (status != CKV_OK) return status;
   return ckv::launched(ckv::launch_merge_update(*args, stream));
+}
+
+int ckv_prefill_topk(const ckv_prefill_args* args, void* cuda_stream) {
+  if (args == nullptr) return CKV_ERR_NULL;
+  const ckv_prefill_args& a = *args;
+  if (a.batch <= 0 || a.seq_len <= 0 || a.query_heads <= 0 || a.kv_heads <= 0) return CKV_ERR_SHAPE;
+  if (a.query_heads % a.kv_heads) return CKV_ERR_SHAPE;
+  const int group = a.query_heads / a.kv_heads;
+  if (group != 1 && group != 2 && group != 4 && group != 8) return CKV_ERR_UNSUPPORTED;
+  if (a.mode < 0 || a.mode > 2 || a.num_sink < 0) return CKV_ERR_SHAPE;
+  if (a.kv_heads > 65535 || a.batch > 65535) return CKV_ERR_CAPACITY;
+  if (!a.query || !a.key || !a.value || !a.output || !a.lse) return CKV_ERR_NULL;
+  if (a.mode == 1) {
+    if (!a.topk_val || !a.topk_idx) return CKV_ERR_NULL;
+    if (a.seq_len > (1 << 17)) return CKV_ERR_CAPACITY;  /* 17-bit packed key index */
+  }
+  if (a.mode == 2) {
+    if (!a.candidates || !a.edge_idx || !a.edge_score) return CKV_ERR_NULL;
+    if (a.edges_per_row < 1 || a.edges_per_row > 16) return CKV_ERR_SHAPE;
+  }
+  const int64_t strides[] = {a.q_batch_stride, a.q_row_stride, a.q_head_stride, a.k_batch_stride,
+                             a.k_row_stride,   a.k_head_stride, a.v_batch_stride, a.v_row_stride,
+                             a.v_head_stride,  a.o_batch_stride, a.o_row_stride,  a.o_head_stride};
+  for (int64_t stride : strides) {
+    if (stride % 8) return CKV_ERR_ALIGN;
+  }
+  const void* pointers[] = {a.query, a.key, a.value, a.output};
+  for (const void* pointer : pointers) {
+    if (reinterpret_cast<uintptr_t>(pointer) % 16) return CKV_ERR_ALIGN;
+  }
+  int current = -1;
+  if (cudaGetDevice(&current) != cudaSuccess) return CKV_ERR_DEVICE;
+  if (current != a.device && cudaSetDevice(a.device) != cudaSuccess) return CKV_ERR_DEVICE;
+  return ckv::launched(ckv::launch_prefill(a, static_cast<cudaStream_t>(cuda_stream)));
 }
 
 }  // extern "C"

@@ -1,0 +1,726 @@
+// Prefill score-graph emission: causal attention that also reports, for every
+// query row, the keys it attends to most (sm_100a, tcgen05 tensor cores + TMEM).
+//
+// One CTA owns a 128-row tile: 128/G consecutive positions times the G query
+// heads of one KV head (the heads of a group share every K/V tile).  Per 128-key
+// block:
+//   S  = Q K^T   tcgen05.mma (M=128, N=128, K=16 x 8), operands in shared memory
+//                in the canonical un-swizzled 8x16-byte core-matrix layout,
+//                accumulator in tensor memory;
+//   each thread owns one row: it reads the row back with tcgen05.ld, applies the
+//   causal mask, feeds the neighbour-candidate queues, updates the running
+//   softmax and writes P (bf16) to shared memory;
+//   O' = P V     tcgen05.mma again (V is consumed N-major straight from the same
+//                [key][dim] staging layout), read back and folded into the
+//                thread's fp32 output row.
+// K/V tiles are staged with 16-byte cp.async; the next tile's fetch overlaps the
+// softmax and the second MMA.  Every wait on a tensor-core completion barrier is
+// bounded and reports through the status word.
+//
+// Neighbour candidates, mode 1 (the reference's rule, community-kv.patch
+// hopper/topk_warpselect.h): per row, four classes of columns (class = (j%8)/2)
+// each keep their six best packed candidates, key15 = clamp(rn((s+48)*256)) on
+// the raw Q.K score, packed = key15 << 17 | j; the row reports the eight largest
+// of the 24, probability = exp2(dequant(key15)*scale*log2e - lse*log2e).
+// Mode 2 (exact top-m per KV head): per position the group maximum of the scaled
+// scores is ranked; each of the G lanes of a position keeps the 16 best of the
+// columns j % G == lane, and a second kernel re-scores that short list in the
+// fixed fp32 order shared with the CPU oracle and emits the exact top-m.
+
+#include "ckv_device.cuh"
+
+namespace ckv {
+
+constexpr int kPfThreads = 128;
+constexpr int kPfRows = 128;
+constexpr int kPfKeys = 128;
+constexpr int kTileBytes = kPfRows * kHeadDim * 2;  // 32 KiB
+constexpr int kLocalK = 6;
+constexpr int kExactKeep = 16;
+constexpr uint32_t kBarrierPolls = 1u << 22;
+
+__device__ __forceinline__ uint32_t core_offset(int row, int chunk) {
+  // 8 rows x 16 bytes form one contiguous 128-byte core matrix; the 16 chunks
+  // of a row group are adjacent, row groups are 2048 bytes apart.
+  return static_cast<uint32_t>((row >> 3) * 2048 + chunk * 128 + (row & 7) * 16);
+}
+
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t leading_bytes,
+                                                    uint32_t stride_bytes) {
+  return static_cast<uint64_t>((address & 0x3ffffu) >> 4) |
+         (static_cast<uint64_t>(leading_bytes >> 4) << 16) |
+         (static_cast<uint64_t>(stride_bytes >> 4) << 32) | (1ull << 46);
+}
+
+// bf16 x bf16 -> fp32, M = 128, N = 128
+__device__ __forceinline__ uint32_t instruction_descriptor(bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+         ((kPfKeys >> 3) << 17) | ((kPfRows >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                     uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    v[i] = __uint_as_float(r[i]);
+  }
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+// Polls a completion barrier a bounded number of times.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t poll = 0; poll < kBarrierPolls; ++poll) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) {
+      return true;
+    }
+    if (poll > 64) {
+      __nanosleep(32);
+    }
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void async_proxy_fence() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t quantised_key(float raw) {
+  int key = __float2int_rn((raw + 48.0f) * 256.0f);
+  key = max(0, min(key, 32767));
+  return static_cast<uint32_t>(key);
+}
+
+template <int kDepth>
+__device__ __forceinline__ void queue_insert(uint32_t (&queue)[kDepth], uint32_t candidate) {
+#pragma unroll
+  for (int k = 0; k < kDepth; ++k) {
+    const uint32_t resident = queue[k];
+    queue[k] = max(candidate, resident);
+    candidate = min(candidate, resident);
+  }
+}
+
+// Returns the key that fell off the end (the candidate itself when it did not enter).
+__device__ __forceinline__ uint64_t queue_insert64(uint64_t (&queue)[kExactKeep], uint64_t candidate) {
+#pragma unroll
+  for (int k = 0; k < kExactKeep; ++k) {
+    const uint64_t resident = queue[k];
+    const bool greater = candidate > resident;
+    queue[k] = greater ? candidate : resident;
+    candidate = greater ? resident : candidate;
+  }
+  return candidate;
+}
+
+// kGroup: query heads per KV head (1, 2, 4, 8).  kMode: 0 attention only,
+// 1 reference top-8 per query head, 2 candidate lists for the exact top-m.
+template <int kGroup, int kMode>
+__global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefill_args a) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* s_q = smem;
+  uint8_t* s_k = smem + kTileBytes;
+  uint8_t* s_v = smem + 2 * kTileBytes;
+  uint8_t* s_p = smem + 3 * kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 4 * kTileBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+
+  constexpr int kPositions = kPfRows / kGroup;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int tile = blockIdx.x;
+  const int kv_head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int pos0 = tile * kPositions;
+  const int length = a.seq_len;
+  const int row_pos = pos0 + tid / kGroup;
+  const int row_head = kv_head * kGroup + tid % kGroup;
+  const bool row_live = row_pos < length;
+
+  const uint32_t bar_s = smem_u32(bars);
+  const uint32_t bar_o = smem_u32(bars + 1);
+  if (tid == 0) {
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(256)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+
+  const __nv_bfloat16* q_base = reinterpret_cast<const __nv_bfloat16*>(a.query) +
+                                batch * a.q_batch_stride;
+  const __nv_bfloat16* k_base = reinterpret_cast<const __nv_bfloat16*>(a.key) +
+                                batch * a.k_batch_stride + kv_head * a.k_head_stride;
+  const __nv_bfloat16* v_base = reinterpret_cast<const __nv_bfloat16*>(a.value) +
+                                batch * a.v_batch_stride + kv_head * a.v_head_stride;
+
+  // ---- stage Q once: row r = (position pos0 + r / G, head kv_head*G + r % G) ----
+  for (int index = tid; index < kPfRows * 16; index += kPfThreads) {
+    const int row = index >> 4;
+    const int chunk = index & 15;
+    const int pos = pos0 + row / kGroup;
+    const int head = kv_head * kGroup + row % kGroup;
+    const bool live = pos < length;
+    const __nv_bfloat16* src =
+        q_base + (live ? pos : 0) * a.q_row_stride + head * a.q_head_stride + chunk * 8;
+    cp_async16(smem_u32(s_q) + core_offset(row, chunk), src, live ? 16u : 0u);
+  }
+  auto stage_tile = [&](uint8_t* dst, const __nv_bfloat16* base, int64_t row_stride, int key0) {
+    for (int index = tid; index < kPfKeys * 16; index += kPfThreads) {
+      const int row = index >> 4;
+      const int chunk = index & 15;
+      const int key = key0 + row;
+      const bool live = key < length;
+      cp_async16(smem_u32(dst) + core_offset(row, chunk),
+                 base + (live ? key : 0) * row_stride + chunk * 8, live ? 16u : 0u);
+    }
+  };
+  const int last_pos = min(length, pos0 + kPositions) - 1;
+  const int blocks = last_pos / kPfKeys + 1;
+  stage_tile(s_k, k_base, a.k_row_stride, 0);
+  stage_tile(s_v, v_base, a.v_row_stride, 0);
+  cp_async_commit();
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_s = tmem + ((warp * 32u) << 16);
+  const uint32_t tmem_o = tmem_s + 128u;
+  const uint32_t idesc_qk = instruction_descriptor(false);
+  const uint32_t idesc_pv = instruction_descriptor(true);
+
+  float out[kHeadDim];
+#pragma unroll
+  for (int d = 0; d < kHeadDim; ++d) {
+    out[d] = 0.f;
+  }
+  float run_max = -INFINITY;  // of the raw (unscaled) scores
+  float run_sum = 0.f;
+  const float scale_log2 = a.softmax_scale * kLog2e;
+  uint32_t q32[4][kLocalK];
+  uint64_t q64[kExactKeep];
+  uint64_t dropped = 0ull;
+  if constexpr (kMode == 1) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int k = 0; k < kLocalK; ++k) {
+        q32[c][k] = 0u;
+      }
+    }
+  }
+  if constexpr (kMode == 2) {
+#pragma unroll
+    for (int k = 0; k < kExactKeep; ++k) {
+      q64[k] = 0ull;
+    }
+  }
+  bool failed = false;
+
+  for (int block = 0; block < blocks; ++block) {
+    const int key0 = block * kPfKeys;
+    const uint32_t parity = block & 1;
+    cp_async_wait<0>();
+    async_proxy_fence();
+    __syncthreads();
+    // ---- S = Q K^T ----
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t desc_q = smem_descriptor(smem_u32(s_q) + ks * 256, 128, 2048);
+        const uint64_t desc_k = smem_descriptor(smem_u32(s_k) + ks * 256, 128, 2048);
+        umma(tmem, desc_q, desc_k, idesc_qk, ks > 0 ? 1u : 0u);
+      }
+      umma_commit(bar_s);
+    }
+    if (!mbar_wait(bar_s, parity)) {
+      failed = true;
+    }
+    if (__syncthreads_or(failed ? 1 : 0)) {
+      failed = true;
+      break;
+    }
+    tc_fence_after();
+    // the K tile is free again: fetch the next one while this block is processed
+    if (block + 1 < blocks) {
+      stage_tile(s_k, k_base, a.k_row_stride, key0 + kPfKeys);
+    }
+    cp_async_commit();
+
+    // ---- pass A: row maximum of the masked raw scores, candidates ----
+    const int limit = row_live ? min(row_pos, length - 1) : -1;  // last visible key
+    float tile_max = -INFINITY;
+#pragma unroll 1
+    for (int chunk = 0; chunk < 4; ++chunk) {
+      float s[32];
+      tmem_load32(tmem_s + chunk * 32, s);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const int j = key0 + chunk * 32 + c;
+        const bool visible = j <= limit;
+        tile_max = fmaxf(tile_max, visible ? s[c] : -INFINITY);
+      }
+      if constexpr (kMode == 1) {
+        // skip the whole chunk when nothing in it can enter any class queue
+        float chunk_max = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int j = key0 + chunk * 32 + c;
+          chunk_max = fmaxf(chunk_max, (j <= limit && j >= a.num_sink) ? s[c] : -INFINITY);
+        }
+        const uint32_t floor_key =
+            min(min(q32[0][kLocalK - 1], q32[1][kLocalK - 1]),
+                min(q32[2][kLocalK - 1], q32[3][kLocalK - 1])) >> 17;
+        if (chunk_max > -INFINITY && quantised_key(chunk_max) >= floor_key) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int j = key0 + chunk * 32 + c;
+            if (j <= limit && j >= a.num_sink) {
+              const uint32_t candidate = (quantised_key(s[c]) << 17) | (static_cast<uint32_t>(j) & 0x1ffffu);
+              uint32_t(&queue)[kLocalK] = q32[(c & 7) >> 1];
+              if (candidate > queue[kLocalK - 1]) {
+                queue_insert<kLocalK>(queue, candidate);
+              }
+            }
+          }
+        }
+      }
+      if constexpr (kMode == 2) {
+        // group maximum of the scaled scores, shared by the G lanes of a position;
+        // lane h of the group ranks the columns j % G == h
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int j = key0 + chunk * 32 + c;
+          float v = (j <= limit && j >= a.num_sink) ? s[c] * a.softmax_scale : -INFINITY;
+#pragma unroll
+          for (int offset = 1; offset < kGroup; offset <<= 1) {
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+          }
+          if ((c % kGroup) == (tid % kGroup) && v > -INFINITY) {
+            const uint64_t candidate = (static_cast<uint64_t>(ordered_key32(v)) << 32) |
+                                       (0xffffffffu - static_cast<uint32_t>(j));
+            // keep the best key that was ever turned away: the second kernel needs it
+            // to prove that the short list is complete
+            const uint64_t lost =
+                candidate > q64[kExactKeep - 1] ? queue_insert64(q64, candidate) : candidate;
+            dropped = lost > dropped ? lost : dropped;
+          }
+        }
+      }
+    }
+    const float new_max = fmaxf(run_max, tile_max);
+    const float safe_max = new_max == -INFINITY ? 0.f : new_max;
+    const float corr = exp2f((run_max - safe_max) * scale_log2);
+    run_max = new_max;
+    run_sum *= corr;
+
+    // ---- pass B: probabilities -> shared memory (bf16, operand layout) ----
+#pragma unroll 1
+    for (int chunk = 0; chunk < 4; ++chunk) {
+      float s[32];
+      tmem_load32(tmem_s + chunk * 32, s);
+      uint32_t packed[16];
+#pragma unroll
+      for (int c = 0; c < 32; c += 2) {
+        const int j = key0 + chunk * 32 + c;
+        const float p0 = j <= limit ? exp2f((s[c] - safe_max) * scale_log2) : 0.f;
+        const float p1 = j + 1 <= limit ? exp2f((s[c + 1] - safe_max) * scale_log2) : 0.f;
+        run_sum += p0 + p1;
+        packed[c >> 1] = pack_bf16(p0, p1);
+      }
+#pragma unroll
+      for (int piece = 0; piece < 4; ++piece) {
+        *reinterpret_cast<uint4*>(s_p + core_offset(tid, chunk * 4 + piece)) =
+            make_uint4(packed[4 * piece], packed[4 * piece + 1], packed[4 * piece + 2],
+                       packed[4 * piece + 3]);
+      }
+    }
+    async_proxy_fence();
+    tc_fence_before();
+    __syncthreads();
+    // ---- O' = P V ----
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t desc_p = smem_descriptor(smem_u32(s_p) + ks * 256, 128, 2048);
+        const uint64_t desc_v = smem_descriptor(smem_u32(s_v) + ks * 4096, 2048, 128);
+        umma(tmem + 128u, desc_p, desc_v, idesc_pv, ks > 0 ? 1u : 0u);
+      }
+      umma_commit(bar_o);
+    }
+    if (!mbar_wait(bar_o, parity)) {
+      failed = true;
+    }
+    if (__syncthreads_or(failed ? 1 : 0)) {
+      failed = true;
+      break;
+    }
+    tc_fence_after();
+    if (block + 1 < blocks) {
+      stage_tile(s_v, v_base, a.v_row_stride, key0 + kPfKeys);
+    }
+    cp_async_commit();
+#pragma unroll
+    for (int chunk = 0; chunk < 4; ++chunk) {
+      float o[32];
+      tmem_load32(tmem_o + chunk * 32, o);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        out[chunk * 32 + c] = out[chunk * 32 + c] * corr + o[c];
+      }
+    }
+    tc_fence_before();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256)
+                 : "memory");
+  }
+  if (failed) {
+    if (tid == 0 && a.status != nullptr) {
+      atomicOr(a.status, CKV_DEV_WAIT_TIMEOUT);
+    }
+    return;
+  }
+  if (!row_live) {
+    return;
+  }
+
+  // ---- epilogue: normalise, write the output row, the lse and the edges ----
+  const float inverse = 1.f / run_sum;
+  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.output) + batch * a.o_batch_stride +
+                       static_cast<int64_t>(row_pos) * a.o_row_stride + row_head * a.o_head_stride;
+#pragma unroll
+  for (int d = 0; d < kHeadDim; d += 8) {
+    uint4 v;
+    v.x = pack_bf16(out[d] * inverse, out[d + 1] * inverse);
+    v.y = pack_bf16(out[d + 2] * inverse, out[d + 3] * inverse);
+    v.z = pack_bf16(out[d + 4] * inverse, out[d + 5] * inverse);
+    v.w = pack_bf16(out[d + 6] * inverse, out[d + 7] * inverse);
+    *reinterpret_cast<uint4*>(dst + d) = v;
+  }
+  const float lse = run_max * a.softmax_scale + logf(run_sum);
+  const int64_t heads_total = static_cast<int64_t>(gridDim.y) * kGroup;
+  a.lse[(batch * heads_total + row_head) * length + row_pos] = lse;
+
+  if constexpr (kMode == 1) {
+    const int skip = a.num_sink + kKappa - 1;
+    if (row_pos >= skip) {
+      // merge the four sorted class queues: eight rounds of "largest head wins"
+      int cursor[4] = {0, 0, 0, 0};
+      const int64_t base =
+          ((batch * heads_total + row_head) * (length - skip) + (row_pos - skip)) * kKappa;
+      const float lse_log2 = lse * kLog2e;
+#pragma unroll
+      for (int rank = 0; rank < kKappa; ++rank) {
+        uint32_t best = 0u;
+        int winner = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t head = 0u;
+#pragma unroll
+          for (int k = 0; k < kLocalK; ++k) {
+            head = cursor[c] == k ? q32[c][k] : head;
+          }
+          if (head > best) {
+            best = head;
+            winner = c;
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          cursor[c] += (c == winner) ? 1 : 0;
+        }
+        const float dequant = static_cast<float>(best >> 17) / 256.0f - 48.0f;
+        a.topk_val[base + rank] = exp2f(dequant * scale_log2 - lse_log2);
+        a.topk_idx[base + rank] = static_cast<int32_t>(best & 0x1ffffu);
+      }
+    }
+  }
+  if constexpr (kMode == 2) {
+    // [batch, kv head, position, G lanes, 16 kept + best dropped] for the second kernel
+    uint64_t* list = a.candidates +
+                     (((static_cast<int64_t>(batch) * gridDim.y + kv_head) * length + row_pos) * kGroup +
+                      tid % kGroup) * (kExactKeep + 1);
+#pragma unroll
+    for (int k = 0; k < kExactKeep; ++k) {
+      list[k] = q64[k];
+    }
+    list[kExactKeep] = dropped;
+  }
+}
+
+// ---- exact top-m from the candidate lists (mode 2, second kernel) ----
+// One warp per (batch, KV head, position).  The G x 16 candidate keys are
+// re-scored as max over the group of scale * (q . k) in the fixed fp32 order
+// and ranked by (score descending, key index ascending).  A row is flagged when
+// a key that was turned away could still belong to the top-m: the best
+// approximate score among the dropped keys is within `slack` of the exact m-th.
+__global__ void __launch_bounds__(128) exact_edges_kernel(const ckv_prefill_args a, int group) {
+  const int warps_per_block = 4;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * warps_per_block + warp;
+  const int length = a.seq_len;
+  const int skip = a.num_sink + a.edges_per_row - 1;
+  const int rows = length - skip;
+  const int64_t total = static_cast<int64_t>(a.batch) * a.kv_heads * rows;
+  if (item >= total || rows <= 0) {
+    return;
+  }
+  const int pos = skip + static_cast<int>(item % rows);
+  const int kv_head = static_cast<int>((item / rows) % a.kv_heads);
+  const int batch = static_cast<int>(item / (static_cast<int64_t>(rows) * a.kv_heads));
+  const uint64_t* list = a.candidates +
+                         ((static_cast<int64_t>(batch) * a.kv_heads + kv_head) * length + pos) *
+                             group * (kExactKeep + 1);
+  const __nv_bfloat16* q_base = reinterpret_cast<const __nv_bfloat16*>(a.query) +
+                                batch * a.q_batch_stride + static_cast<int64_t>(pos) * a.q_row_stride +
+                                kv_head * group * a.q_head_stride;
+  const __nv_bfloat16* k_base = reinterpret_cast<const __nv_bfloat16*>(a.key) +
+                                batch * a.k_batch_stride + kv_head * a.k_head_stride;
+  const int candidates = group * kExactKeep;  // <= 128
+  uint64_t best_key[4];
+  float best_dropped = -INFINITY;  // best approximate score among the keys turned away
+  if (lane < group) {
+    const uint64_t lost = list[lane * (kExactKeep + 1) + kExactKeep];
+    if (lost != 0ull) {
+      best_dropped = key32_to_float(static_cast<uint32_t>(lost >> 32));
+    }
+  }
+#pragma unroll
+  for (int slot = 0; slot < 4; ++slot) {
+    best_key[slot] = 0ull;
+    const int index = lane + 32 * slot;
+    if (index >= candidates) {
+      continue;
+    }
+    const uint64_t packed = list[(index / kExactKeep) * (kExactKeep + 1) + index % kExactKeep];
+    if (packed == 0ull) {
+      continue;
+    }
+    const int j = static_cast<int>(0xffffffffu - static_cast<uint32_t>(packed));
+    const __nv_bfloat16* k_row = k_base + static_cast<int64_t>(j) * a.k_row_stride;
+    float score = -INFINITY;
+    for (int g = 0; g < group; ++g) {
+      const __nv_bfloat16* q_row = q_base + g * a.q_head_stride;
+      float part[8];
+#pragma unroll
+      for (int piece = 0; piece < 8; ++piece) {
+        float acc = 0.f;
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          const uint32_t kk = *reinterpret_cast<const uint32_t*>(k_row + piece * 16 + e);
+          const uint32_t qq = *reinterpret_cast<const uint32_t*>(q_row + piece * 16 + e);
+          acc = __fmaf_rn(bf16_lo(kk), bf16_lo(qq), acc);
+          acc = __fmaf_rn(bf16_hi(kk), bf16_hi(qq), acc);
+        }
+        part[piece] = acc;
+      }
+      const float even = __fadd_rn(__fadd_rn(part[0], part[4]), __fadd_rn(part[2], part[6]));
+      const float odd = __fadd_rn(__fadd_rn(part[1], part[5]), __fadd_rn(part[3], part[7]));
+      score = fmaxf(score, __fmul_rn(__fadd_rn(even, odd), a.softmax_scale));
+    }
+    best_key[slot] = (static_cast<uint64_t>(ordered_key32(score)) << 32) |
+                     (0xffffffffu - static_cast<uint32_t>(j));
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    best_dropped = fmaxf(best_dropped, __shfl_xor_sync(0xffffffffu, best_dropped, offset));
+  }
+  const int64_t out_base = ((static_cast<int64_t>(batch) * a.kv_heads + kv_head) * rows + (pos - skip)) *
+                           a.edges_per_row;
+  float last_score = 0.f;
+  for (int rank = 0; rank < a.edges_per_row; ++rank) {
+    uint64_t local = 0ull;
+#pragma unroll
+    for (int slot = 0; slot < 4; ++slot) {
+      local = best_key[slot] > local ? best_key[slot] : local;
+    }
+    const uint64_t winner = warp_max_u64(local);
+    if (winner != 0ull) {
+#pragma unroll
+      for (int slot = 0; slot < 4; ++slot) {
+        best_key[slot] = best_key[slot] == winner ? 0ull : best_key[slot];
+      }
+    }
+    last_score = key32_to_float(static_cast<uint32_t>(winner >> 32));
+    if (lane == 0) {
+      a.edge_idx[out_base + rank] =
+          winner == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(winner));
+      a.edge_score[out_base + rank] = winner == 0ull ? -INFINITY : last_score;
+    }
+  }
+  if (lane == 0 && a.edge_flags != nullptr) {
+    a.edge_flags[(static_cast<int64_t>(batch) * a.kv_heads + kv_head) * rows + (pos - skip)] =
+        (best_dropped + a.exact_slack >= last_score) ? 1 : 0;
+  }
+}
+
+// Brute-force exact top-m of flagged rows (rare): one CTA per (batch, kv head, row).
+__global__ void __launch_bounds__(256) exact_rescan_kernel(const ckv_prefill_args a, int group) {
+  __shared__ uint64_t s_best[256];
+  const int length = a.seq_len;
+  const int skip = a.num_sink + a.edges_per_row - 1;
+  const int rows = length - skip;
+  const int64_t item = blockIdx.x;
+  if (a.edge_flags[item] == 0) {
+    return;
+  }
+  const int pos = skip + static_cast<int>(item % rows);
+  const int kv_head = static_cast<int>((item / rows) % a.kv_heads);
+  const int batch = static_cast<int>(item / (static_cast<int64_t>(rows) * a.kv_heads));
+  const __nv_bfloat16* q_base = reinterpret_cast<const __nv_bfloat16*>(a.query) +
+                                batch * a.q_batch_stride + static_cast<int64_t>(pos) * a.q_row_stride +
+                                kv_head * group * a.q_head_stride;
+  const __nv_bfloat16* k_base = reinterpret_cast<const __nv_bfloat16*>(a.key) +
+                                batch * a.k_batch_stride + kv_head * a.k_head_stride;
+  const int64_t out_base = item * a.edges_per_row;
+  uint64_t previous = ~0ull;
+  for (int rank = 0; rank < a.edges_per_row; ++rank) {
+    uint64_t local = 0ull;
+    for (int j = a.num_sink + threadIdx.x; j <= pos; j += 256) {
+      const __nv_bfloat16* k_row = k_base + static_cast<int64_t>(j) * a.k_row_stride;
+      float score = -INFINITY;
+      for (int g = 0; g < group; ++g) {
+        const __nv_bfloat16* q_row = q_base + g * a.q_head_stride;
+        float part[8];
+        for (int piece = 0; piece < 8; ++piece) {
+          float acc = 0.f;
+          for (int e = 0; e < 16; ++e) {
+            acc = __fmaf_rn(__bfloat162float(k_row[piece * 16 + e]),
+                            __bfloat162float(q_row[piece * 16 + e]), acc);
+          }
+          part[piece] = acc;
+        }
+        const float even = __fadd_rn(__fadd_rn(part[0], part[4]), __fadd_rn(part[2], part[6]));
+        const float odd = __fadd_rn(__fadd_rn(part[1], part[5]), __fadd_rn(part[3], part[7]));
+        score = fmaxf(score, __fmul_rn(__fadd_rn(even, odd), a.softmax_scale));
+      }
+      const uint64_t packed = (static_cast<uint64_t>(ordered_key32(score)) << 32) |
+                              (0xffffffffu - static_cast<uint32_t>(j));
+      if (packed < previous && packed > local) {
+        local = packed;
+      }
+    }
+    s_best[threadIdx.x] = local;
+    __syncthreads();
+    for (int stride = 128; stride > 0; stride >>= 1) {
+      if (threadIdx.x < stride && s_best[threadIdx.x + stride] > s_best[threadIdx.x]) {
+        s_best[threadIdx.x] = s_best[threadIdx.x + stride];
+      }
+      __syncthreads();
+    }
+    previous = s_best[0];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      a.edge_idx[out_base + rank] =
+          previous == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(previous));
+      a.edge_score[out_base + rank] =
+          previous == 0ull ? -INFINITY : key32_to_float(static_cast<uint32_t>(previous >> 32));
+    }
+  }
+}
+
+namespace {
+
+template <int kGroup>
+cudaError_t launch_for_group(const ckv_prefill_args& a, cudaStream_t stream) {
+  constexpr int kSmem = 4 * kTileBytes + 64;
+  const dim3 grid((a.seq_len + kPfRows / kGroup - 1) / (kPfRows / kGroup), a.kv_heads, a.batch);
+  auto run = [&](auto kernel) -> cudaError_t {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (err != cudaSuccess) return err;
+    kernel<<<grid, kPfThreads, kSmem, stream>>>(a);
+    return cudaGetLastError();
+  };
+  if (a.mode == 0) return run(prefill_kernel<kGroup, 0>);
+  if (a.mode == 1) return run(prefill_kernel<kGroup, 1>);
+  return run(prefill_kernel<kGroup, 2>);
+}
+
+}  // namespace
+
+cudaError_t launch_prefill(const ckv_prefill_args& a, cudaStream_t stream) {
+  const int group = a.query_heads / a.kv_heads;
+  cudaError_t err;
+  switch (group) {
+    case 1: err = launch_for_group<1>(a, stream); break;
+    case 2: err = launch_for_group<2>(a, stream); break;
+    case 4: err = launch_for_group<4>(a, stream); break;
+    case 8: err = launch_for_group<8>(a, stream); break;
+    default: return cudaErrorInvalidValue;
+  }
+  if (err != cudaSuccess || a.mode != 2) {
+    return err;
+  }
+  const int rows = a.seq_len - (a.num_sink + a.edges_per_row - 1);
+  if (rows <= 0) {
+    return cudaSuccess;
+  }
+  const int64_t items = static_cast<int64_t>(a.batch) * a.kv_heads * rows;
+  exact_edges_kernel<<<static_cast<unsigned>((items + 3) / 4), 128, 0, stream>>>(a, group);
+  err = cudaGetLastError();
+  if (err != cudaSuccess || a.edge_flags == nullptr) {
+    return err;
+  }
+  exact_rescan_kernel<<<static_cast<unsigned>(items), 256, 0, stream>>>(a, group);
+  return cudaGetLastError();
+}
+
+}  // namespace ckv

@@ -96,6 +96,47 @@ class LayerArgs(ctypes.Structure):
     ]
 
 
+class PrefillArgs(ctypes.Structure):
+    """Field-for-field mirror of ``struct ckv_prefill_args``."""
+
+    _fields_ = [
+        ("device", _i32),
+        ("batch", _i32),
+        ("seq_len", _i32),
+        ("query_heads", _i32),
+        ("kv_heads", _i32),
+        ("num_sink", _i32),
+        ("mode", _i32),
+        ("edges_per_row", _i32),
+        ("softmax_scale", _f32),
+        ("exact_slack", _f32),
+        ("q_batch_stride", _i64),
+        ("q_row_stride", _i64),
+        ("q_head_stride", _i64),
+        ("k_batch_stride", _i64),
+        ("k_row_stride", _i64),
+        ("k_head_stride", _i64),
+        ("v_batch_stride", _i64),
+        ("v_row_stride", _i64),
+        ("v_head_stride", _i64),
+        ("o_batch_stride", _i64),
+        ("o_row_stride", _i64),
+        ("o_head_stride", _i64),
+        ("query", _ptr),
+        ("key", _ptr),
+        ("value", _ptr),
+        ("output", _ptr),
+        ("lse", _ptr),
+        ("topk_val", _ptr),
+        ("topk_idx", _ptr),
+        ("candidates", _ptr),
+        ("edge_idx", _ptr),
+        ("edge_score", _ptr),
+        ("edge_flags", _ptr),
+        ("status", _ptr),
+    ]
+
+
 FLAG_SKIP_UPDATE = 1
 STATIC_MAX_UNITS = 64
 STATIC_MAX_BUDGET = 4096
@@ -114,6 +155,7 @@ ENTRY_POINTS = (
     "ckv_decode_layer",
     "ckv_attention_smem_bytes",
     "ckv_segmented_attention_static",
+    "ckv_prefill_topk",
 )
 
 
@@ -144,6 +186,8 @@ def library() -> ctypes.CDLL:
         function = getattr(lib, name)
         function.restype = ctypes.c_int
         function.argtypes = [ctypes.POINTER(LayerArgs), ctypes.c_void_p]
+    lib.ckv_prefill_topk.restype = ctypes.c_int
+    lib.ckv_prefill_topk.argtypes = [ctypes.POINTER(PrefillArgs), ctypes.c_void_p]
     return lib
 
 
@@ -157,14 +201,14 @@ def current_stream(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def call(name: str, args: LayerArgs, stream: int) -> None:
+def call(name: str, args: ctypes.Structure, stream: int) -> None:
     status = getattr(library(), name)(ctypes.byref(args), ctypes.c_void_p(stream))
     if status != 0:
         message = library().ckv_status_string(status).decode()
         raise NativeError(f"{name} failed with status {status}: {message}")
 
 
-def fill(args: LayerArgs, **values: Any) -> LayerArgs:
+def fill(args: ctypes.Structure, **values: Any) -> ctypes.Structure:
     for key, value in values.items():
         setattr(args, key, value)
     return args
@@ -178,6 +222,7 @@ __all__ = [
     "LayerArgs",
     "NativeError",
     "PARTIAL_STRIDE",
+    "PrefillArgs",
     "call",
     "current_stream",
     "fill",

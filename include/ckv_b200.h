@@ -136,6 +136,39 @@ typedef struct ckv_layer_args {
   uint32_t* status;            /* one device word, may be null */
 } ckv_layer_args;
 
+/* Arguments of the prefill score-graph kernel.  Q, K, V, O are bf16 with a
+ * contiguous last dimension of 128 and element strides for batch, sequence row
+ * and head; the reference passes [B, S, H, 128] tensors. */
+typedef struct ckv_prefill_args {
+  int32_t device;
+  int32_t batch;
+  int32_t seq_len;
+  int32_t query_heads;
+  int32_t kv_heads;        /* query_heads / kv_heads must be 1, 2, 4 or 8 */
+  int32_t num_sink;        /* keys below this index are never reported as neighbours */
+  int32_t mode;            /* 0 attention only; 1 reference top-8 per query head;
+                              2 exact top-`edges_per_row` per KV head */
+  int32_t edges_per_row;   /* mode 2: 1..16 */
+  float softmax_scale;
+  float exact_slack;       /* mode 2: margin (in scaled-score units) for the completeness check */
+  int64_t q_batch_stride, q_row_stride, q_head_stride;
+  int64_t k_batch_stride, k_row_stride, k_head_stride;
+  int64_t v_batch_stride, v_row_stride, v_head_stride;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  const void* query;
+  const void* key;
+  const void* value;
+  void* output;            /* bf16, strides above */
+  float* lse;              /* [batch, query_heads, seq_len] natural-log sum-exp */
+  float* topk_val;         /* mode 1: [batch, query_heads, seq_len - (num_sink+7), 8] */
+  int32_t* topk_idx;       /* mode 1: same shape */
+  uint64_t* candidates;    /* mode 2 scratch: [batch, kv_heads, seq_len, group, 17] */
+  int32_t* edge_idx;       /* mode 2: [batch, kv_heads, seq_len - (num_sink+m-1), m] */
+  float* edge_score;       /* mode 2: same shape, scaled scores */
+  int32_t* edge_flags;     /* mode 2, optional: [batch, kv_heads, rows]; 1 = row was re-scanned */
+  uint32_t* status;        /* one device word, may be null */
+} ckv_prefill_args;
+
 /* Library version: major*10000 + minor*100 + patch. */
 int ckv_version(void);
 const char* ckv_status_string(int status);
@@ -154,6 +187,11 @@ int ckv_segmented_attention(const ckv_layer_args* args, void* cuda_stream);
 
 /* A1..A5 back to back: the whole per-layer decode transition. */
 int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream);
+
+/* P1.  Causal attention (output + lse) that also emits each row's strongest
+ * Q.K neighbours: the reference's top-8 rule (mode 1) or exact top-m per KV head
+ * (mode 2). */
+int ckv_prefill_topk(const ckv_prefill_args* args, void* cuda_stream);
 
 /* Same operation and results as ckv_segmented_attention for callers that cannot
  * allocate device memory (no counterpart in the reference: its Triton launcher

@@ -1,0 +1,123 @@
+"""The prefill score-graph kernel (tcgen05) against the CPU oracle, through the C ABI."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from community_kv_b200.prefill import (
+    prefill_attention,
+    prefill_attention_edges,
+    prefill_attention_topk,
+)
+from oracle import prefill_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+SCALE = 128 ** -0.5
+
+
+def _inputs(seed, length, heads, kv_heads, clusters=16, batch=1):
+    generator = torch.Generator().manual_seed(seed)
+    centres = torch.randn((kv_heads, clusters, 128), generator=generator)
+    labels = torch.randint(0, clusters, (batch, length, kv_heads), generator=generator)
+    key = centres[torch.arange(kv_heads).view(1, 1, -1), labels] + 0.3 * torch.randn(
+        (batch, length, kv_heads, 128), generator=generator
+    )
+    value = torch.randn((batch, length, kv_heads, 128), generator=generator)
+    query = torch.randn((batch, length, heads, 128), generator=generator)
+    # planted structure: queries lean towards their own cluster centre
+    query = query + 0.5 * key.repeat_interleave(heads // kv_heads, dim=2)
+    return (query.to(torch.bfloat16), (key / 128**0.5).to(torch.bfloat16) * 4, (value / 128**0.5).to(torch.bfloat16))
+
+
+def _check_attention(out, lse, q, k, v, want_out, want_lse):
+    diff = (out.float().cpu().numpy() - want_out)
+    assert np.abs(diff).max() <= 2e-2, np.abs(diff).max()
+    assert np.abs(diff).mean() <= 1e-3
+    np.testing.assert_allclose(lse.cpu().numpy(), want_lse, atol=2e-3, rtol=0)
+
+
+@pytest.mark.parametrize("length,heads,kv_heads", [(256, 4, 1), (300, 8, 2), (640, 2, 2), (200, 8, 1), (512, 2, 1)])
+def test_attention_output_and_lse(length, heads, kv_heads):
+    q, k, v = _inputs(1, length, heads, kv_heads)
+    out, lse = prefill_attention(q.cuda(), k.cuda(), v.cuda(), softmax_scale=SCALE)
+    torch.cuda.synchronize()
+    want_out, want_lse, _ = oracle.causal_attention(q[0].float().numpy(), k[0].float().numpy(), v[0].float().numpy(), SCALE)
+    _check_attention(out[0], lse[0], q, k, v, want_out, want_lse)
+
+
+def test_reference_topk_rule():
+    length, heads, kv_heads, sinks = 640, 4, 1, 10
+    q, k, v = _inputs(2, length, heads, kv_heads)
+    out, lse, _, _, val, idx = prefill_attention_topk(q.cuda(), k.cuda(), v.cuda(), softmax_scale=SCALE, num_sink=sinks)
+    torch.cuda.synchronize()
+    assert val.shape == (1, heads, length - sinks - 7, 8) and idx.dtype == torch.int32
+    want_out, want_lse, raw = oracle.causal_attention(q[0].float().numpy(), k[0].float().numpy(), v[0].float().numpy(), SCALE)
+    _check_attention(out[0], lse[0], q, k, v, want_out, want_lse)
+    got_idx = idx[0].cpu().numpy()
+    got_val = val[0].cpu().numpy()
+    exact_rows = 0
+    total_rows = 0
+    for head in range(heads):
+        want_val, want_idx, want_key = oracle.reference_topk(raw[head], want_lse[head], SCALE, sinks)
+        keys = oracle.quantised_keys(raw[head])
+        for row in range(want_idx.shape[0]):
+            position = row + sinks + 7
+            total_rows += 1
+            mine = got_idx[head, row]
+            assert mine.min() >= sinks and mine.max() <= position
+            assert len(set(mine.tolist())) == 8
+            if np.array_equal(mine, want_idx[row]):
+                exact_rows += 1
+                np.testing.assert_allclose(got_val[head, row], want_val[row], rtol=2e-2, atol=1e-9)
+                continue
+            # the tensor-core score may land on the other side of a quantisation step:
+            # every disagreement must sit within one step of the cut
+            floor_key = want_key[row].min()
+            for j in set(mine.tolist()) ^ set(want_idx[row].tolist()):
+                assert abs(int(keys[position, j]) - int(floor_key)) <= 1, (head, row, j)
+    assert exact_rows / total_rows > 0.97, exact_rows / total_rows
+
+
+@pytest.mark.parametrize("length,heads,kv_heads,edges", [(384, 4, 1, 16), (300, 8, 2, 8), (260, 2, 2, 16)])
+def test_exact_edges_are_bit_exact(length, heads, kv_heads, edges):
+    sinks = 4
+    q, k, v = _inputs(3, length, heads, kv_heads)
+    out, lse, edge_idx, edge_score, flags = prefill_attention_edges(
+        q.cuda(), k.cuda(), v.cuda(), softmax_scale=SCALE, num_sink=sinks, edges_per_row=edges
+    )
+    torch.cuda.synchronize()
+    want_idx, want_score = oracle.exact_edges(q[0].float().numpy(), k[0].float().numpy(), SCALE, sinks, edges)
+    assert np.array_equal(edge_idx[0].cpu().numpy(), want_idx)
+    assert np.array_equal(edge_score[0].cpu().numpy().view(np.uint32), want_score.view(np.uint32))
+    want_out, want_lse, _ = oracle.causal_attention(q[0].float().numpy(), k[0].float().numpy(), v[0].float().numpy(), SCALE)
+    _check_attention(out[0], lse[0], q, k, v, want_out, want_lse)
+    assert int(flags.sum()) <= flags.numel() // 20
+
+
+def test_exact_edges_rescan_path():
+    """A huge slack flags every row: the brute-force re-scan must give the same exact answer."""
+
+    length, heads, kv_heads, edges, sinks = 200, 4, 1, 16, 3
+    q, k, v = _inputs(4, length, heads, kv_heads)
+    _, _, edge_idx, edge_score, flags = prefill_attention_edges(
+        q.cuda(), k.cuda(), v.cuda(), softmax_scale=SCALE, num_sink=sinks, edges_per_row=edges, exact_slack=1e9
+    )
+    torch.cuda.synchronize()
+    want_idx, want_score = oracle.exact_edges(q[0].float().numpy(), k[0].float().numpy(), SCALE, sinks, edges)
+    assert np.array_equal(edge_idx[0].cpu().numpy(), want_idx)
+    assert np.array_equal(edge_score[0].cpu().numpy().view(np.uint32), want_score.view(np.uint32))
+
+
+def test_batch_and_validation():
+    q, k, v = _inputs(5, 192, 4, 2, batch=2)
+    out, lse = prefill_attention(q.cuda(), k.cuda(), v.cuda(), softmax_scale=SCALE)
+    torch.cuda.synchronize()
+    for b in range(2):
+        want_out, want_lse, _ = oracle.causal_attention(q[b].float().numpy(), k[b].float().numpy(), v[b].float().numpy(), SCALE)
+        _check_attention(out[b], lse[b], q, k, v, want_out, want_lse)
+    with pytest.raises(TypeError):
+        prefill_attention(q.cuda().float(), k.cuda(), v.cuda(), softmax_scale=SCALE)
+    with pytest.raises(ValueError):
+        prefill_attention(q.cuda()[:, :, :3], k.cuda(), v.cuda(), softmax_scale=SCALE)

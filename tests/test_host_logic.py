@@ -277,6 +277,28 @@ def test_ctypes_struct_matches_the_header(tmp_path):
         assert getattr(native.LayerArgs, name).offset == offset, name
 
 
+def test_prefill_struct_matches_the_header(tmp_path):
+    source = tmp_path / "layout.c"
+    fields = [name for name, _ in native.PrefillArgs._fields_]
+    probes = "\n".join(f'  printf("%zu\\n", offsetof(ckv_prefill_args, {name}));' for name in fields)
+    source.write_text(
+        '#include <stdio.h>\n#include <stddef.h>\n#include "ckv_b200.h"\nint main(void) {\n'
+        '  printf("%zu\\n", sizeof(ckv_prefill_args));\n' + probes + "\n  return 0;\n}\n"
+    )
+    binary = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", str(ROOT / "include"), str(source), "-o", str(binary)], check=True)
+    numbers = [int(x) for x in subprocess.run([str(binary)], capture_output=True, text=True, check=True).stdout.split()]
+    assert numbers[0] == ctypes.sizeof(native.PrefillArgs)
+    for name, offset in zip(fields, numbers[1:]):
+        assert getattr(native.PrefillArgs, name).offset == offset, name
+    lib = native.library()
+    args = native.PrefillArgs()
+    assert lib.ckv_prefill_topk(None, None) == -1
+    assert lib.ckv_prefill_topk(ctypes.byref(args), None) == -2
+    native.fill(args, batch=1, seq_len=64, query_heads=6, kv_heads=2)
+    assert lib.ckv_prefill_topk(ctypes.byref(args), None) == -6   # group size 3 is not supported
+
+
 def test_argument_errors_come_back_as_status_codes():
     """Host-side validation only: no kernel is launched for a rejected argument block."""
 
