@@ -60,6 +60,9 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--cpu-seconds", type=float, default=15.0)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--workload", choices=["decode", "prefill"], default="decode",
+                        help="prefill: the score-graph emission kernel at S=16384 (a second, separate line)")
+    parser.add_argument("--prefill-length", type=int, default=16384)
     return parser.parse_args()
 
 
@@ -514,8 +517,89 @@ def finish(world: int, dist) -> None:
         os._exit(0)
 
 
+def run_prefill(args: argparse.Namespace) -> None:
+    """Prefill score-graph emission (BASELINE config 2): one layer, 32/8 heads, causal, planted clusters."""
+
+    import torch
+
+    from community_kv_b200.prefill import prefill_attention, prefill_attention_edges, prefill_attention_topk
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    length = args.prefill_length
+    generator = torch.Generator(device=device).manual_seed(args.seed)
+    centres = torch.randn((KV_HEADS, 256, HEAD_DIM), generator=generator, device=device)
+    labels = torch.randint(0, 256, (length, KV_HEADS), generator=generator, device=device)
+    key = centres[torch.arange(KV_HEADS, device=device).view(1, -1), labels]
+    key = ((key + 0.3 * torch.randn(key.shape, generator=generator, device=device)) * SCALE).to(torch.bfloat16)[None]
+    value = (torch.randn((1, length, KV_HEADS, HEAD_DIM), generator=generator, device=device) * SCALE).to(torch.bfloat16)
+    query = torch.randn((1, length, QUERY_HEADS, HEAD_DIM), generator=generator, device=device).to(torch.bfloat16)
+    flops = 2.0 * length * length * HEAD_DIM * QUERY_HEADS  # causal Q.K^T + P.V
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_path.read_text())["bf16_tflops"]) if peaks_path.exists() else 1590.0
+    variants = {
+        "attention_only": lambda: prefill_attention(query, key, value, softmax_scale=SCALE),
+        "reference_top8": lambda: prefill_attention_topk(query, key, value, softmax_scale=SCALE, num_sink=NUM_SINK),
+        "exact_top16_per_kv_head": lambda: prefill_attention_edges(
+            query, key, value, softmax_scale=SCALE, num_sink=NUM_SINK, edges_per_row=16),
+    }
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    timings = {}
+    rescanned = None
+    for name, run in variants.items():
+        for _ in range(max(args.warmup, 3)):
+            result = run()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(args.steps):
+            result = run()
+        end.record()
+        torch.cuda.synchronize()
+        timings[name] = begin.elapsed_time(end) / args.steps
+        if name == "exact_top16_per_kv_head":
+            rescanned = int(result[4].sum())
+    clocks = sampler.stop()
+    headline = timings["exact_top16_per_kv_head"]
+    line = {
+        "metric": "prefill score-graph emission, ms per layer (S=%d, 32/8 heads, top-16 edges per KV head)" % length,
+        "value": headline,
+        "unit": "ms",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": max(args.warmup, 3),
+        "ms_per_step": headline,
+        "higher_is_better": False,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "prefill score-graph emission: 1 layer, 32 Q / 8 KV heads, head_dim 128, "
+                               f"S={length}, causal, 256 planted key clusters", "l2": "each step streams 2*S*8*256 B of K/V per query tile"},
+        "variants_ms": timings,
+        "rows_rescanned": rescanned,
+        "roofline": {
+            "kernel": "prefill_kernel (tcgen05 Q.K^T and P.V)",
+            "bound": "tensor",
+            "achieved": flops / (timings["attention_only"] * 1e-3) / 1e12,
+            "achieved_with_edges": flops / (headline * 1e-3) / 1e12,
+            "peak": peak,
+            "unit": "TFLOP/s",
+            "frac": flops / (timings["attention_only"] * 1e-3) / 1e12 / peak,
+            "traffic": None,
+        },
+        "gpu_launches": args.steps * 3,
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     args = parse_args()
+    if args.workload == "prefill" and args.impl != "reference":
+        run_prefill(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:
