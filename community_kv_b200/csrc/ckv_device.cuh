@@ -74,6 +74,33 @@ __device__ __forceinline__ uint32_t smem_u32(const void* pointer) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
 }
 
+// Programmatic dependent launch: a kernel lets the next kernel in the stream
+// start its prologue early, and waits for its own predecessor's results just
+// before it first reads them.
+__device__ __forceinline__ void pdl_release_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait_for_predecessor() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Host side: launch with the programmatic-serialisation attribute.
+template <typename Kernel>
+inline cudaError_t launch_dependent(Kernel kernel, dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, const ckv_layer_args& a) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, a);
+}
+
 // 16-byte asynchronous global -> shared copy (L2 only); src_bytes 0 zero-fills.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)

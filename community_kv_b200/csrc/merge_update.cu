@@ -37,6 +37,8 @@ __global__ void __launch_bounds__(kMergeThreads + 32) merge_update_kernel(const 
   const bool leader = u.head == u.graph && !(a.flags & CKV_FLAG_SKIP_UPDATE);
   const int64_t graph_slot = static_cast<int64_t>(u.batch) * a.graphs + u.graph;
   const float* partial = a.partials + static_cast<int64_t>(flat) * splits * group * kPartialStride;
+  pdl_release_dependents();
+  pdl_wait_for_predecessor();  // partials and candidates come from the attention kernel
 
   // state of the update warp that crosses the barrier
   float my_score = 0.f;
@@ -360,8 +362,8 @@ __global__ void __launch_bounds__(kMergeThreads) sync_shared_kernel(const ckv_la
 }
 
 cudaError_t launch_merge_update(const ckv_layer_args& a, cudaStream_t stream) {
-  merge_update_kernel<<<a.batch * a.retrieval_heads, kMergeThreads + 32, 0, stream>>>(a);
-  cudaError_t err = cudaGetLastError();
+  cudaError_t err = launch_dependent(merge_update_kernel, dim3(a.batch * a.retrieval_heads),
+                                     dim3(kMergeThreads + 32), 0, stream, a);
   if (err != cudaSuccess) {
     return err;
   }

@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_kernel(const ckv_layer
   const int lane = threadIdx.x & 31;
   const int slice = lane & 7;   // which 16 of the 128 dimensions
   const int quad = lane >> 3;   // row inside a group of four consecutive rows
+  pdl_release_dependents();
 
   // inclusive prefix of the per-unit group counts
   for (int unit = threadIdx.x; unit < units; unit += kScoreThreads) {
@@ -90,6 +91,7 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_kernel(const ckv_layer
     }
   }
   __syncthreads();
+  pdl_wait_for_predecessor();  // the query (and last step's state) come from upstream
   const int total = prefix[units];
   const int my_begin = static_cast<int>(static_cast<int64_t>(blockIdx.x) * total / gridDim.x);
   const int my_end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * total / gridDim.x);
@@ -161,40 +163,49 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_kernel(const ckv_layer
       }
 
       float best = -INFINITY;
-      for (int g = 0; g < group; ++g) {
-        float qv[16];
+      // two heads per pass: eight independent accumulation chains per lane
+      for (int g = 0; g < group; g += 2) {
+        const bool pair = g + 1 < group;
+        float qa[16], qb[16];
         const float4* qp = reinterpret_cast<const float4*>(q_s) + g * 32 + slice;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const float4 v = qp[k * 8];
-          qv[4 * k + 0] = v.x;
-          qv[4 * k + 1] = v.y;
-          qv[4 * k + 2] = v.z;
-          qv[4 * k + 3] = v.w;
+          const float4 w = pair ? qp[32 + k * 8] : v;
+          qa[4 * k + 0] = v.x; qa[4 * k + 1] = v.y; qa[4 * k + 2] = v.z; qa[4 * k + 3] = v.w;
+          qb[4 * k + 0] = w.x; qb[4 * k + 1] = w.y; qb[4 * k + 2] = w.z; qb[4 * k + 3] = w.w;
         }
-        float p[4];
+        float pa[4], pb[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          float acc = __fmul_rn(x[i][0], qv[0]);
+          float acc_a = __fmul_rn(x[i][0], qa[0]);
+          float acc_b = __fmul_rn(x[i][0], qb[0]);
 #pragma unroll
           for (int k = 1; k < 16; ++k) {
-            acc = __fmaf_rn(x[i][k], qv[k], acc);
+            acc_a = __fmaf_rn(x[i][k], qa[k], acc_a);
+            acc_b = __fmaf_rn(x[i][k], qb[k], acc_b);
           }
-          p[i] = acc;
+          pa[i] = acc_a;
+          pb[i] = acc_b;
         }
         // Sum the eight slices of each row: (j, j^4), then (j, j^2), then (j, j^1),
         // folding the four rows onto the lanes on the way (a transposing butterfly).
-        float keep0 = up_a ? p[2] : p[0];
-        float keep1 = up_a ? p[3] : p[1];
-        const float send0 = up_a ? p[0] : p[2];
-        const float send1 = up_a ? p[1] : p[3];
-        keep0 = __fadd_rn(keep0, __shfl_xor_sync(0xffffffffu, send0, 4));
-        keep1 = __fadd_rn(keep1, __shfl_xor_sync(0xffffffffu, send1, 4));
-        float keep = up_b ? keep1 : keep0;
-        const float send = up_b ? keep0 : keep1;
-        keep = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 2));
-        keep = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, keep, 1));
-        best = fmaxf(best, keep);
+        float keep0_a = up_a ? pa[2] : pa[0], keep1_a = up_a ? pa[3] : pa[1];
+        float keep0_b = up_a ? pb[2] : pb[0], keep1_b = up_a ? pb[3] : pb[1];
+        keep0_a = __fadd_rn(keep0_a, __shfl_xor_sync(0xffffffffu, up_a ? pa[0] : pa[2], 4));
+        keep1_a = __fadd_rn(keep1_a, __shfl_xor_sync(0xffffffffu, up_a ? pa[1] : pa[3], 4));
+        keep0_b = __fadd_rn(keep0_b, __shfl_xor_sync(0xffffffffu, up_a ? pb[0] : pb[2], 4));
+        keep1_b = __fadd_rn(keep1_b, __shfl_xor_sync(0xffffffffu, up_a ? pb[1] : pb[3], 4));
+        float keep_a = up_b ? keep1_a : keep0_a;
+        float keep_b = up_b ? keep1_b : keep0_b;
+        keep_a = __fadd_rn(keep_a, __shfl_xor_sync(0xffffffffu, up_b ? keep0_a : keep1_a, 2));
+        keep_b = __fadd_rn(keep_b, __shfl_xor_sync(0xffffffffu, up_b ? keep0_b : keep1_b, 2));
+        keep_a = __fadd_rn(keep_a, __shfl_xor_sync(0xffffffffu, keep_a, 1));
+        keep_b = __fadd_rn(keep_b, __shfl_xor_sync(0xffffffffu, keep_b, 1));
+        best = fmaxf(best, keep_a);
+        if (pair) {
+          best = fmaxf(best, keep_b);
+        }
       }
       if ((slice & 1) == 0 && row < limit) {
         const bool live = row < count && size > 0;
@@ -346,6 +357,7 @@ __global__ void __launch_bounds__(kSelectThreads, 1) select_kernel(const ckv_lay
       reinterpret_cast<const uint16_t*>(a.scores) + static_cast<int64_t>(flat) * capacity;
   const int32_t* sizes = a.community_sizes + static_cast<int64_t>(flat) * capacity;
   const bool stashed = active <= kStash;
+  pdl_release_dependents();
 
   if (tid < 256) {
     hist_mass[tid] = 0;
@@ -354,6 +366,7 @@ __global__ void __launch_bounds__(kSelectThreads, 1) select_kernel(const ckv_lay
   if (tid == 0) {
     s_stored_equal = 0;
   }
+  pdl_wait_for_predecessor();  // the fp16 scores come from the scoring kernel
   if (stashed) {
 #pragma unroll 5
     for (int c = tid; c < active; c += kSelectThreads) {
@@ -606,13 +619,12 @@ cudaError_t launch_score(const ckv_layer_args& a, cudaStream_t stream) {
   }
   const long long finest = static_cast<long long>(units) * ((a.community_capacity + 127) / 128);
   const int grid = finest < 1 ? 1 : (finest > 2 * 148 ? 2 * 148 : static_cast<int>(finest));
-  score_kernel<<<grid, kScoreThreads, 0, stream>>>(a);
-  return cudaGetLastError();
+  return launch_dependent(score_kernel, dim3(grid), dim3(kScoreThreads), 0, stream, a);
 }
 
 cudaError_t launch_select(const ckv_layer_args& a, cudaStream_t stream) {
-  select_kernel<<<a.batch * a.retrieval_heads, kSelectThreads, 0, stream>>>(a);
-  return cudaGetLastError();
+  return launch_dependent(select_kernel, dim3(a.batch * a.retrieval_heads), dim3(kSelectThreads), 0,
+                          stream, a);
 }
 
 cudaError_t launch_resolve(const ckv_layer_args& a, cudaStream_t stream) {

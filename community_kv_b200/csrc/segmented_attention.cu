@@ -106,6 +106,8 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const ckv_la
   const __nv_bfloat16* query = reinterpret_cast<const __nv_bfloat16*>(a.query) +
                                (static_cast<int64_t>(u.batch) * a.retrieval_heads + u.head) *
                                    group * kHeadDim;
+  pdl_release_dependents();
+  pdl_wait_for_predecessor();  // positions (and the query) are produced upstream
   if (threadIdx.x < kHeadDim / 2) {
     reinterpret_cast<uint32_t*>(q_rep)[threadIdx.x] =
         reinterpret_cast<const uint32_t*>(query)[threadIdx.x];
@@ -429,11 +431,9 @@ cudaError_t launch_attention(const ckv_layer_args& a, cudaStream_t stream) {
   }
   const dim3 grid(a.splits, a.batch * a.retrieval_heads);
   if (a.group_size > 8) {
-    attention_kernel<2><<<grid, kAttnThreads, AttnSmem::kTotal, stream>>>(a);
-  } else {
-    attention_kernel<1><<<grid, kAttnThreads, AttnSmem::kTotal, stream>>>(a);
+    return launch_dependent(attention_kernel<2>, grid, dim3(kAttnThreads), AttnSmem::kTotal, stream, a);
   }
-  return cudaGetLastError();
+  return launch_dependent(attention_kernel<1>, grid, dim3(kAttnThreads), AttnSmem::kTotal, stream, a);
 }
 
 }  // namespace ckv
