@@ -52,14 +52,25 @@ __global__ void __launch_bounds__(kMergeThreads + 32) merge_update_kernel(const 
   // key element of the new token, fetched early by the merging threads
   float key_value = 0.f;
 
+  const bool update_only = (a.flags & CKV_FLAG_UPDATE_ONLY) != 0;
   if (warp < kMergeThreads / 32) {
     if (leader) {
       const int position = a.current_position[graph_slot];
-      if (position >= 0 && position < a.sequence_capacity) {
+      if (a.current_key != nullptr) {
+        // [batch, R, 128]: the new token's key for this retrieval head's KV head
+        const __nv_bfloat16* key_row = reinterpret_cast<const __nv_bfloat16*>(a.current_key) +
+                                       static_cast<int64_t>(flat) * kHeadDim;
+        key_value = __bfloat162float(key_row[threadIdx.x]);
+      } else if (position >= 0 && position < a.sequence_capacity) {
         const __nv_bfloat16* key_row = reinterpret_cast<const __nv_bfloat16*>(a.key) +
                                        u.batch * a.key_batch_stride + u.kv * a.key_head_stride +
                                        static_cast<int64_t>(position) * a.key_row_stride;
         key_value = __bfloat162float(key_row[threadIdx.x]);
+      }
+    }
+    if (update_only) {
+      if (threadIdx.x == 0) {
+        lse_s = a.lse[static_cast<int64_t>(flat) * group];
       }
     }
     // ---- split merge: warp w takes heads w, w+4, ...; lane s reads split s's
@@ -67,7 +78,7 @@ __global__ void __launch_bounds__(kMergeThreads + 32) merge_update_kernel(const 
     // independent 16-byte loads ----
     __nv_bfloat16* output = reinterpret_cast<__nv_bfloat16*>(a.output) +
                             static_cast<int64_t>(flat) * group * kHeadDim;
-    for (int g = warp; g < group; g += kMergeThreads / 32) {
+    for (int g = warp; g < group && !update_only; g += kMergeThreads / 32) {
       float my_max = -INFINITY;
       float my_sum = 0.f;
       if (lane < splits) {
@@ -99,6 +110,14 @@ __global__ void __launch_bounds__(kMergeThreads + 32) merge_update_kernel(const 
         numerator.z += v.z * w;
         numerator.w += v.w * w;
       }
+      if (a.merged != nullptr) {
+        float* row = a.merged + (static_cast<int64_t>(flat) * group + g) * kPartialStride;
+        *reinterpret_cast<float4*>(row + 4 * lane) = numerator;
+        if (lane == 0) {
+          row[kHeadDim] = best;
+          row[kHeadDim + 1] = denominator;
+        }
+      }
       const __nv_bfloat162 lo =
           __floats2bfloat162_rn(numerator.x / denominator, numerator.y / denominator);
       const __nv_bfloat162 hi =
@@ -124,14 +143,14 @@ __global__ void __launch_bounds__(kMergeThreads + 32) merge_update_kernel(const 
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int index = lane + 32 * i;
-      mine[i] = index < total ? candidates[index] : 0ull;
+      mine[i] = (index < total && !update_only) ? candidates[index] : 0ull;
     }
     if (leader) {
       active = a.community_counts[flat];
       old_total = a.total_weight[graph_slot];
       current = a.current_position[graph_slot];
     }
-    for (int k = 0; k < kKappa; ++k) {
+    for (int k = 0; k < kKappa && !update_only; ++k) {
       uint64_t local = 0ull;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -149,7 +168,12 @@ __global__ void __launch_bounds__(kMergeThreads + 32) merge_update_kernel(const 
         my_position = static_cast<int>(0xffffffffu - static_cast<uint32_t>(best));
       }
     }
-    if (lane < kKappa) {
+    if (update_only) {
+      if (lane < kKappa) {
+        my_score = a.topk_scores[static_cast<int64_t>(flat) * kKappa + lane];
+        my_position = a.topk_positions[static_cast<int64_t>(flat) * kKappa + lane];
+      }
+    } else if (lane < kKappa) {
       a.topk_scores[static_cast<int64_t>(flat) * kKappa + lane] = my_score;
       a.topk_positions[static_cast<int64_t>(flat) * kKappa + lane] = my_position;
     }
@@ -346,9 +370,11 @@ __global__ void __launch_bounds__(kMergeThreads) sync_shared_kernel(const ckv_la
   if (current >= 0 && current < a.sequence_capacity) {
     __nv_fp8_storage_t* centroid = reinterpret_cast<__nv_fp8_storage_t*>(a.centroids) +
                                    size_index * kHeadDim;
-    const __nv_bfloat16* key_row = reinterpret_cast<const __nv_bfloat16*>(a.key) +
-                                   u.batch * a.key_batch_stride + u.kv * a.key_head_stride +
-                                   static_cast<int64_t>(current) * a.key_row_stride;
+    const __nv_bfloat16* key_row =
+        a.current_key != nullptr
+            ? reinterpret_cast<const __nv_bfloat16*>(a.current_key) + static_cast<int64_t>(flat) * kHeadDim
+            : reinterpret_cast<const __nv_bfloat16*>(a.key) + u.batch * a.key_batch_stride +
+                  u.kv * a.key_head_stride + static_cast<int64_t>(current) * a.key_row_stride;
     const float key_value = __bfloat162float(key_row[d]);
     float updated = key_value;
     if (old_size > 0) {

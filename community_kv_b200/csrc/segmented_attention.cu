@@ -115,6 +115,11 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const ckv_la
   __syncthreads();
 
   const int32_t* positions = a.positions + static_cast<int64_t>(flat) * a.token_budget;
+  // With a sequence-sharded cache only rows [begin, begin+count) are local: other
+  // selected rows become masked slots here and are attended to by their owner.
+  const int row_begin = a.kv_row_count > 0 ? a.kv_row_begin : 0;
+  const int row_end = a.kv_row_count > 0 ? a.kv_row_begin + a.kv_row_count : 0x7fffffff;
+  auto local_row = [&](int pos) { return (pos >= row_begin && pos < row_end) ? pos - row_begin : -1; };
   const __nv_bfloat16* key_head = reinterpret_cast<const __nv_bfloat16*>(a.key) +
                                   u.batch * a.key_batch_stride + u.kv * a.key_head_stride;
   const __nv_bfloat16* value_head = reinterpret_cast<const __nv_bfloat16*>(a.value) +
@@ -142,8 +147,8 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const ckv_la
 
   // positions of the steps in flight (this lane's token) and of the next one
   static_assert(kStages == 2, "the position ring below is written for two stages");
-  int pos_even = 0 < steps ? positions[warp_token0 + token_lane] : -1;
-  int pos_odd = 1 < steps ? positions[warp_token0 + kStepTokens + token_lane] : -1;
+  int pos_even = 0 < steps ? local_row(positions[warp_token0 + token_lane]) : -1;
+  int pos_odd = 1 < steps ? local_row(positions[warp_token0 + kStepTokens + token_lane]) : -1;
   if (0 < steps) {
     issue(0, pos_even);
   }
@@ -193,7 +198,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const ckv_la
     // position of the token this lane will fetch for step + kStages (prefetch now)
     const int next_step = step + kStages;
     const int next_pos =
-        next_step < steps ? positions[warp_token0 + next_step * kStepTokens + token_lane] : -1;
+        next_step < steps ? local_row(positions[warp_token0 + next_step * kStepTokens + token_lane]) : -1;
     cp_async_wait<kStages - 1>();  // this step's group has landed (one younger group may be pending)
     __syncwarp();
     const uint32_t k_u32 = rows_u32 + stage * kStageBytes;
@@ -307,7 +312,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const ckv_la
         const int logical = warp_token0 + step * kStepTokens + token_lane;
         const float score = logical < a.num_sink ? -INFINITY : __fmul_rn(total, scale);
         candidate = (static_cast<uint64_t>(ordered_key32(score)) << 32) |
-                    (0xffffffffu - static_cast<uint32_t>(my_pos));
+                    (0xffffffffu - static_cast<uint32_t>(my_pos + row_begin));
       }
       unsigned pending = __ballot_sync(0xffffffffu, candidate > warp_floor);
       while (pending) {

@@ -93,6 +93,10 @@ class LayerArgs(ctypes.Structure):
         ("assigned", _ptr),
         ("overflow", _ptr),
         ("status", _ptr),
+        ("kv_row_begin", _i32),
+        ("kv_row_count", _i32),
+        ("merged", _ptr),
+        ("current_key", _ptr),
     ]
 
 
@@ -143,6 +147,7 @@ STATIC_MAX_BUDGET = 4096
 STATIC_MAX_SPLITS = 8
 STATIC_MAX_GROUP = 8
 FLAG_ATTENTION_ONLY = 2
+FLAG_UPDATE_ONLY = 4
 DEV_WAIT_TIMEOUT = 1
 PARTIAL_STRIDE = 132
 
@@ -156,6 +161,7 @@ ENTRY_POINTS = (
     "ckv_attention_smem_bytes",
     "ckv_segmented_attention_static",
     "ckv_prefill_topk",
+    "ckv_online_update",
 )
 
 
@@ -182,6 +188,7 @@ def library() -> ctypes.CDLL:
         "ckv_segmented_attention",
         "ckv_decode_layer",
         "ckv_segmented_attention_static",
+        "ckv_online_update",
     ):
         function = getattr(lib, name)
         function.restype = ctypes.c_int
@@ -219,6 +226,7 @@ __all__ = [
     "ENTRY_POINTS",
     "FLAG_ATTENTION_ONLY",
     "FLAG_SKIP_UPDATE",
+    "FLAG_UPDATE_ONLY",
     "LayerArgs",
     "NativeError",
     "PARTIAL_STRIDE",

@@ -58,6 +58,8 @@ typedef enum ckv_status {
 
 /* flags */
 #define CKV_FLAG_SKIP_UPDATE 1    /* attention only: leave the graph state untouched */
+#define CKV_FLAG_UPDATE_ONLY 4    /* ckv_online_update: take lse / topk_scores / topk_positions
+                                     as inputs and only apply the online assignment */
 #define CKV_FLAG_ATTENTION_ONLY 2 /* ckv_segmented_attention: launch only the gather+attention
                                      kernel on the positions already in the workspace (no
                                      position resolution, no merge); for kernel timing */
@@ -134,6 +136,15 @@ typedef struct ckv_layer_args {
   int32_t* assigned;           /* [batch, graphs] */
   int32_t* overflow;           /* [batch, graphs] */
   uint32_t* status;            /* one device word, may be null */
+  /* ---- sequence sharding (all zero / null when the whole cache is local) ---- */
+  int32_t kv_row_begin;        /* first global cache row held in `key` / `value` */
+  int32_t kv_row_count;        /* rows held locally; 0 = unsharded.  Selected rows outside
+                                  [begin, begin+count) are skipped by the attention kernel */
+  float* merged;               /* optional [batch, R, G, 132]: the merged, un-normalised
+                                  (acc[128], max, sum) of every head, for a cross-GPU combine */
+  const void* current_key;     /* optional bf16 [batch, R, 128]: key of the token being decoded
+                                  (row of each retrieval head's KV head), used for the centroid
+                                  update instead of a cache read */
 } ckv_layer_args;
 
 /* Arguments of the prefill score-graph kernel.  Q, K, V, O are bf16 with a
@@ -187,6 +198,11 @@ int ckv_segmented_attention(const ckv_layer_args* args, void* cuda_stream);
 
 /* A1..A5 back to back: the whole per-layer decode transition. */
 int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream);
+
+/* A5 alone.  Applies the online assignment and centroid update from the
+ * `lse`, `topk_scores` and `topk_positions` already in the workspace (for
+ * sequence-sharded decoding, where those are combined across GPUs first). */
+int ckv_online_update(const ckv_layer_args* args, void* cuda_stream);
 
 /* P1.  Causal attention (output + lse) that also emits each row's strongest
  * Q.K neighbours: the reference's top-8 rule (mode 1) or exact top-m per KV head
