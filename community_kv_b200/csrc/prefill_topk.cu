@@ -31,7 +31,7 @@
 
 namespace ckv {
 
-constexpr int kPfThreads = 128;
+constexpr int kPfThreads = 256;
 constexpr int kPfRows = 128;
 constexpr int kPfKeys = 128;
 constexpr int kTileBytes = kPfRows * kHeadDim * 2;  // 32 KiB
@@ -161,39 +161,61 @@ __device__ __forceinline__ uint64_t queue_insert64(uint64_t (&queue)[kExactKeep]
 
 // kGroup: query heads per KV head (1, 2, 4, 8).  kMode: 0 attention only,
 // 1 reference top-8 per query head, 2 candidate lists for the exact top-m.
+//
+// 256 threads: thread t owns row t % 128 and the column half t / 128 of every
+// 128-key block (and the same half of the 128 output dimensions).  K, V and the
+// S accumulator are double buffered so that the next block's Q.K^T runs on the
+// tensor cores while this block's softmax and candidate bookkeeping run on the
+// CUDA cores, and P.V of this block runs under the next block's softmax.
+struct PrefillSmem {
+  static constexpr int kQ = 0;
+  static constexpr int kK = kTileBytes;            // two buffers
+  static constexpr int kV = 3 * kTileBytes;        // two buffers
+  static constexpr int kP = 5 * kTileBytes;
+  static constexpr int kExchange = 6 * kTileBytes;  // float [2][128] row maxima / sums
+  static constexpr int kBars = kExchange + 2 * kPfRows * 4;
+  static constexpr int kTotal = kBars + 64;
+};
+
 template <int kGroup, int kMode>
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefill_args a) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint8_t* s_q = smem;
-  uint8_t* s_k = smem + kTileBytes;
-  uint8_t* s_v = smem + 2 * kTileBytes;
-  uint8_t* s_p = smem + 3 * kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 4 * kTileBytes);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  uint8_t* s_q = smem + PrefillSmem::kQ;
+  uint8_t* s_k = smem + PrefillSmem::kK;
+  uint8_t* s_v = smem + PrefillSmem::kV;
+  uint8_t* s_p = smem + PrefillSmem::kP;
+  float* exchange = reinterpret_cast<float*>(smem + PrefillSmem::kExchange);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PrefillSmem::kBars);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
 
   constexpr int kPositions = kPfRows / kGroup;
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
+  const int row = tid & (kPfRows - 1);
+  const int half = tid >> 7;            // which 64 of the 128 columns / output dims
+  const int col0 = half * 64;
   const int tile = blockIdx.x;
   const int kv_head = blockIdx.y;
   const int batch = blockIdx.z;
   const int pos0 = tile * kPositions;
   const int length = a.seq_len;
-  const int row_pos = pos0 + tid / kGroup;
-  const int row_head = kv_head * kGroup + tid % kGroup;
+  const int row_pos = pos0 + row / kGroup;
+  const int row_head = kv_head * kGroup + row % kGroup;
   const bool row_live = row_pos < length;
 
-  const uint32_t bar_s = smem_u32(bars);
-  const uint32_t bar_o = smem_u32(bars + 1);
+  const uint32_t bar_s0 = smem_u32(bars);
+  const uint32_t bar_s1 = smem_u32(bars + 1);
+  const uint32_t bar_o = smem_u32(bars + 2);
   if (tid == 0) {
-    mbar_init(bar_s, 1);
+    mbar_init(bar_s0, 1);
+    mbar_init(bar_s1, 1);
     mbar_init(bar_o, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
-                 "r"(256)
+                 "r"(512)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -207,22 +229,22 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
 
   // ---- stage Q once: row r = (position pos0 + r / G, head kv_head*G + r % G) ----
   for (int index = tid; index < kPfRows * 16; index += kPfThreads) {
-    const int row = index >> 4;
+    const int r = index >> 4;
     const int chunk = index & 15;
-    const int pos = pos0 + row / kGroup;
-    const int head = kv_head * kGroup + row % kGroup;
+    const int pos = pos0 + r / kGroup;
+    const int head = kv_head * kGroup + r % kGroup;
     const bool live = pos < length;
     const __nv_bfloat16* src =
         q_base + (live ? pos : 0) * a.q_row_stride + head * a.q_head_stride + chunk * 8;
-    cp_async16(smem_u32(s_q) + core_offset(row, chunk), src, live ? 16u : 0u);
+    cp_async16(smem_u32(s_q) + core_offset(r, chunk), src, live ? 16u : 0u);
   }
   auto stage_tile = [&](uint8_t* dst, const __nv_bfloat16* base, int64_t row_stride, int key0) {
     for (int index = tid; index < kPfKeys * 16; index += kPfThreads) {
-      const int row = index >> 4;
+      const int r = index >> 4;
       const int chunk = index & 15;
-      const int key = key0 + row;
+      const int key = key0 + r;
       const bool live = key < length;
-      cp_async16(smem_u32(dst) + core_offset(row, chunk),
+      cp_async16(smem_u32(dst) + core_offset(r, chunk),
                  base + (live ? key : 0) * row_stride + chunk * 8, live ? 16u : 0u);
     }
   };
@@ -231,23 +253,39 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
   stage_tile(s_k, k_base, a.k_row_stride, 0);
   stage_tile(s_v, v_base, a.v_row_stride, 0);
   cp_async_commit();
-
+  cp_async_wait<0>();
+  async_proxy_fence();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_s = tmem + ((warp * 32u) << 16);
-  const uint32_t tmem_o = tmem_s + 128u;
+  const uint32_t lane_base = tmem + (((warp & 3) * 32u) << 16);
   const uint32_t idesc_qk = instruction_descriptor(false);
   const uint32_t idesc_pv = instruction_descriptor(true);
 
-  float out[kHeadDim];
+  auto issue_qk = [&](int block) {
+    const int buffer = block & 1;
 #pragma unroll
-  for (int d = 0; d < kHeadDim; ++d) {
+    for (int ks = 0; ks < 8; ++ks) {
+      const uint64_t desc_q = smem_descriptor(smem_u32(s_q) + ks * 256, 128, 2048);
+      const uint64_t desc_k =
+          smem_descriptor(smem_u32(s_k) + buffer * kTileBytes + ks * 256, 128, 2048);
+      umma(tmem + buffer * 128u, desc_q, desc_k, idesc_qk, ks > 0 ? 1u : 0u);
+    }
+    umma_commit(buffer ? bar_s1 : bar_s0);
+  };
+  if (tid == 0) {
+    issue_qk(0);
+  }
+
+  float out[64];
+#pragma unroll
+  for (int d = 0; d < 64; ++d) {
     out[d] = 0.f;
   }
-  float run_max = -INFINITY;  // of the raw (unscaled) scores
-  float run_sum = 0.f;
+  float run_max = -INFINITY;  // of the raw (unscaled) scores, whole row
+  float run_sum = 0.f;        // this thread's column half only
+  float pending_corr = 1.f;   // rescale that goes with the P.V result still in flight
   const float scale_log2 = a.softmax_scale * kLog2e;
   uint32_t q32[4][kLocalK];
   uint64_t q64[kExactKeep];
@@ -268,185 +306,221 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
     }
   }
   bool failed = false;
+  const int limit = row_live ? min(row_pos, length - 1) : -1;  // last visible key
+
+  auto fold_output = [&](int block) {
+    // O' of `block` is complete: add it to the running output row
+    if (!mbar_wait(bar_o, block & 1)) {
+      failed = true;
+    }
+    tc_fence_after();
+#pragma unroll
+    for (int chunk = 0; chunk < 2; ++chunk) {
+      float o[32];
+      tmem_load32(lane_base + 256u + col0 + chunk * 32, o);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        out[chunk * 32 + c] = out[chunk * 32 + c] * pending_corr + o[c];
+      }
+    }
+  };
 
   for (int block = 0; block < blocks; ++block) {
     const int key0 = block * kPfKeys;
-    const uint32_t parity = block & 1;
-    cp_async_wait<0>();
-    async_proxy_fence();
-    __syncthreads();
-    // ---- S = Q K^T ----
-    if (tid == 0) {
-      tc_fence_after();
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint64_t desc_q = smem_descriptor(smem_u32(s_q) + ks * 256, 128, 2048);
-        const uint64_t desc_k = smem_descriptor(smem_u32(s_k) + ks * 256, 128, 2048);
-        umma(tmem, desc_q, desc_k, idesc_qk, ks > 0 ? 1u : 0u);
-      }
-      umma_commit(bar_s);
+    const int buffer = block & 1;
+    // K buffer of block+1 was last read by Q.K^T of block-1, which every thread has
+    // already waited for
+    if (block + 1 < blocks) {
+      stage_tile(s_k + (buffer ^ 1) * kTileBytes, k_base, a.k_row_stride, key0 + kPfKeys);
     }
-    if (!mbar_wait(bar_s, parity)) {
+    cp_async_commit();
+    if (!mbar_wait(buffer ? bar_s1 : bar_s0, (block >> 1) & 1)) {
       failed = true;
     }
+    tc_fence_after();
+    // ---- this thread's 64 raw scores, kept in registers ----
+    float s[64];
+    {
+      float part[32];
+      tmem_load32(lane_base + buffer * 128u + col0, part);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        s[c] = part[c];
+      }
+      tmem_load32(lane_base + buffer * 128u + col0 + 32, part);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        s[32 + c] = part[c];
+      }
+    }
+    float half_max = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < 64; ++c) {
+      const int j = key0 + col0 + c;
+      half_max = fmaxf(half_max, j <= limit ? s[c] : -INFINITY);
+    }
+    exchange[half * kPfRows + row] = half_max;
+    if (block > 0) {
+      fold_output(block - 1);
+    }
+    // P.V of block-1 is complete for this thread, so its V buffer may be refilled;
+    // that copy is only needed one iteration from now
+    if (block + 1 < blocks) {
+      stage_tile(s_v + (buffer ^ 1) * kTileBytes, v_base, a.v_row_stride, key0 + kPfKeys);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();  // K of block+1 and V of this block have landed
+    async_proxy_fence();
+    tc_fence_before();
     if (__syncthreads_or(failed ? 1 : 0)) {
       failed = true;
       break;
     }
-    tc_fence_after();
-    // the K tile is free again: fetch the next one while this block is processed
-    if (block + 1 < blocks) {
-      stage_tile(s_k, k_base, a.k_row_stride, key0 + kPfKeys);
+    // ---- next block's S = Q K^T starts now, under this block's softmax ----
+    if (tid == 0 && block + 1 < blocks) {
+      tc_fence_after();
+      issue_qk(block + 1);
     }
-    cp_async_commit();
+    const float tile_max = fmaxf(half_max, exchange[(half ^ 1) * kPfRows + row]);
 
-    // ---- pass A: row maximum of the masked raw scores, candidates ----
-    const int limit = row_live ? min(row_pos, length - 1) : -1;  // last visible key
-    float tile_max = -INFINITY;
-#pragma unroll 1
-    for (int chunk = 0; chunk < 4; ++chunk) {
-      float s[32];
-      tmem_load32(tmem_s + chunk * 32, s);
+    if constexpr (kMode == 1) {
+      float eligible_max = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const int j = key0 + chunk * 32 + c;
-        const bool visible = j <= limit;
-        tile_max = fmaxf(tile_max, visible ? s[c] : -INFINITY);
+      for (int c = 0; c < 64; ++c) {
+        const int j = key0 + col0 + c;
+        eligible_max = fmaxf(eligible_max, (j <= limit && j >= a.num_sink) ? s[c] : -INFINITY);
       }
-      if constexpr (kMode == 1) {
-        // skip the whole chunk when nothing in it can enter any class queue
-        float chunk_max = -INFINITY;
+      const uint32_t floor_key = min(min(q32[0][kLocalK - 1], q32[1][kLocalK - 1]),
+                                     min(q32[2][kLocalK - 1], q32[3][kLocalK - 1])) >> 17;
+      if (eligible_max > -INFINITY && quantised_key(eligible_max) >= floor_key) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int j = key0 + chunk * 32 + c;
-          chunk_max = fmaxf(chunk_max, (j <= limit && j >= a.num_sink) ? s[c] : -INFINITY);
-        }
-        const uint32_t floor_key =
-            min(min(q32[0][kLocalK - 1], q32[1][kLocalK - 1]),
-                min(q32[2][kLocalK - 1], q32[3][kLocalK - 1])) >> 17;
-        if (chunk_max > -INFINITY && quantised_key(chunk_max) >= floor_key) {
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const int j = key0 + chunk * 32 + c;
-            if (j <= limit && j >= a.num_sink) {
-              const uint32_t candidate = (quantised_key(s[c]) << 17) | (static_cast<uint32_t>(j) & 0x1ffffu);
-              uint32_t(&queue)[kLocalK] = q32[(c & 7) >> 1];
-              if (candidate > queue[kLocalK - 1]) {
-                queue_insert<kLocalK>(queue, candidate);
-              }
+        for (int c = 0; c < 64; ++c) {
+          const int j = key0 + col0 + c;
+          if (j <= limit && j >= a.num_sink) {
+            const uint32_t candidate =
+                (quantised_key(s[c]) << 17) | (static_cast<uint32_t>(j) & 0x1ffffu);
+            uint32_t(&queue)[kLocalK] = q32[(c & 7) >> 1];
+            if (candidate > queue[kLocalK - 1]) {
+              queue_insert<kLocalK>(queue, candidate);
             }
           }
         }
       }
-      if constexpr (kMode == 2) {
-        // group maximum of the scaled scores, shared by the G lanes of a position;
-        // lane h of the group ranks the columns j % G == h
+    }
+    if constexpr (kMode == 2) {
+      // group maximum of the scaled scores, shared by the G lanes of a position;
+      // lane h of the group ranks the columns j % G == h
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int j = key0 + chunk * 32 + c;
-          float v = (j <= limit && j >= a.num_sink) ? s[c] * a.softmax_scale : -INFINITY;
+      for (int c = 0; c < 64; ++c) {
+        const int j = key0 + col0 + c;
+        float v = (j <= limit && j >= a.num_sink) ? s[c] * a.softmax_scale : -INFINITY;
 #pragma unroll
-          for (int offset = 1; offset < kGroup; offset <<= 1) {
-            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
-          }
-          if ((c % kGroup) == (tid % kGroup) && v > -INFINITY) {
-            const uint64_t candidate = (static_cast<uint64_t>(ordered_key32(v)) << 32) |
-                                       (0xffffffffu - static_cast<uint32_t>(j));
-            // keep the best key that was ever turned away: the second kernel needs it
-            // to prove that the short list is complete
-            const uint64_t lost =
-                candidate > q64[kExactKeep - 1] ? queue_insert64(q64, candidate) : candidate;
-            dropped = lost > dropped ? lost : dropped;
-          }
+        for (int offset = 1; offset < kGroup; offset <<= 1) {
+          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+        }
+        if ((c % kGroup) == (row % kGroup) && v > -INFINITY) {
+          const uint64_t candidate = (static_cast<uint64_t>(ordered_key32(v)) << 32) |
+                                     (0xffffffffu - static_cast<uint32_t>(j));
+          // keep the best key that was ever turned away: the second kernel needs it
+          // to prove that the short list is complete
+          const uint64_t lost =
+              candidate > q64[kExactKeep - 1] ? queue_insert64(q64, candidate) : candidate;
+          dropped = lost > dropped ? lost : dropped;
         }
       }
     }
+
     const float new_max = fmaxf(run_max, tile_max);
     const float safe_max = new_max == -INFINITY ? 0.f : new_max;
     const float corr = exp2f((run_max - safe_max) * scale_log2);
     run_max = new_max;
     run_sum *= corr;
+    // `out` holds everything up to block-1; the rescale for this block's maximum is
+    // applied when this block's P.V result is folded in
+    pending_corr = corr;
 
-    // ---- pass B: probabilities -> shared memory (bf16, operand layout) ----
-#pragma unroll 1
-    for (int chunk = 0; chunk < 4; ++chunk) {
-      float s[32];
-      tmem_load32(tmem_s + chunk * 32, s);
-      uint32_t packed[16];
+    // ---- probabilities -> shared memory (bf16, operand layout) ----
 #pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        const int j = key0 + chunk * 32 + c;
+    for (int piece = 0; piece < 8; ++piece) {
+      uint32_t packed[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int c = piece * 8 + 2 * e;
+        const int j = key0 + col0 + c;
         const float p0 = j <= limit ? exp2f((s[c] - safe_max) * scale_log2) : 0.f;
         const float p1 = j + 1 <= limit ? exp2f((s[c + 1] - safe_max) * scale_log2) : 0.f;
         run_sum += p0 + p1;
-        packed[c >> 1] = pack_bf16(p0, p1);
+        packed[e] = pack_bf16(p0, p1);
       }
-#pragma unroll
-      for (int piece = 0; piece < 4; ++piece) {
-        *reinterpret_cast<uint4*>(s_p + core_offset(tid, chunk * 4 + piece)) =
-            make_uint4(packed[4 * piece], packed[4 * piece + 1], packed[4 * piece + 2],
-                       packed[4 * piece + 3]);
-      }
+      *reinterpret_cast<uint4*>(s_p + core_offset(row, half * 8 + piece)) =
+          make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
     async_proxy_fence();
     tc_fence_before();
     __syncthreads();
-    // ---- O' = P V ----
+    // ---- O' = P V, runs under the next block's softmax ----
     if (tid == 0) {
       tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         const uint64_t desc_p = smem_descriptor(smem_u32(s_p) + ks * 256, 128, 2048);
-        const uint64_t desc_v = smem_descriptor(smem_u32(s_v) + ks * 4096, 2048, 128);
-        umma(tmem + 128u, desc_p, desc_v, idesc_pv, ks > 0 ? 1u : 0u);
+        const uint64_t desc_v =
+            smem_descriptor(smem_u32(s_v) + buffer * kTileBytes + ks * 4096, 2048, 128);
+        umma(tmem + 256u, desc_p, desc_v, idesc_pv, ks > 0 ? 1u : 0u);
       }
       umma_commit(bar_o);
     }
-    if (!mbar_wait(bar_o, parity)) {
-      failed = true;
-    }
-    if (__syncthreads_or(failed ? 1 : 0)) {
-      failed = true;
-      break;
-    }
-    tc_fence_after();
-    if (block + 1 < blocks) {
-      stage_tile(s_v, v_base, a.v_row_stride, key0 + kPfKeys);
-    }
-    cp_async_commit();
-#pragma unroll
-    for (int chunk = 0; chunk < 4; ++chunk) {
-      float o[32];
-      tmem_load32(tmem_o + chunk * 32, o);
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        out[chunk * 32 + c] = out[chunk * 32 + c] * corr + o[c];
-      }
-    }
-    tc_fence_before();
+  }
+  if (!failed) {
+    fold_output(blocks - 1);
   }
   cp_async_wait<0>();
-  __syncthreads();
+  tc_fence_before();
+  const int any_failed = __syncthreads_or(failed ? 1 : 0);
   if (warp == 0) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512)
                  : "memory");
   }
-  if (failed) {
+  if (any_failed) {
     if (tid == 0 && a.status != nullptr) {
       atomicOr(a.status, CKV_DEV_WAIT_TIMEOUT);
     }
     return;
   }
+
+  // ---- epilogue: combine the two column halves of every row ----
+  exchange[half * kPfRows + row] = run_sum;
+  uint32_t* queue_exchange = reinterpret_cast<uint32_t*>(s_p);  // P tile is idle now
+  if (half == 1) {
+    if constexpr (kMode == 1) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int k = 0; k < kLocalK; ++k) {
+          queue_exchange[row * 24 + c * kLocalK + k] = q32[c][k];
+        }
+      }
+    }
+    if constexpr (kMode == 2) {
+      uint64_t* wide = reinterpret_cast<uint64_t*>(s_p) + row * (kExactKeep + 1);
+#pragma unroll
+      for (int k = 0; k < kExactKeep; ++k) {
+        wide[k] = q64[k];
+      }
+      wide[kExactKeep] = dropped;
+    }
+  }
+  __syncthreads();
   if (!row_live) {
     return;
   }
-
-  // ---- epilogue: normalise, write the output row, the lse and the edges ----
-  const float inverse = 1.f / run_sum;
+  const float total = exchange[row] + exchange[kPfRows + row];
+  const float inverse = 1.f / total;
   __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.output) + batch * a.o_batch_stride +
-                       static_cast<int64_t>(row_pos) * a.o_row_stride + row_head * a.o_head_stride;
+                       static_cast<int64_t>(row_pos) * a.o_row_stride + row_head * a.o_head_stride +
+                       col0;
 #pragma unroll
-  for (int d = 0; d < kHeadDim; d += 8) {
+  for (int d = 0; d < 64; d += 8) {
     uint4 v;
     v.x = pack_bf16(out[d] * inverse, out[d + 1] * inverse);
     v.y = pack_bf16(out[d + 2] * inverse, out[d + 3] * inverse);
@@ -454,11 +528,25 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
     v.w = pack_bf16(out[d + 6] * inverse, out[d + 7] * inverse);
     *reinterpret_cast<uint4*>(dst + d) = v;
   }
-  const float lse = run_max * a.softmax_scale + logf(run_sum);
+  if (half == 1) {
+    return;
+  }
+  const float lse = run_max * a.softmax_scale + logf(total);
   const int64_t heads_total = static_cast<int64_t>(gridDim.y) * kGroup;
   a.lse[(batch * heads_total + row_head) * length + row_pos] = lse;
 
   if constexpr (kMode == 1) {
+    // fold the other half's class queues into this thread's
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int k = 0; k < kLocalK; ++k) {
+        const uint32_t candidate = queue_exchange[row * 24 + c * kLocalK + k];
+        if (candidate > q32[c][kLocalK - 1]) {
+          queue_insert<kLocalK>(q32[c], candidate);
+        }
+      }
+    }
     const int skip = a.num_sink + kKappa - 1;
     if (row_pos >= skip) {
       // merge the four sorted class queues: eight rounds of "largest head wins"
@@ -493,10 +581,19 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
     }
   }
   if constexpr (kMode == 2) {
+    const uint64_t* wide = reinterpret_cast<const uint64_t*>(s_p) + row * (kExactKeep + 1);
+    dropped = wide[kExactKeep] > dropped ? wide[kExactKeep] : dropped;
+#pragma unroll
+    for (int k = 0; k < kExactKeep; ++k) {
+      const uint64_t candidate = wide[k];
+      const uint64_t lost =
+          candidate > q64[kExactKeep - 1] ? queue_insert64(q64, candidate) : candidate;
+      dropped = lost > dropped ? lost : dropped;
+    }
     // [batch, kv head, position, G lanes, 16 kept + best dropped] for the second kernel
     uint64_t* list = a.candidates +
                      (((static_cast<int64_t>(batch) * gridDim.y + kv_head) * length + row_pos) * kGroup +
-                      tid % kGroup) * (kExactKeep + 1);
+                      row % kGroup) * (kExactKeep + 1);
 #pragma unroll
     for (int k = 0; k < kExactKeep; ++k) {
       list[k] = q64[k];
@@ -681,7 +778,7 @@ namespace {
 
 template <int kGroup>
 cudaError_t launch_for_group(const ckv_prefill_args& a, cudaStream_t stream) {
-  constexpr int kSmem = 4 * kTileBytes + 64;
+  constexpr int kSmem = PrefillSmem::kTotal;
   const dim3 grid((a.seq_len + kPfRows / kGroup - 1) / (kPfRows / kGroup), a.kv_heads, a.batch);
   auto run = [&](auto kernel) -> cudaError_t {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
