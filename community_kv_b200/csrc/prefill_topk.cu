@@ -159,6 +159,55 @@ __device__ __forceinline__ uint64_t queue_insert64(uint64_t (&queue)[kExactKeep]
   return candidate;
 }
 
+// One step of a max reduce-scatter over 2 * kWidth columns between lane pairs
+// `offset` apart: the lane with `upper` set keeps the upper half of the columns.
+template <int kWidth>
+__device__ __forceinline__ void butterfly_stage(const float (&in)[2 * kWidth], float (&out)[kWidth],
+                                                bool upper, int offset) {
+#pragma unroll
+  for (int i = 0; i < kWidth; ++i) {
+    const float keep = upper ? in[kWidth + i] : in[i];
+    const float send = upper ? in[i] : in[kWidth + i];
+    out[i] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, offset));
+  }
+}
+
+// Ranks kCount group-maximum scores (columns first, first + 1, ...) into the lane's
+// list.  `prune`: scores below it cannot be among the position's best 16.  `dropped`
+// collects the best score that was turned away.
+template <int kCount>
+__device__ __forceinline__ void rank_owned(const float (&raw)[kCount], int first, float scale,
+                                           float prune, uint64_t (&list)[kExactKeep],
+                                           float& dropped) {
+  float best = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kCount; ++i) {
+    best = fmaxf(best, raw[i]);
+  }
+  const uint64_t last = list[kExactKeep - 1];
+  const float own = last == 0ull ? -INFINITY : key32_to_float(static_cast<uint32_t>(last >> 32));
+  const float gate = fmaxf(prune, own);
+  if (best * scale < gate) {
+    dropped = fmaxf(dropped, best * scale);
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < kCount; ++i) {
+    const float v = raw[i] * scale;
+    if (v >= gate) {
+      const uint64_t candidate = (static_cast<uint64_t>(ordered_key32(v)) << 32) |
+                                 (0xffffffffu - static_cast<uint32_t>(first + i));
+      const uint64_t lost =
+          candidate > list[kExactKeep - 1] ? queue_insert64(list, candidate) : candidate;
+      if (lost != 0ull) {
+        dropped = fmaxf(dropped, key32_to_float(static_cast<uint32_t>(lost >> 32)));
+      }
+    } else {
+      dropped = fmaxf(dropped, v);
+    }
+  }
+}
+
 // kGroup: query heads per KV head (1, 2, 4, 8).  kMode: 0 attention only,
 // 1 reference top-8 per query head, 2 candidate lists for the exact top-m.
 //
@@ -173,7 +222,8 @@ struct PrefillSmem {
   static constexpr int kV = 3 * kTileBytes;        // two buffers
   static constexpr int kP = 5 * kTileBytes;
   static constexpr int kExchange = 6 * kTileBytes;  // float [2][128] row maxima / sums
-  static constexpr int kBars = kExchange + 2 * kPfRows * 4;
+  static constexpr int kFloors = kExchange + 2 * kPfRows * 4;  // uint32 [2][128] list floors
+  static constexpr int kBars = kFloors + 2 * kPfRows * 4;
   static constexpr int kTotal = kBars + 64;
 };
 
@@ -185,6 +235,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
   uint8_t* s_v = smem + PrefillSmem::kV;
   uint8_t* s_p = smem + PrefillSmem::kP;
   float* exchange = reinterpret_cast<float*>(smem + PrefillSmem::kExchange);
+  uint32_t* floor_exchange = reinterpret_cast<uint32_t*>(smem + PrefillSmem::kFloors);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PrefillSmem::kBars);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
 
@@ -289,7 +340,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
   const float scale_log2 = a.softmax_scale * kLog2e;
   uint32_t q32[4][kLocalK];
   uint64_t q64[kExactKeep];
-  uint64_t dropped = 0ull;
+  float dropped = -INFINITY;  // best score this list ever turned away
   if constexpr (kMode == 1) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
@@ -353,23 +404,33 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
         s[32 + c] = part[c];
       }
     }
+    // interior block: every key is visible to every row of the tile.  Elsewhere the
+    // causal mask is applied once, in place.
+    const bool interior = key0 + kPfKeys - 1 <= pos0;
+    if (!interior) {
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        s[c] = (key0 + col0 + c) <= limit ? s[c] : -INFINITY;
+      }
+    }
     float half_max = -INFINITY;
 #pragma unroll
     for (int c = 0; c < 64; ++c) {
-      const int j = key0 + col0 + c;
-      half_max = fmaxf(half_max, j <= limit ? s[c] : -INFINITY);
+      half_max = fmaxf(half_max, s[c]);
     }
     exchange[half * kPfRows + row] = half_max;
-    if (block > 0) {
-      fold_output(block - 1);
+    if constexpr (kMode == 2) {
+      // 16th-best key of this list, maximised over the lists of the position: no
+      // list's 16th entry can lie above the position's 16th best, so anything
+      // clearly below it is out of the race
+      uint32_t floor_key = static_cast<uint32_t>(q64[kExactKeep - 1] >> 32);
+#pragma unroll
+      for (int offset = 1; offset < kGroup; offset <<= 1) {
+        floor_key = max(floor_key, __shfl_xor_sync(0xffffffffu, floor_key, offset));
+      }
+      floor_exchange[half * kPfRows + row] = floor_key;
     }
-    // P.V of block-1 is complete for this thread, so its V buffer may be refilled;
-    // that copy is only needed one iteration from now
-    if (block + 1 < blocks) {
-      stage_tile(s_v + (buffer ^ 1) * kTileBytes, v_base, a.v_row_stride, key0 + kPfKeys);
-    }
-    cp_async_commit();
-    cp_async_wait<1>();  // K of block+1 and V of this block have landed
+    cp_async_wait<0>();  // K of block+1 and V of this block have landed
     async_proxy_fence();
     tc_fence_before();
     if (__syncthreads_or(failed ? 1 : 0)) {
@@ -382,21 +443,41 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
       issue_qk(block + 1);
     }
     const float tile_max = fmaxf(half_max, exchange[(half ^ 1) * kPfRows + row]);
+    const bool sink_free = key0 >= a.num_sink;
 
     if constexpr (kMode == 1) {
-      float eligible_max = -INFINITY;
+      if (sink_free) {
+        // A key that is below eight keys already held can never reach the output:
+        // the second-best entries of the four classes are eight such keys, and so
+        // are the top four of the two best classes.
+        const uint32_t third0 = q32[0][3], third1 = q32[1][3], third2 = q32[2][3], third3 = q32[3][3];
+        const uint32_t second_of_fourths =
+            max(min(max(third0, third1), max(third2, third3)),
+                max(min(third0, third1), min(third2, third3)));
+        const uint32_t row_floor = max(min(min(q32[0][1], q32[1][1]), min(q32[2][1], q32[3][1])),
+                                       second_of_fourths);
+        // smallest raw score whose quantised key can reach the floor, a little low
+        const float gate = (row_floor >> 17) == 0u
+                               ? -3.0e38f
+                               : (static_cast<float>(row_floor >> 17) - 0.75f) * (1.0f / 256.0f) - 48.0f;
+        if (half_max >= gate) {
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const int j = key0 + col0 + c;
-        eligible_max = fmaxf(eligible_max, (j <= limit && j >= a.num_sink) ? s[c] : -INFINITY);
-      }
-      const uint32_t floor_key = min(min(q32[0][kLocalK - 1], q32[1][kLocalK - 1]),
-                                     min(q32[2][kLocalK - 1], q32[3][kLocalK - 1])) >> 17;
-      if (eligible_max > -INFINITY && quantised_key(eligible_max) >= floor_key) {
+          for (int c = 0; c < 64; ++c) {
+            if (s[c] >= gate) {
+              const uint32_t candidate = (quantised_key(s[c]) << 17) |
+                                         (static_cast<uint32_t>(key0 + col0 + c) & 0x1ffffu);
+              uint32_t(&queue)[kLocalK] = q32[(c & 7) >> 1];
+              if (candidate > queue[kLocalK - 1]) {
+                queue_insert<kLocalK>(queue, candidate);
+              }
+            }
+          }
+        }
+      } else {
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
           const int j = key0 + col0 + c;
-          if (j <= limit && j >= a.num_sink) {
+          if (s[c] > -INFINITY && j >= a.num_sink) {
             const uint32_t candidate =
                 (quantised_key(s[c]) << 17) | (static_cast<uint32_t>(j) & 0x1ffffu);
             uint32_t(&queue)[kLocalK] = q32[(c & 7) >> 1];
@@ -408,24 +489,69 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
       }
     }
     if constexpr (kMode == 2) {
-      // group maximum of the scaled scores, shared by the G lanes of a position;
-      // lane h of the group ranks the columns j % G == h
-#pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const int j = key0 + col0 + c;
-        float v = (j <= limit && j >= a.num_sink) ? s[c] * a.softmax_scale : -INFINITY;
+      // The score of a key for a position is the maximum over the G heads of the
+      // group (G adjacent lanes).
+      if (interior && sink_free) {
+        const uint32_t floor_key =
+            max(floor_exchange[row], floor_exchange[kPfRows + row]);  // both halves' lists
+        const float prune =
+            floor_key == 0u ? -INFINITY : key32_to_float(floor_key) - 2.0f * a.exact_slack;
+        float group_max = half_max;
 #pragma unroll
         for (int offset = 1; offset < kGroup; offset <<= 1) {
-          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+          group_max = fmaxf(group_max, __shfl_xor_sync(0xffffffffu, group_max, offset));
         }
-        if ((c % kGroup) == (row % kGroup) && v > -INFINITY) {
-          const uint64_t candidate = (static_cast<uint64_t>(ordered_key32(v)) << 32) |
-                                     (0xffffffffu - static_cast<uint32_t>(j));
-          // keep the best key that was ever turned away: the second kernel needs it
-          // to prove that the short list is complete
-          const uint64_t lost =
-              candidate > q64[kExactKeep - 1] ? queue_insert64(q64, candidate) : candidate;
-          dropped = lost > dropped ? lost : dropped;
+        const float block_best = group_max * a.softmax_scale;
+        if (!__any_sync(0xffffffffu, block_best >= prune)) {
+          dropped = fmaxf(dropped, block_best);
+        } else {
+          // reduce-scatter over the group: afterwards every lane holds the group
+          // maximum of 64 / G columns of its own
+          const int lane = tid & 31;
+          if constexpr (kGroup == 1) {
+            rank_owned<64>(s, key0 + col0, a.softmax_scale, prune, q64, dropped);
+          } else {
+            float half32[32];
+            butterfly_stage<32>(s, half32, (lane & 1) != 0, 1);
+            int first = key0 + col0 + ((lane & 1) ? 32 : 0);
+            if constexpr (kGroup == 2) {
+              rank_owned<32>(half32, first, a.softmax_scale, prune, q64, dropped);
+            } else {
+              float quarter[16];
+              butterfly_stage<16>(half32, quarter, (lane & 2) != 0, 2);
+              first += (lane & 2) ? 16 : 0;
+              if constexpr (kGroup == 4) {
+                rank_owned<16>(quarter, first, a.softmax_scale, prune, q64, dropped);
+              } else {
+                float eighth[8];
+                butterfly_stage<8>(quarter, eighth, (lane & 4) != 0, 4);
+                first += (lane & 4) ? 8 : 0;
+                rank_owned<8>(eighth, first, a.softmax_scale, prune, q64, dropped);
+              }
+            }
+          }
+        }
+      } else {
+        // masked or sink-bearing block: lane h of the group ranks the columns j % G == h
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int j = key0 + col0 + c;
+          float v = j >= a.num_sink ? s[c] * a.softmax_scale : -INFINITY;
+#pragma unroll
+          for (int offset = 1; offset < kGroup; offset <<= 1) {
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+          }
+          if ((c % kGroup) == (row % kGroup) && v > -INFINITY) {
+            const uint64_t candidate = (static_cast<uint64_t>(ordered_key32(v)) << 32) |
+                                       (0xffffffffu - static_cast<uint32_t>(j));
+            // keep the best score that was ever turned away: the second kernel needs
+            // it to prove that the short list is complete
+            const uint64_t lost =
+                candidate > q64[kExactKeep - 1] ? queue_insert64(q64, candidate) : candidate;
+            if (lost != 0ull) {
+              dropped = fmaxf(dropped, key32_to_float(static_cast<uint32_t>(lost >> 32)));
+            }
+          }
         }
       }
     }
@@ -435,29 +561,37 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
     const float corr = exp2f((run_max - safe_max) * scale_log2);
     run_max = new_max;
     run_sum *= corr;
-    // `out` holds everything up to block-1; the rescale for this block's maximum is
-    // applied when this block's P.V result is folded in
-    pending_corr = corr;
 
-    // ---- probabilities -> shared memory (bf16, operand layout) ----
+    // ---- probabilities (bf16 pairs; masked keys are -inf and come out as 0) ----
+    uint32_t packed[32];
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      const float p0 = exp2f((s[2 * e] - safe_max) * scale_log2);
+      const float p1 = exp2f((s[2 * e + 1] - safe_max) * scale_log2);
+      run_sum += p0 + p1;
+      packed[e] = pack_bf16(p0, p1);
+    }
+    // P.V of block-1 ran under the work above; fold it in, which also frees the P tile
+    // and that block's V buffer
+    if (block > 0) {
+      fold_output(block - 1);
+    }
+    pending_corr = corr;  // goes with this block's P.V result
+    if (block + 1 < blocks) {
+      stage_tile(s_v + (buffer ^ 1) * kTileBytes, v_base, a.v_row_stride, key0 + kPfKeys);
+    }
+    cp_async_commit();
 #pragma unroll
     for (int piece = 0; piece < 8; ++piece) {
-      uint32_t packed[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int c = piece * 8 + 2 * e;
-        const int j = key0 + col0 + c;
-        const float p0 = j <= limit ? exp2f((s[c] - safe_max) * scale_log2) : 0.f;
-        const float p1 = j + 1 <= limit ? exp2f((s[c + 1] - safe_max) * scale_log2) : 0.f;
-        run_sum += p0 + p1;
-        packed[e] = pack_bf16(p0, p1);
-      }
-      *reinterpret_cast<uint4*>(s_p + core_offset(row, half * 8 + piece)) =
-          make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      *reinterpret_cast<uint4*>(s_p + core_offset(row, half * 8 + piece)) = make_uint4(
+          packed[piece * 4], packed[piece * 4 + 1], packed[piece * 4 + 2], packed[piece * 4 + 3]);
     }
     async_proxy_fence();
     tc_fence_before();
-    __syncthreads();
+    if (__syncthreads_or(failed ? 1 : 0)) {
+      failed = true;
+      break;
+    }
     // ---- O' = P V, runs under the next block's softmax ----
     if (tid == 0) {
       tc_fence_after();
@@ -507,7 +641,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
       for (int k = 0; k < kExactKeep; ++k) {
         wide[k] = q64[k];
       }
-      wide[kExactKeep] = dropped;
+      wide[kExactKeep] = __float_as_uint(dropped);
     }
   }
   __syncthreads();
@@ -582,13 +716,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
   }
   if constexpr (kMode == 2) {
     const uint64_t* wide = reinterpret_cast<const uint64_t*>(s_p) + row * (kExactKeep + 1);
-    dropped = wide[kExactKeep] > dropped ? wide[kExactKeep] : dropped;
+    dropped = fmaxf(dropped, __uint_as_float(static_cast<uint32_t>(wide[kExactKeep])));
 #pragma unroll
     for (int k = 0; k < kExactKeep; ++k) {
       const uint64_t candidate = wide[k];
       const uint64_t lost =
           candidate > q64[kExactKeep - 1] ? queue_insert64(q64, candidate) : candidate;
-      dropped = lost > dropped ? lost : dropped;
+      if (lost != 0ull) {
+        dropped = fmaxf(dropped, key32_to_float(static_cast<uint32_t>(lost >> 32)));
+      }
     }
     // [batch, kv head, position, G lanes, 16 kept + best dropped] for the second kernel
     uint64_t* list = a.candidates +
@@ -598,7 +734,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
     for (int k = 0; k < kExactKeep; ++k) {
       list[k] = q64[k];
     }
-    list[kExactKeep] = dropped;
+    list[kExactKeep] =
+        dropped == -INFINITY ? 0ull : static_cast<uint64_t>(ordered_key32(dropped)) << 32;
   }
 }
 
