@@ -27,6 +27,9 @@
 // columns j % G == lane, and a second kernel re-scores that short list in the
 // fixed fp32 order shared with the CPU oracle and emits the exact top-m.
 
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
 #include "ckv_device.cuh"
 
 namespace ckv {
@@ -40,9 +43,11 @@ constexpr int kExactKeep = 16;
 constexpr uint32_t kBarrierPolls = 1u << 22;
 
 __device__ __forceinline__ uint32_t core_offset(int row, int chunk) {
-  // 8 rows x 16 bytes form one contiguous 128-byte core matrix; the 16 chunks
-  // of a row group are adjacent, row groups are 2048 bytes apart.
-  return static_cast<uint32_t>((row >> 3) * 2048 + chunk * 128 + (row & 7) * 16);
+  // 8 rows x 16 bytes form one contiguous 128-byte core matrix; the row groups of
+  // one 16-byte column chunk are adjacent (so a chunk is 128 rows x 16 B = 2048 B,
+  // exactly what one slice of the K/V tensor-map box writes), chunks are 2048
+  // bytes apart.
+  return static_cast<uint32_t>(chunk * 2048 + row * 16);
 }
 
 __device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t leading_bytes,
@@ -94,6 +99,32 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
   }
 }
 
+__device__ __forceinline__ void tmem_load64(uint32_t taddr, float (&v)[64]) {
+  uint32_t r[64];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,"
+      "%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,"
+      "%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]),
+        "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]),
+        "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
+        "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+        "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]),
+        "=r"(r[63])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) {
+    v[i] = __uint_as_float(r[i]);
+  }
+}
+
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -119,6 +150,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
   }
   return false;
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+// One 128-row x 128-column bf16 tile (rows row0.. of one KV head) into shared memory
+// in the operand layout; rows past the end of the sequence arrive as zeros.  The
+// tensor map's dimensions are (8 elements, rows, 16 column chunks, KV heads, batch).
+__device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                              int row0, int kv_head, int batch) {
+  mbar_expect_tx(bar, kTileBytes);
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
+      "l"(map), "r"(0), "r"(row0), "r"(0), "r"(kv_head), "r"(batch), "r"(bar)
+      : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() {
@@ -224,11 +273,13 @@ struct PrefillSmem {
   static constexpr int kExchange = 6 * kTileBytes;  // float [2][128] row maxima / sums
   static constexpr int kFloors = kExchange + 2 * kPfRows * 4;  // uint32 [2][128] list floors
   static constexpr int kBars = kFloors + 2 * kPfRows * 4;
-  static constexpr int kTotal = kBars + 64;
+  static constexpr int kTotal = kBars + 64;  // 7 barriers and the TMEM base slot
 };
 
 template <int kGroup, int kMode>
-__global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefill_args a) {
+__global__ void __launch_bounds__(kPfThreads, 1)
+    prefill_kernel(const ckv_prefill_args a, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* s_q = smem + PrefillSmem::kQ;
   uint8_t* s_k = smem + PrefillSmem::kK;
@@ -237,7 +288,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
   float* exchange = reinterpret_cast<float*>(smem + PrefillSmem::kExchange);
   uint32_t* floor_exchange = reinterpret_cast<uint32_t*>(smem + PrefillSmem::kFloors);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PrefillSmem::kBars);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
 
   constexpr int kPositions = kPfRows / kGroup;
   const int tid = threadIdx.x;
@@ -245,7 +296,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
   const int row = tid & (kPfRows - 1);
   const int half = tid >> 7;            // which 64 of the 128 columns / output dims
   const int col0 = half * 64;
-  const int tile = blockIdx.x;
+  const int tile = gridDim.x - 1 - blockIdx.x;  // longest rows first
   const int kv_head = blockIdx.y;
   const int batch = blockIdx.z;
   const int pos0 = tile * kPositions;
@@ -257,11 +308,22 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
   const uint32_t bar_s0 = smem_u32(bars);
   const uint32_t bar_s1 = smem_u32(bars + 1);
   const uint32_t bar_o = smem_u32(bars + 2);
+  const uint32_t bar_k = smem_u32(bars + 3);  // two barriers: K buffer filled
+  const uint32_t bar_v = smem_u32(bars + 5);  // two barriers: V buffer filled
+  const int last_pos = min(length, pos0 + kPositions) - 1;
+  const int blocks = last_pos / kPfKeys + 1;
   if (tid == 0) {
-    mbar_init(bar_s0, 1);
-    mbar_init(bar_s1, 1);
-    mbar_init(bar_o, 1);
+#pragma unroll
+    for (int i = 0; i < 7; ++i) {
+      mbar_init(bar_s0 + 8 * i, 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tma_load_tile(smem_u32(s_k), &map_k, bar_k, 0, kv_head, batch);
+    tma_load_tile(smem_u32(s_v), &map_v, bar_v, 0, kv_head, batch);
+    if (blocks > 1) {
+      tma_load_tile(smem_u32(s_k) + kTileBytes, &map_k, bar_k + 8, kPfKeys, kv_head, batch);
+    }
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -273,15 +335,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
 
   const __nv_bfloat16* q_base = reinterpret_cast<const __nv_bfloat16*>(a.query) +
                                 batch * a.q_batch_stride;
-  const __nv_bfloat16* k_base = reinterpret_cast<const __nv_bfloat16*>(a.key) +
-                                batch * a.k_batch_stride + kv_head * a.k_head_stride;
-  const __nv_bfloat16* v_base = reinterpret_cast<const __nv_bfloat16*>(a.value) +
-                                batch * a.v_batch_stride + kv_head * a.v_head_stride;
-
   // ---- stage Q once: row r = (position pos0 + r / G, head kv_head*G + r % G) ----
   for (int index = tid; index < kPfRows * 16; index += kPfThreads) {
-    const int r = index >> 4;
-    const int chunk = index & 15;
+    const int r = (index & 7) | ((index >> 7) << 3);
+    const int chunk = (index >> 3) & 15;
     const int pos = pos0 + r / kGroup;
     const int head = kv_head * kGroup + r % kGroup;
     const bool live = pos < length;
@@ -289,20 +346,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
         q_base + (live ? pos : 0) * a.q_row_stride + head * a.q_head_stride + chunk * 8;
     cp_async16(smem_u32(s_q) + core_offset(r, chunk), src, live ? 16u : 0u);
   }
-  auto stage_tile = [&](uint8_t* dst, const __nv_bfloat16* base, int64_t row_stride, int key0) {
-    for (int index = tid; index < kPfKeys * 16; index += kPfThreads) {
-      const int r = index >> 4;
-      const int chunk = index & 15;
-      const int key = key0 + r;
-      const bool live = key < length;
-      cp_async16(smem_u32(dst) + core_offset(r, chunk),
-                 base + (live ? key : 0) * row_stride + chunk * 8, live ? 16u : 0u);
-    }
-  };
-  const int last_pos = min(length, pos0 + kPositions) - 1;
-  const int blocks = last_pos / kPfKeys + 1;
-  stage_tile(s_k, k_base, a.k_row_stride, 0);
-  stage_tile(s_v, v_base, a.v_row_stride, 0);
   cp_async_commit();
   cp_async_wait<0>();
   async_proxy_fence();
@@ -318,15 +361,21 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
     const int buffer = block & 1;
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-      const uint64_t desc_q = smem_descriptor(smem_u32(s_q) + ks * 256, 128, 2048);
+      const uint64_t desc_q = smem_descriptor(smem_u32(s_q) + ks * 4096, 2048, 128);
       const uint64_t desc_k =
-          smem_descriptor(smem_u32(s_k) + buffer * kTileBytes + ks * 256, 128, 2048);
+          smem_descriptor(smem_u32(s_k) + buffer * kTileBytes + ks * 4096, 2048, 128);
       umma(tmem + buffer * 128u, desc_q, desc_k, idesc_qk, ks > 0 ? 1u : 0u);
     }
     umma_commit(buffer ? bar_s1 : bar_s0);
   };
+  bool failed = false;
   if (tid == 0) {
-    issue_qk(0);
+    if (mbar_wait(bar_k, 0)) {
+      tc_fence_after();
+      issue_qk(0);
+    } else {
+      failed = true;
+    }
   }
 
   float out[64];
@@ -356,7 +405,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
       q64[k] = 0ull;
     }
   }
-  bool failed = false;
   const int limit = row_live ? min(row_pos, length - 1) : -1;  // last visible key
 
   auto fold_output = [&](int block) {
@@ -365,44 +413,28 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
       failed = true;
     }
     tc_fence_after();
+    float o[64];
+    tmem_load64(lane_base + 256u + col0, o);
 #pragma unroll
-    for (int chunk = 0; chunk < 2; ++chunk) {
-      float o[32];
-      tmem_load32(lane_base + 256u + col0 + chunk * 32, o);
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        out[chunk * 32 + c] = out[chunk * 32 + c] * pending_corr + o[c];
-      }
+    for (int c = 0; c < 64; ++c) {
+      out[c] = out[c] * pending_corr + o[c];
     }
   };
 
   for (int block = 0; block < blocks; ++block) {
     const int key0 = block * kPfKeys;
     const int buffer = block & 1;
-    // K buffer of block+1 was last read by Q.K^T of block-1, which every thread has
-    // already waited for
-    if (block + 1 < blocks) {
-      stage_tile(s_k + (buffer ^ 1) * kTileBytes, k_base, a.k_row_stride, key0 + kPfKeys);
-    }
-    cp_async_commit();
     if (!mbar_wait(buffer ? bar_s1 : bar_s0, (block >> 1) & 1)) {
       failed = true;
     }
     tc_fence_after();
     // ---- this thread's 64 raw scores, kept in registers ----
     float s[64];
-    {
-      float part[32];
-      tmem_load32(lane_base + buffer * 128u + col0, part);
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        s[c] = part[c];
-      }
-      tmem_load32(lane_base + buffer * 128u + col0 + 32, part);
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        s[32 + c] = part[c];
-      }
+    tmem_load64(lane_base + buffer * 128u + col0, s);
+    // its K buffer is free again: fetch the block after next into it
+    if (tid == 0 && block + 2 < blocks) {
+      tma_load_tile(smem_u32(s_k) + buffer * kTileBytes, &map_k, bar_k + 8 * buffer,
+                    key0 + 2 * kPfKeys, kv_head, batch);
     }
     // interior block: every key is visible to every row of the tile.  Elsewhere the
     // causal mask is applied once, in place.
@@ -430,8 +462,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
       }
       floor_exchange[half * kPfRows + row] = floor_key;
     }
-    cp_async_wait<0>();  // K of block+1 and V of this block have landed
-    async_proxy_fence();
     tc_fence_before();
     if (__syncthreads_or(failed ? 1 : 0)) {
       failed = true;
@@ -439,8 +469,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
     }
     // ---- next block's S = Q K^T starts now, under this block's softmax ----
     if (tid == 0 && block + 1 < blocks) {
-      tc_fence_after();
-      issue_qk(block + 1);
+      if (mbar_wait(bar_k + 8 * (buffer ^ 1), ((block + 1) >> 1) & 1)) {
+        tc_fence_after();
+        issue_qk(block + 1);
+      } else {
+        failed = true;
+      }
     }
     const float tile_max = fmaxf(half_max, exchange[(half ^ 1) * kPfRows + row]);
     const bool sink_free = key0 >= a.num_sink;
@@ -577,10 +611,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
       fold_output(block - 1);
     }
     pending_corr = corr;  // goes with this block's P.V result
-    if (block + 1 < blocks) {
-      stage_tile(s_v + (buffer ^ 1) * kTileBytes, v_base, a.v_row_stride, key0 + kPfKeys);
+    if (tid == 0 && block + 1 < blocks) {
+      tma_load_tile(smem_u32(s_v) + (buffer ^ 1) * kTileBytes, &map_v, bar_v + 8 * (buffer ^ 1),
+                    key0 + kPfKeys, kv_head, batch);
     }
-    cp_async_commit();
 #pragma unroll
     for (int piece = 0; piece < 8; ++piece) {
       *reinterpret_cast<uint4*>(s_p + core_offset(row, half * 8 + piece)) = make_uint4(
@@ -593,13 +627,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
       break;
     }
     // ---- O' = P V, runs under the next block's softmax ----
-    if (tid == 0) {
+    if (tid == 0 && !mbar_wait(bar_v + 8 * buffer, (block >> 1) & 1)) {
+      failed = true;  // seen by every thread at the next barrier
+    } else if (tid == 0) {
       tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        const uint64_t desc_p = smem_descriptor(smem_u32(s_p) + ks * 256, 128, 2048);
+        const uint64_t desc_p = smem_descriptor(smem_u32(s_p) + ks * 4096, 2048, 128);
         const uint64_t desc_v =
-            smem_descriptor(smem_u32(s_v) + buffer * kTileBytes + ks * 4096, 2048, 128);
+            smem_descriptor(smem_u32(s_v) + buffer * kTileBytes + ks * 256, 128, 2048);
         umma(tmem + 256u, desc_p, desc_v, idesc_pv, ks > 0 ? 1u : 0u);
       }
       umma_commit(bar_o);
@@ -608,7 +644,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const ckv_prefil
   if (!failed) {
     fold_output(blocks - 1);
   }
-  cp_async_wait<0>();
   tc_fence_before();
   const int any_failed = __syncthreads_or(failed ? 1 : 0);
   if (warp == 0) {
@@ -913,14 +948,63 @@ __global__ void __launch_bounds__(256) exact_rescan_kernel(const ckv_prefill_arg
 
 namespace {
 
+// The driver's tensor-map encoder, looked up through the runtime so that the
+// library does not link against the driver library.
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+  static PFN_cuTensorMapEncodeTiled_v12000 encoder = [] {
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult found;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &found) !=
+            cudaSuccess ||
+        found != cudaDriverEntryPointSuccess) {
+      entry = nullptr;
+    }
+    return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(entry);
+  }();
+  return encoder;
+}
+
+// K or V [batch, rows, kv heads, 128] bf16 seen as (8 elements, rows, 16 chunks of
+// 16 bytes, kv heads, batch): one box of (8, 128, 16, 1, 1) lands in shared memory as
+// 16 chunks of 128 rows x 16 bytes, which is the tensor-core operand layout.
+bool tile_map(CUtensorMap* map, const void* base, const ckv_prefill_args& a, int64_t row_stride,
+              int64_t head_stride, int64_t batch_stride) {
+  const auto encoder = tensor_map_encoder();
+  if (encoder == nullptr || (reinterpret_cast<uintptr_t>(base) & 15u) != 0) {
+    return false;
+  }
+  const uint64_t row_bytes = static_cast<uint64_t>(row_stride) * 2;
+  // a dimension of extent 1 never uses its stride; give it a legal one
+  const uint64_t head_bytes =
+      a.kv_heads > 1 ? static_cast<uint64_t>(head_stride) * 2 : static_cast<uint64_t>(kHeadDim) * 2;
+  const uint64_t batch_bytes =
+      a.batch > 1 ? static_cast<uint64_t>(batch_stride) * 2 : row_bytes * static_cast<uint64_t>(a.seq_len);
+  if (row_stride <= 0 || (row_bytes & 15u) || (head_bytes & 15u) || (batch_bytes & 15u)) {
+    return false;
+  }
+  const cuuint64_t extent[5] = {8, static_cast<cuuint64_t>(a.seq_len), 16,
+                                static_cast<cuuint64_t>(a.kv_heads), static_cast<cuuint64_t>(a.batch)};
+  const cuuint64_t strides[4] = {row_bytes, 16, head_bytes, batch_bytes};
+  const cuuint32_t box[5] = {8, kPfKeys, 16, 1, 1};
+  const cuuint32_t steps[5] = {1, 1, 1, 1, 1};
+  return encoder(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), extent, strides,
+                 box, steps, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int kGroup>
 cudaError_t launch_for_group(const ckv_prefill_args& a, cudaStream_t stream) {
   constexpr int kSmem = PrefillSmem::kTotal;
   const dim3 grid((a.seq_len + kPfRows / kGroup - 1) / (kPfRows / kGroup), a.kv_heads, a.batch);
+  CUtensorMap map_k, map_v;
+  if (!tile_map(&map_k, a.key, a, a.k_row_stride, a.k_head_stride, a.k_batch_stride) ||
+      !tile_map(&map_v, a.value, a, a.v_row_stride, a.v_head_stride, a.v_batch_stride)) {
+    return cudaErrorInvalidValue;
+  }
   auto run = [&](auto kernel) -> cudaError_t {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (err != cudaSuccess) return err;
-    kernel<<<grid, kPfThreads, kSmem, stream>>>(a);
+    kernel<<<grid, kPfThreads, kSmem, stream>>>(a, map_k, map_v);
     return cudaGetLastError();
   };
   if (a.mode == 0) return run(prefill_kernel<kGroup, 0>);
