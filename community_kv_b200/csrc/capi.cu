@@ -8,6 +8,8 @@ cudaError_t launch_select(const ckv_layer_args& a, cudaStream_t stream);
 cudaError_t launch_resolve(const ckv_layer_args& a, cudaStream_t stream);
 cudaError_t launch_attention(const ckv_layer_args& a, cudaStream_t stream);
 cudaError_t launch_merge_update(const ckv_layer_args& a, cudaStream_t stream);
+bool fused_layer_supported(const ckv_layer_args& a);
+cudaError_t launch_fused_layer(const ckv_layer_args& a, cudaStream_t stream);
 int attention_smem_bytes();
 cudaError_t launch_prefill(const ckv_prefill_args& a, cudaStream_t stream);
 
@@ -151,6 +153,10 @@ int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream) {
   status = ckv::select_device(args);
   if (status != CKV_OK) return status;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (ckv::fused_layer_supported(*args)) {
+    // one cluster launch per layer: scoring, selection, attention, merge and update
+    return ckv::launched(ckv::launch_fused_layer(*args, stream));
+  }
   status = ckv::launched(ckv::launch_score(*args, stream));
   if (status != CKV_OK) return status;
   status = ckv::launched(ckv::launch_select(*args, stream));

@@ -1,0 +1,127 @@
+// One launch per decode layer: a thread-block cluster per (sequence, retrieval head).
+//
+// Grid (splits, batch*R), cluster (splits, 1, 1), 128 threads, three CTAs per SM.
+// The CTAs of a cluster are co-scheduled, so they can hand work to one another
+// through the hardware cluster barrier instead of through kernel boundaries:
+//
+//   1. every CTA scores a 1/splits share of the unit's centroid rows and writes
+//      the fp16 scores to the workspace;                      -- cluster barrier --
+//   2. every CTA runs the (cheap, deterministic) budgeted selection over all of
+//      the unit's scores, so each one knows the descriptors without any further
+//      exchange; rank 0 reports them to the workspace; each CTA resolves only the
+//      logical tokens of its own attention split to cache rows;
+//   3. every CTA gathers and attends to its split and writes its partial
+//      (acc, max, sum) rows and neighbour candidates;         -- cluster barrier --
+//   4. rank 0 merges the partials, writes the output and applies the online
+//      graph update; the other CTAs have already left.
+//
+// The result is bit for bit the one of the four stand-alone kernels: the same
+// device functions run in the same order on the same data.  The path needs one
+// graph per retrieval head (a graph shared by several heads is updated by its
+// leader while followers may still be reading it, which only a kernel boundary
+// orders) and descriptors that fit the selection's shared-memory stash.
+
+#include "merge_update.cuh"
+#include "score_select.cuh"
+#include "segmented_attention.cuh"
+
+namespace ckv {
+
+constexpr int kFusedThreads = 128;
+constexpr int kFusedSmem =
+    AttnSmem::kTotal > static_cast<int>(sizeof(SelectSmem)) ? AttnSmem::kTotal
+                                                            : static_cast<int>(sizeof(SelectSmem));
+static_assert(16 * kHeadDim * 4 <= kFusedSmem, "the staged query group must fit");
+
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int kBlocks>
+__global__ void __launch_bounds__(kFusedThreads, 3) decode_cluster_kernel(const ckv_layer_args a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ UpdateDecision decision;
+  __shared__ float lse_s;
+  const int flat = blockIdx.y;
+  const int split = blockIdx.x;  // == rank in the cluster
+  pdl_release_dependents();
+  pdl_wait_for_predecessor();  // the query and last step's state come from upstream
+
+  // ---- 1. centroid scores: this CTA's share of the unit's 16-row groups ----
+  {
+    const int groups = (score_limit(a, flat) + 15) / 16;
+    const int first = static_cast<int>(static_cast<int64_t>(split) * groups / a.splits);
+    const int last = static_cast<int>(static_cast<int64_t>(split + 1) * groups / a.splits);
+    score_groups<kFusedThreads>(a, flat, first, last, reinterpret_cast<float*>(smem));
+  }
+  __threadfence();
+  cluster_arrive();
+  cluster_wait();
+
+  // ---- 2. selection (every CTA, same result) and this split's cache rows ----
+  {
+    const int steps_total = a.token_budget / kStepTokens;
+    const int step_begin = static_cast<int>(static_cast<int64_t>(split) * steps_total / a.splits);
+    const int step_end = static_cast<int>(static_cast<int64_t>(split + 1) * steps_total / a.splits);
+    select_unit<kFusedThreads>(a, flat, *reinterpret_cast<SelectSmem*>(smem), split == 0,
+                               step_begin * kStepTokens, step_end * kStepTokens);
+  }
+  __syncthreads();  // positions written above are read by other threads of this CTA
+
+  // ---- 3. gather + attention over this split ----
+  attention_split<kBlocks>(a, flat, split, smem);
+  __threadfence();
+  cluster_arrive();
+  if (split != 0) {
+    return;
+  }
+  cluster_wait();
+
+  // ---- 4. merge, output, online update ----
+  merge_update_unit(a, flat, kFusedThreads / 32 - 1, decision, lse_s);
+}
+
+bool fused_layer_supported(const ckv_layer_args& a) {
+  const int budget = a.token_budget - a.num_sink - 1;
+  const int descriptors = a.descriptor_capacity < budget ? a.descriptor_capacity : budget;
+  return a.graphs == a.retrieval_heads && a.splits >= 1 && a.splits <= 8 &&
+         descriptors <= kDescStash &&
+         !(a.flags & (CKV_FLAG_ATTENTION_ONLY | CKV_FLAG_UPDATE_ONLY | CKV_FLAG_UNFUSED));
+}
+
+cudaError_t launch_fused_layer(const ckv_layer_args& a, cudaStream_t stream) {
+  static bool configured[64] = {};
+  const int device = a.device >= 0 && a.device < 64 ? a.device : 0;
+  if (!configured[device]) {
+    cudaError_t err = cudaFuncSetAttribute(decode_cluster_kernel<1>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmem);
+    if (err != cudaSuccess) return err;
+    err = cudaFuncSetAttribute(decode_cluster_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kFusedSmem);
+    if (err != cudaSuccess) return err;
+    configured[device] = true;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(a.splits, a.batch * a.retrieval_heads);
+  config.blockDim = dim3(kFusedThreads);
+  config.dynamicSmemBytes = kFusedSmem;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = a.splits;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = 2;
+  if (a.group_size > 8) {
+    return cudaLaunchKernelEx(&config, decode_cluster_kernel<2>, a);
+  }
+  return cudaLaunchKernelEx(&config, decode_cluster_kernel<1>, a);
+}
+
+}  // namespace ckv

@@ -148,6 +148,8 @@ STATIC_MAX_SPLITS = 8
 STATIC_MAX_GROUP = 8
 FLAG_ATTENTION_ONLY = 2
 FLAG_UPDATE_ONLY = 4
+# ckv_decode_layer: four stand-alone kernels instead of the single cluster launch
+FLAG_UNFUSED = 8
 DEV_WAIT_TIMEOUT = 1
 PARTIAL_STRIDE = 132
 
@@ -226,6 +228,7 @@ __all__ = [
     "ENTRY_POINTS",
     "FLAG_ATTENTION_ONLY",
     "FLAG_SKIP_UPDATE",
+    "FLAG_UNFUSED",
     "FLAG_UPDATE_ONLY",
     "LayerArgs",
     "NativeError",

@@ -11,6 +11,8 @@ Tensors may carry a leading batch axis (see ``community_kv_b200.state``).
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from community_kv_b200 import native
@@ -196,7 +198,7 @@ def _attention_args(
         topk_scores=native.pointer(workspace.topk_scores),
         topk_positions=native.pointer(workspace.topk_positions),
         status=native.pointer(workspace.status),
-        flags=0 if update is not None else native.FLAG_SKIP_UPDATE,
+        flags=(0 if update is not None else native.FLAG_SKIP_UPDATE) | _layout_flags(),
         assigned=native.pointer(update.assigned_communities) if update is not None else None,
         overflow=native.pointer(update.overflow) if update is not None else None,
     )
@@ -482,6 +484,14 @@ def segmented_attention_static(
     )
     native.call("ckv_segmented_attention_static", args, native.current_stream(device))
     return workspace.output, workspace.lse, workspace.topk_scores, workspace.topk_positions
+
+
+def _layout_flags() -> int:
+    """``CKV_UNFUSED=1`` in the environment selects the four stand-alone kernels for
+    ``ckv_decode_layer`` instead of the single cluster launch (same results; a
+    debugging and A/B-timing switch)."""
+
+    return native.FLAG_UNFUSED if os.environ.get("CKV_UNFUSED") == "1" else 0
 
 
 def build_layer_args(

@@ -63,6 +63,8 @@ typedef enum ckv_status {
 #define CKV_FLAG_ATTENTION_ONLY 2 /* ckv_segmented_attention: launch only the gather+attention
                                      kernel on the positions already in the workspace (no
                                      position resolution, no merge); for kernel timing */
+#define CKV_FLAG_UNFUSED 8        /* ckv_decode_layer: run the four stand-alone kernels even when
+                                     the single cluster launch is available (same results) */
 
 typedef struct ckv_layer_args {
   /* ---- geometry ---- */

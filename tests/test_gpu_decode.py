@@ -73,6 +73,15 @@ def test_single_layer_config0_parity(aggregation):
     _run_sequence(layer, config, steps=4, seed=100)
 
 
+def test_unfused_kernels_give_the_same_result(monkeypatch):
+    """The four stand-alone kernels and the single cluster launch are the same path."""
+
+    monkeypatch.setenv("CKV_UNFUSED", "1")
+    layer = make_layer(seed=0, seq_len=8192, communities=64, max_decode_tokens=8, aggregation="query_group")
+    config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation="query_group")
+    _run_sequence(layer, config, steps=4, seed=100)
+
+
 def test_many_small_communities_and_delta_chains():
     """Mean community size ~16 (the tuned regime): many descriptors, decode deltas get re-selected."""
 
