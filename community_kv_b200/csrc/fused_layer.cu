@@ -28,10 +28,9 @@
 namespace ckv {
 
 constexpr int kFusedThreads = 128;
-constexpr int kFusedSmem =
-    AttnSmem::kTotal > static_cast<int>(sizeof(SelectSmem)) ? AttnSmem::kTotal
-                                                            : static_cast<int>(sizeof(SelectSmem));
-static_assert(16 * kHeadDim * 4 <= kFusedSmem, "the staged query group must fit");
+constexpr int kFusedSmem = AttnSmem::kTotal > static_cast<int>(sizeof(ClusterSelectSmem))
+                               ? AttnSmem::kTotal
+                               : static_cast<int>(sizeof(ClusterSelectSmem));
 
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -50,24 +49,28 @@ __global__ void __launch_bounds__(kFusedThreads, 3) decode_cluster_kernel(const 
   pdl_release_dependents();
   pdl_wait_for_predecessor();  // the query and last step's state come from upstream
 
-  // ---- 1. centroid scores: this CTA's share of the unit's 16-row groups ----
+  // ---- 1. centroid scores: this CTA's share of the unit's 16-row groups; the keys
+  // stay in shared memory and are counted into the slice's histogram on the way ----
+  ClusterSelectSmem& sm = *reinterpret_cast<ClusterSelectSmem*>(smem);
+  const int groups = (score_limit(a, flat) + 15) / 16;
+  const int first_group = static_cast<int>(static_cast<int64_t>(split) * groups / a.splits);
+  const int last_group = static_cast<int>(static_cast<int64_t>(split + 1) * groups / a.splits);
+  cluster_select_begin<kFusedThreads>(sm);
   {
-    const int groups = (score_limit(a, flat) + 15) / 16;
-    const int first = static_cast<int>(static_cast<int64_t>(split) * groups / a.splits);
-    const int last = static_cast<int>(static_cast<int64_t>(split + 1) * groups / a.splits);
-    score_groups<kFusedThreads>(a, flat, first, last, reinterpret_cast<float*>(smem));
+    const ScoreSlice slice = {sm.key, sm.size, sm.hist_mass, sm.hist_count, first_group * 16};
+    score_groups<kFusedThreads>(a, flat, first_group, last_group, sm.query, &slice);
   }
-  __threadfence();
-  cluster_arrive();
-  cluster_wait();
+  __syncthreads();
 
-  // ---- 2. selection (every CTA, same result) and this split's cache rows ----
+  // ---- 2. selection across the cluster, then this split's cache rows ----
   {
     const int steps_total = a.token_budget / kStepTokens;
     const int step_begin = static_cast<int>(static_cast<int64_t>(split) * steps_total / a.splits);
     const int step_end = static_cast<int>(static_cast<int64_t>(split + 1) * steps_total / a.splits);
-    select_unit<kFusedThreads>(a, flat, *reinterpret_cast<SelectSmem*>(smem), split == 0,
-                               step_begin * kStepTokens, step_end * kStepTokens);
+    const int row0 = first_group * 16;
+    const int rows = min(score_limit(a, flat), last_group * 16) - row0;
+    select_cluster<kFusedThreads>(a, flat, sm, split, a.splits, row0, rows,
+                                  step_begin * kStepTokens, step_end * kStepTokens);
   }
   __syncthreads();  // positions written above are read by other threads of this CTA
 
@@ -88,7 +91,7 @@ bool fused_layer_supported(const ckv_layer_args& a) {
   const int budget = a.token_budget - a.num_sink - 1;
   const int descriptors = a.descriptor_capacity < budget ? a.descriptor_capacity : budget;
   return a.graphs == a.retrieval_heads && a.splits >= 1 && a.splits <= 8 &&
-         descriptors <= kDescStash &&
+         descriptors <= kDescStash && a.community_capacity <= kStash &&
          !(a.flags & (CKV_FLAG_ATTENTION_ONLY | CKV_FLAG_UPDATE_ONLY | CKV_FLAG_UNFUSED));
 }
 

@@ -41,9 +41,22 @@ __device__ __forceinline__ int score_limit(const ckv_layer_args& a, int flat) {
 // it with the same arguments (the query group is staged in `q_s`, 16 * 128 floats
 // of shared memory, behind block barriers); a warp takes every (kThreads / 32)-th
 // group and keeps the next group's loads in flight while it computes.
+//
+// With `slice` set, the keys and sizes of the scored rows are also kept in shared
+// memory (index row - slice->row0) and counted into the slice's first-pass
+// histogram, which is what a cluster-wide selection starts from.
+struct ScoreSlice {
+  uint16_t* key;     // order-preserving 16-bit key, 0 for dead rows
+  int* size;         // community size, 0 for dead rows
+  int* hist_mass;    // 256 bins over the high key byte, weighted by size
+  int* hist_count;
+  int row0;
+};
+
 template <int kThreads>
 __device__ __forceinline__ void score_groups(const ckv_layer_args& a, int flat, int first_group,
-                                             int last_group, float* q_s) {
+                                             int last_group, float* q_s,
+                                             const ScoreSlice* slice_out = nullptr) {
   const int group = a.group_size;
   const int capacity = a.community_capacity;
   const int warp = threadIdx.x >> 5;
@@ -141,7 +154,17 @@ __device__ __forceinline__ void score_groups(const ckv_layer_args& a, int flat, 
     }
     if ((slice & 1) == 0 && row < limit) {
       const bool live = row < count && size > 0;
-      out[row] = __float2half_rn(live ? best : -INFINITY);
+      const __half rounded = __float2half_rn(live ? best : -INFINITY);
+      out[row] = rounded;
+      if (slice_out != nullptr) {
+        const int key = live ? ordered_key16(__half_as_ushort(rounded)) : 0;
+        slice_out->key[row - slice_out->row0] = static_cast<uint16_t>(key);
+        slice_out->size[row - slice_out->row0] = live ? size : 0;
+        if (live) {
+          atomicAdd(&slice_out->hist_mass[key >> 8], size);
+          atomicAdd(&slice_out->hist_count[key >> 8], 1);
+        }
+      }
     }
   }
 }
@@ -478,6 +501,321 @@ __device__ __forceinline__ void select_unit(const ckv_layer_args& a, int flat, S
   // Resolve every logical token of the budget to its cache row.
   // Two logical tokens per thread and pass, so that the two dependent global
   // reads of each (community tables, then the member list) overlap.
+  int32_t* positions = a.positions + static_cast<int64_t>(flat) * a.token_budget;
+  const int64_t graph_slot = static_cast<int64_t>(u.batch) * a.graphs + u.graph;
+  const int32_t* delta_sizes = a.delta_sizes + graph_slot * capacity;
+  const int32_t* offsets = a.member_offsets + graph_slot * (capacity + 1);
+  const int32_t* members = a.member_positions + graph_slot * a.member_capacity;
+  for (int base = token_begin; base < token_end; base += 2 * kThreads) {
+    int logical[2], community[2], member[2], direct[2];
+    bool lookup[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      logical[i] = base + i * kThreads + tid;
+      lookup[i] = false;
+      direct[i] = -1;
+      community[i] = 0;
+      member[i] = 0;
+      if (logical[i] >= token_end) {
+        continue;
+      }
+      if (logical[i] < a.num_sink) {
+        direct[i] = a.sink_positions[logical[i]];
+      } else if (logical[i] == a.token_budget - 1) {
+        direct[i] = a.current_position[graph_slot];
+      } else {
+        const int offset = logical[i] - a.num_sink;
+        int low = 0;
+        int high = descriptors;
+        while (low < high) {
+          const int middle = (low + high) >> 1;
+          if (search_ends[middle] <= offset) {
+            low = middle + 1;
+          } else {
+            high = middle;
+          }
+        }
+        if (low < descriptors) {
+          lookup[i] = true;
+          community[i] = search_comm[low];
+          member[i] = offset - (low > 0 ? search_ends[low - 1] : 0);
+        }
+      }
+    }
+    int delta_count[2], start[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      delta_count[i] = lookup[i] ? delta_sizes[community[i]] : 0;
+      start[i] = lookup[i] ? offsets[community[i]] : 0;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (lookup[i] && member[i] >= delta_count[i]) {
+        direct[i] = members[start[i] + member[i] - delta_count[i]];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (lookup[i] && member[i] < delta_count[i]) {
+        direct[i] = delta_member_position(a, graph_slot, community[i], member[i]);
+      }
+      if (logical[i] < token_end) {
+        positions[logical[i]] = direct[i];
+      }
+    }
+  }
+}
+
+
+// ---- selection spread over a thread-block cluster ----
+//
+// The CTAs of a cluster own contiguous, index-ordered slices of the unit's
+// communities (the rows each one scored).  Histograms and per-slice totals are
+// summed by reading the other CTAs' shared memory; every CTA ends up with the
+// complete descriptor list in its own shared memory, written there by the slices'
+// owners.  Same result as select_unit.
+__device__ __forceinline__ uint32_t cluster_address(const void* local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ int cluster_load(uint32_t address) {
+  int value;
+  asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(value) : "r"(address) : "memory");
+  return value;
+}
+__device__ __forceinline__ void cluster_store(uint32_t address, int value) {
+  asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(address), "r"(value) : "memory");
+}
+__device__ __forceinline__ void cluster_add(uint32_t address, int value) {
+  asm volatile("red.shared::cluster.add.s32 [%0], %1;" ::"r"(address), "r"(value) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+struct ClusterSelectSmem {
+  alignas(16) float query[16 * kHeadDim];  // staged query group (read with 16-byte loads)
+  uint16_t key[kStash];   // this CTA's slice
+  int size[kStash];
+  int hist_mass[256];     // slice histograms, read by the other CTAs
+  int hist_count[256];
+  int low_mass[256];
+  int low_count[256];
+  int sum_mass[256];      // cluster-wide sums (private)
+  int sum_count[256];
+  Quad scan_scratch[32];
+  Quad scan_total;        // this slice's (above, equal) counts and masses, read by the others
+  int stored_equal;       // stored at-threshold communities of all slices (every owner adds here)
+  int bin, mass, count, descriptors;
+  int32_t desc_comm[kDescStash];  // the complete list, filled by every slice's owner
+  int32_t desc_end[kDescStash];
+};
+
+// Zeroes what scoring accumulates into; call before score_groups, followed by a
+// block barrier (score_groups starts with one).
+template <int kThreads>
+__device__ __forceinline__ void cluster_select_begin(ClusterSelectSmem& sm) {
+  for (int bin = threadIdx.x; bin < 256; bin += kThreads) {
+    sm.hist_mass[bin] = 0;
+    sm.hist_count[bin] = 0;
+    sm.low_mass[bin] = 0;
+    sm.low_count[bin] = 0;
+  }
+  if (threadIdx.x == 0) {
+    sm.stored_equal = 0;
+  }
+}
+
+// `row0`, `rows`: this CTA's slice (rows it scored; the stash and the first-pass
+// histogram are already filled by score_groups).  Every CTA of the cluster calls
+// this; on return sm.desc_* hold all descriptors and the logical tokens
+// [token_begin, token_end) are resolved to cache rows.
+template <int kThreads>
+__device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat, ClusterSelectSmem& sm,
+                                               int rank, int ranks, int row0, int rows,
+                                               int token_begin, int token_end) {
+  const Unit u = make_unit(a, flat);
+  const int tid = threadIdx.x;
+  const int capacity = a.community_capacity;
+  const int active = max(0, min(capacity, a.community_counts[flat]));
+  const int tile_count = a.token_budget / kTile;
+  const int budget = a.token_budget - a.num_sink - 1;
+  const int limit = a.max_communities;
+  // the last slice also takes any active rows beyond the scored cover
+  if (rank == ranks - 1 && active > row0 + rows) {
+    const uint16_t* score_bits =
+        reinterpret_cast<const uint16_t*>(a.scores) + static_cast<int64_t>(flat) * capacity;
+    const int32_t* sizes = a.community_sizes + static_cast<int64_t>(flat) * capacity;
+    for (int c = row0 + rows + tid; c < active; c += kThreads) {
+      const int size = __ldg(sizes + c);
+      const int key = size > 0 ? ordered_key16(__ldcg(score_bits + c)) : 0;
+      sm.size[c - row0] = size > 0 ? size : 0;
+      sm.key[c - row0] = static_cast<uint16_t>(key);
+      if (size > 0) {
+        atomicAdd(&sm.hist_mass[key >> 8], size);
+        atomicAdd(&sm.hist_count[key >> 8], 1);
+      }
+    }
+    rows = active - row0;
+  }
+  rows = max(0, min(rows, active - row0));
+  cluster_sync_all();  // every slice's first-pass histogram is complete
+
+  auto sum_histograms = [&](const int* mass, const int* count) {
+    for (int bin = tid; bin < 256; bin += kThreads) {
+      int total_mass = 0;
+      int total_count = 0;
+      for (int r = 0; r < ranks; ++r) {
+        total_mass += cluster_load(cluster_address(mass + bin, r));
+        total_count += cluster_load(cluster_address(count + bin, r));
+      }
+      sm.sum_mass[bin] = total_mass;
+      sm.sum_count[bin] = total_count;
+    }
+    __syncthreads();
+  };
+  sum_histograms(sm.hist_mass, sm.hist_count);
+  if (tid < 32) {
+    find_threshold_bin(sm.sum_mass, sm.sum_count, budget, limit, 0, 0, &sm.bin, &sm.mass, &sm.count);
+  }
+  __syncthreads();
+  const int high_bin = sm.bin;
+  const int mass_above = sm.mass;
+  const int count_above = sm.count;
+  // Pass 2: low byte inside the chosen high bin, this slice only.
+  for (int i = tid; i < rows; i += kThreads) {
+    const int size = sm.size[i];
+    const int key = sm.key[i];
+    if (size > 0 && (key >> 8) == high_bin) {
+      atomicAdd(&sm.low_mass[key & 0xff], size);
+      atomicAdd(&sm.low_count[key & 0xff], 1);
+    }
+  }
+  cluster_sync_all();
+  sum_histograms(sm.low_mass, sm.low_count);
+  if (tid < 32) {
+    find_threshold_bin(sm.sum_mass, sm.sum_count, budget, limit, mass_above, count_above, &sm.bin,
+                       &sm.mass, &sm.count);
+  }
+  __syncthreads();
+  const int threshold = (high_bin << 8) | sm.bin;
+
+  // Pass 3: totals of this slice in index order.
+  const int per_thread = (rows + kThreads - 1) / kThreads;
+  const int first = min(rows, tid * per_thread);
+  const int last = min(rows, first + per_thread);
+  Quad mine = {0, 0, 0, 0};
+  for (int i = first; i < last; ++i) {
+    const int size = sm.size[i];
+    const int key = sm.key[i];
+    if (size > 0) {
+      if (key > threshold) {
+        mine.high_count += 1;
+        mine.high_mass += size;
+      } else if (key == threshold) {
+        mine.equal_count += 1;
+        mine.equal_mass += size;
+      }
+    }
+  }
+  Quad prefix = block_scan<kThreads / 32>(mine, sm.scan_scratch, &sm.scan_total);
+  cluster_sync_all();  // every slice's totals are published
+  Quad before = {0, 0, 0, 0};  // slices of lower rank
+  Quad all = {0, 0, 0, 0};
+  for (int r = 0; r < ranks; ++r) {
+    const uint32_t remote = cluster_address(&sm.scan_total, r);
+    const Quad other = {cluster_load(remote), cluster_load(remote + 4), cluster_load(remote + 8),
+                        cluster_load(remote + 12)};
+    all = quad_add(all, other);
+    if (r < rank) {
+      before = quad_add(before, other);
+    }
+  }
+  prefix = quad_add(prefix, before);
+  const int total_high_count = all.high_count;
+  const int total_high_mass = all.high_mass;
+
+  // Pass 4: this slice's descriptors, to the workspace and to every CTA's list.
+  int32_t* out_comm = a.communities + static_cast<int64_t>(flat) * a.descriptor_capacity;
+  int32_t* out_ends = a.cumulative_ends + static_cast<int64_t>(flat) * a.descriptor_capacity;
+  auto publish = [&](int descriptor, int community, int end) {
+    if (descriptor < a.descriptor_capacity) {
+      out_comm[descriptor] = community;
+      out_ends[descriptor] = end;
+      if (descriptor < kDescStash) {
+        for (int r = 0; r < ranks; ++r) {
+          cluster_store(cluster_address(sm.desc_comm + descriptor, r), community);
+          cluster_store(cluster_address(sm.desc_end + descriptor, r), end);
+        }
+      }
+    }
+  };
+  int stored_equal = 0;
+  for (int i = first; i < last; ++i) {
+    const int size = sm.size[i];
+    const int key = sm.key[i];
+    if (size <= 0) {
+      continue;
+    }
+    if (key > threshold) {
+      const int descriptor = prefix.high_count;
+      prefix.high_count += 1;
+      prefix.high_mass += size;
+      publish(descriptor, row0 + i, prefix.high_mass);
+    } else if (key == threshold) {
+      const int start = total_high_mass + prefix.equal_mass;
+      const int position = total_high_count + prefix.equal_count;
+      prefix.equal_count += 1;
+      prefix.equal_mass += size;
+      if (start < budget && (limit <= 0 || position < limit)) {
+        publish(position, row0 + i, min(budget, start + size));
+        stored_equal += 1;
+      }
+    }
+  }
+  if (stored_equal > 0) {
+    // counted into every CTA's own counter: nothing reads another CTA's shared
+    // memory after the barrier below, so a CTA may move on and reuse its own
+    for (int r = 0; r < ranks; ++r) {
+      cluster_add(cluster_address(&sm.stored_equal, r), stored_equal);
+    }
+  }
+  cluster_sync_all();  // the lists are complete everywhere
+  if (tid == 0) {
+    const int descriptors = min(a.descriptor_capacity, total_high_count + sm.stored_equal);
+    sm.descriptors = descriptors;
+    if (rank == 0) {
+      a.descriptor_counts[flat] = descriptors;
+      if (a.threshold_state != nullptr) {
+        a.threshold_state[static_cast<int64_t>(flat) * 4] = threshold;
+      }
+    }
+  }
+  __syncthreads();
+  const int descriptors = sm.descriptors;
+  const int32_t* search_ends = sm.desc_end;
+  const int32_t* search_comm = sm.desc_comm;
+
+  // First descriptor of every 64-token tile (one CTA reports them).
+  for (int tile = tid; rank == 0 && tile < tile_count; tile += kThreads) {
+    const int offset = max(tile * kTile - a.num_sink, 0);
+    int low = 0;
+    int high = descriptors;
+    while (low < high) {
+      const int middle = (low + high) >> 1;
+      if (search_ends[middle] <= offset) {
+        low = middle + 1;
+      } else {
+        high = middle;
+      }
+    }
+    a.tile_descriptors[static_cast<int64_t>(flat) * tile_count + tile] =
+        max(0, min(low, descriptors - 1));
+  }
+
+  // This CTA's logical tokens -> cache rows (two per thread and pass).
   int32_t* positions = a.positions + static_cast<int64_t>(flat) * a.token_budget;
   const int64_t graph_slot = static_cast<int64_t>(u.batch) * a.graphs + u.graph;
   const int32_t* delta_sizes = a.delta_sizes + graph_slot * capacity;
