@@ -606,7 +606,7 @@ struct ClusterSelectSmem {
   int sum_mass[256];      // cluster-wide sums (private)
   int sum_count[256];
   Quad scan_scratch[32];
-  Quad scan_total;        // this slice's (above, equal) counts and masses, read by the others
+  Quad scan_total;
   int stored_equal;       // stored at-threshold communities of all slices (every owner adds here)
   int bin, mass, count, descriptors;
   int32_t desc_comm[kDescStash];  // the complete list, filled by every slice's owner
@@ -663,20 +663,64 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
   rows = max(0, min(rows, active - row0));
   cluster_sync_all();  // every slice's first-pass histogram is complete
 
-  auto sum_histograms = [&](const int* mass, const int* count) {
-    for (int bin = tid; bin < 256; bin += kThreads) {
+  // Sum a pair of 256-bin histograms over the cluster.  Each thread owns
+  // 256 / kThreads bins and keeps every slice's values in registers: once the
+  // threshold bin is known they also give the totals above it, for all slices and
+  // for the slices before this one, without another exchange.
+  constexpr int kBins = 256 / kThreads;
+  static_assert(kBins * kThreads == 256, "thread count must divide 256");
+  constexpr int kMaxRanks = 8;
+  int part_mass[kBins][kMaxRanks];
+  int part_count[kBins][kMaxRanks];
+  auto gather = [&](const int* mass, const int* count) {
+#pragma unroll
+    for (int k = 0; k < kBins; ++k) {
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        const bool present = r < ranks;
+        part_mass[k][r] = present ? cluster_load(cluster_address(mass + tid + k * kThreads, r)) : 0;
+        part_count[k][r] = present ? cluster_load(cluster_address(count + tid + k * kThreads, r)) : 0;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kBins; ++k) {
       int total_mass = 0;
       int total_count = 0;
-      for (int r = 0; r < ranks; ++r) {
-        total_mass += cluster_load(cluster_address(mass + bin, r));
-        total_count += cluster_load(cluster_address(count + bin, r));
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        total_mass += part_mass[k][r];
+        total_count += part_count[k][r];
       }
-      sm.sum_mass[bin] = total_mass;
-      sm.sum_count[bin] = total_count;
+      sm.sum_mass[tid + k * kThreads] = total_mass;
+      sm.sum_count[tid + k * kThreads] = total_count;
     }
     __syncthreads();
   };
-  sum_histograms(sm.hist_mass, sm.hist_count);
+  // (count, mass) over the bins above `bin`: all slices, and the slices before this one
+  auto above = [&](int bin) {
+    Quad v = {0, 0, 0, 0};
+#pragma unroll
+    for (int k = 0; k < kBins; ++k) {
+      if (tid + k * kThreads > bin) {
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+          v.high_count += part_count[k][r];
+          v.high_mass += part_mass[k][r];
+          if (r < rank) {
+            v.equal_count += part_count[k][r];
+            v.equal_mass += part_mass[k][r];
+          }
+        }
+      }
+    }
+    Quad total;
+    block_scan<kThreads / 32>(v, sm.scan_scratch, &sm.scan_total);
+    total = sm.scan_total;
+    __syncthreads();  // scan_total is reused
+    return total;
+  };
+
+  gather(sm.hist_mass, sm.hist_count);
   if (tid < 32) {
     find_threshold_bin(sm.sum_mass, sm.sum_count, budget, limit, 0, 0, &sm.bin, &sm.mass, &sm.count);
   }
@@ -684,6 +728,7 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
   const int high_bin = sm.bin;
   const int mass_above = sm.mass;
   const int count_above = sm.count;
+  const Quad coarse = above(high_bin);
   // Pass 2: low byte inside the chosen high bin, this slice only.
   for (int i = tid; i < rows; i += kThreads) {
     const int size = sm.size[i];
@@ -694,15 +739,40 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
     }
   }
   cluster_sync_all();
-  sum_histograms(sm.low_mass, sm.low_count);
+  gather(sm.low_mass, sm.low_count);
   if (tid < 32) {
     find_threshold_bin(sm.sum_mass, sm.sum_count, budget, limit, mass_above, count_above, &sm.bin,
                        &sm.mass, &sm.count);
   }
   __syncthreads();
-  const int threshold = (high_bin << 8) | sm.bin;
+  const int low_bin = sm.bin;
+  const int threshold = (high_bin << 8) | low_bin;
+  const Quad fine = above(low_bin);
+  // at-threshold communities of the slices before this one: the owner of that bin knows
+  if (tid == (low_bin % kThreads)) {
+    const int k = low_bin / kThreads;
+    int count_before = 0;
+    int mass_before = 0;
+#pragma unroll
+    for (int kk = 0; kk < kBins; ++kk) {
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        if (kk == k && r < rank) {
+          count_before += part_count[kk][r];
+          mass_before += part_mass[kk][r];
+        }
+      }
+    }
+    sm.count = count_before;
+    sm.mass = mass_before;
+  }
+  __syncthreads();
+  const Quad before = {coarse.equal_count + fine.equal_count, coarse.equal_mass + fine.equal_mass,
+                       sm.count, sm.mass};
+  const int total_high_count = coarse.high_count + fine.high_count;
+  const int total_high_mass = coarse.high_mass + fine.high_mass;
 
-  // Pass 3: totals of this slice in index order.
+  // Pass 3: this slice in index order.
   const int per_thread = (rows + kThreads - 1) / kThreads;
   const int first = min(rows, tid * per_thread);
   const int last = min(rows, first + per_thread);
@@ -721,21 +791,7 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
     }
   }
   Quad prefix = block_scan<kThreads / 32>(mine, sm.scan_scratch, &sm.scan_total);
-  cluster_sync_all();  // every slice's totals are published
-  Quad before = {0, 0, 0, 0};  // slices of lower rank
-  Quad all = {0, 0, 0, 0};
-  for (int r = 0; r < ranks; ++r) {
-    const uint32_t remote = cluster_address(&sm.scan_total, r);
-    const Quad other = {cluster_load(remote), cluster_load(remote + 4), cluster_load(remote + 8),
-                        cluster_load(remote + 12)};
-    all = quad_add(all, other);
-    if (r < rank) {
-      before = quad_add(before, other);
-    }
-  }
   prefix = quad_add(prefix, before);
-  const int total_high_count = all.high_count;
-  const int total_high_mass = all.high_mass;
 
   // Pass 4: this slice's descriptors, to the workspace and to every CTA's list.
   int32_t* out_comm = a.communities + static_cast<int64_t>(flat) * a.descriptor_capacity;
@@ -815,17 +871,18 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
         max(0, min(low, descriptors - 1));
   }
 
-  // This CTA's logical tokens -> cache rows (two per thread and pass).
+  // This CTA's logical tokens -> cache rows (four per thread and pass, so that the
+  // dependent global reads of each overlap).
   int32_t* positions = a.positions + static_cast<int64_t>(flat) * a.token_budget;
   const int64_t graph_slot = static_cast<int64_t>(u.batch) * a.graphs + u.graph;
   const int32_t* delta_sizes = a.delta_sizes + graph_slot * capacity;
   const int32_t* offsets = a.member_offsets + graph_slot * (capacity + 1);
   const int32_t* members = a.member_positions + graph_slot * a.member_capacity;
-  for (int base = token_begin; base < token_end; base += 2 * kThreads) {
-    int logical[2], community[2], member[2], direct[2];
-    bool lookup[2];
+  for (int base = token_begin; base < token_end; base += 4 * kThreads) {
+    int logical[4], community[4], member[4], direct[4];
+    bool lookup[4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       logical[i] = base + i * kThreads + tid;
       lookup[i] = false;
       direct[i] = -1;
@@ -857,20 +914,20 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
         }
       }
     }
-    int delta_count[2], start[2];
+    int delta_count[4], start[4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       delta_count[i] = lookup[i] ? delta_sizes[community[i]] : 0;
       start[i] = lookup[i] ? offsets[community[i]] : 0;
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       if (lookup[i] && member[i] >= delta_count[i]) {
         direct[i] = members[start[i] + member[i] - delta_count[i]];
       }
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       if (lookup[i] && member[i] < delta_count[i]) {
         direct[i] = delta_member_position(a, graph_slot, community[i], member[i]);
       }
