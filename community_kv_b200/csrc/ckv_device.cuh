@@ -70,6 +70,56 @@ __device__ __forceinline__ void fp8x4_to_float(uint32_t word, float* out) {
   out[3] = b.y;
 }
 
+// Packed two-wide fp32 arithmetic (sm_100): each half is an IEEE round-to-nearest
+// operation, identical to the scalar instruction.
+__device__ __forceinline__ uint64_t pack_f32x2(float low, float high) {
+  uint64_t packed;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(packed) : "f"(low), "f"(high));
+  return packed;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t packed, float& low, float& high) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(low), "=f"(high) : "l"(packed));
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
+// Four e4m3 bytes -> two packed bf16 pairs (exact; NaN encodings are not handled:
+// the saturating centroid update never produces them).  The seven magnitude bits
+// go to the top of the bf16 exponent/mantissa field, which reads as the value
+// times 2^-120 with e4m3 subnormals landing on bf16 subnormals; a bf16 multiply
+// by 2^120 restores the scale.  Integer and FMA pipes only.
+__device__ __forceinline__ void e4m3x4_to_bf16x2(uint32_t word, uint32_t& low, uint32_t& high) {
+  const uint32_t spread_low = __byte_perm(word, 0u, 0x1404);   // (b1 << 24) | (b0 << 8)
+  const uint32_t spread_high = __byte_perm(word, 0u, 0x3424);  // (b3 << 24) | (b2 << 8)
+  const uint32_t tiny_low = ((spread_low >> 4) & 0x07f007f0u) | (spread_low & 0x80008000u);
+  const uint32_t tiny_high = ((spread_high >> 4) & 0x07f007f0u) | (spread_high & 0x80008000u);
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(low) : "r"(tiny_low), "r"(0x7b807b80u));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(high) : "r"(tiny_high), "r"(0x7b807b80u));
+}
+
+// acc += a.lo*b.lo ; acc += a.hi*b.hi  with bf16 operands, fp32 accumulate, each
+// step rounded once (the product of two bf16 values is exact in fp32).
+__device__ __forceinline__ float fma2_bf16(uint32_t a, uint32_t b, float acc) {
+  asm("{\n"
+      ".reg .b16 al, ah, bl, bh;\n"
+      "mov.b32 {al, ah}, %1;\n"
+      "mov.b32 {bl, bh}, %2;\n"
+      "fma.rn.f32.bf16 %0, al, bl, %0;\n"
+      "fma.rn.f32.bf16 %0, ah, bh, %0;\n"
+      "}\n"
+      : "+f"(acc)
+      : "r"(a), "r"(b));
+  return acc;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* pointer) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
 }

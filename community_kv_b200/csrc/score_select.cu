@@ -17,9 +17,8 @@
 namespace ckv {
 
 __global__ void __launch_bounds__(kScoreThreads, 2) score_kernel(const ckv_layer_args a) {
-  // query group as fp32, laid out [head][k][slice][4] so that the eight slices
-  // of one 16-byte read fall into different banks
-  __shared__ __align__(16) float q_s[16 * kHeadDim];
+  // query group as fp32, every value stored twice (see score_groups)
+  __shared__ __align__(16) float q_s[2 * 16 * kHeadDim];
   __shared__ int prefix[kScoreMaxUnits + 1];
   const int units = a.batch * a.retrieval_heads;
   const int warp = threadIdx.x >> 5;

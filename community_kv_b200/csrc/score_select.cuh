@@ -38,8 +38,8 @@ __device__ __forceinline__ int score_limit(const ckv_layer_args& a, int flat) {
 
 // Scores the 16-row groups [first_group, last_group) of one unit: scores[c] =
 // fp16(max over the query group of q . centroid[c]).  Every thread of the CTA calls
-// it with the same arguments (the query group is staged in `q_s`, 16 * 128 floats
-// of shared memory, behind block barriers); a warp takes every (kThreads / 32)-th
+// it with the same arguments (the query group is staged in `q_s`, 2 * 16 * 128 floats
+// of shared memory, 16-byte aligned, behind block barriers); a warp takes every (kThreads / 32)-th
 // group and keeps the next group's loads in flight while it computes.
 //
 // With `slice` set, the keys and sizes of the scored rows are also kept in shared
@@ -53,10 +53,10 @@ struct ScoreSlice {
   int row0;
 };
 
-template <int kThreads>
-__device__ __forceinline__ void score_groups(const ckv_layer_args& a, int flat, int first_group,
-                                             int last_group, float* q_s,
-                                             const ScoreSlice* slice_out = nullptr) {
+template <int kThreads, bool kNarrow>
+__device__ __forceinline__ void score_groups_impl(const ckv_layer_args& a, int flat, int first_group,
+                                                  int last_group, float* q_s,
+                                                  const ScoreSlice* slice_out) {
   const int group = a.group_size;
   const int capacity = a.community_capacity;
   const int warp = threadIdx.x >> 5;
@@ -69,18 +69,44 @@ __device__ __forceinline__ void score_groups(const ckv_layer_args& a, int flat, 
   const int limit = score_limit(a, flat);
   const uint8_t* table = reinterpret_cast<const uint8_t*>(a.centroids) +
                          static_cast<int64_t>(flat) * capacity * kHeadDim;
-  uint4 raw[4];
+  // two groups in flight per warp: with one, the loop runs at one memory round trip
+  // per group
+  constexpr int kStride = kThreads / 32;
+  uint4 raw_even[4], raw_odd[4];
   int current = first_group + warp;
   if (current < last_group) {
-    load_group(table, current * 16, quad, slice, capacity, raw);
+    load_group(table, current * 16, quad, slice, capacity, raw_even);
+  }
+  if (current + kStride < last_group) {
+    load_group(table, (current + kStride) * 16, quad, slice, capacity, raw_odd);
   }
   const __nv_bfloat16* query =
       reinterpret_cast<const __nv_bfloat16*>(a.query) + static_cast<int64_t>(flat) * group * kHeadDim;
   __syncthreads();  // the previous unit's query is no longer read
-  for (int i = threadIdx.x; i < group * kHeadDim; i += kThreads) {
+  // Up to four heads: this lane's 16 dimensions of every head stay in registers as
+  // packed bf16 (a missing head repeats the last one, which leaves the maximum
+  // unchanged).  More heads: the group is staged in shared memory as fp32.
+  uint32_t q_bf16[kNarrow ? 4 : 1][8];
+  if constexpr (kNarrow) {
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const uint4* src =
+          reinterpret_cast<const uint4*>(query + min(h, group - 1) * kHeadDim + slice * 16);
+      const uint4 lo = src[0];
+      const uint4 hi = src[1];
+      q_bf16[h][0] = lo.x; q_bf16[h][1] = lo.y; q_bf16[h][2] = lo.z; q_bf16[h][3] = lo.w;
+      q_bf16[h][4] = hi.x; q_bf16[h][5] = hi.y; q_bf16[h][6] = hi.z; q_bf16[h][7] = hi.w;
+    }
+  }
+  for (int i = threadIdx.x; !kNarrow && i < group * kHeadDim; i += kThreads) {
     const int g = i >> 7;
     const int dim = i & 127;
-    q_s[((g * 4 + ((dim >> 2) & 3)) * 8 + (dim >> 4)) * 4 + (dim & 3)] = __bfloat162float(query[i]);
+    // [head][dimension pair of the slice][slice] x {q, q, q', q'}: a warp's eight
+    // slices read 128 contiguous bytes, every value arrives already duplicated
+    const float value = __bfloat162float(query[i]);
+    const int at = ((g * 8 + ((dim & 15) >> 1)) * 8 + (dim >> 4)) * 4 + (dim & 1) * 2;
+    q_s[at] = value;
+    q_s[at + 1] = value;
   }
   __syncthreads();
 
@@ -88,16 +114,27 @@ __device__ __forceinline__ void score_groups(const ckv_layer_args& a, int flat, 
   const int32_t* sizes = a.community_sizes + static_cast<int64_t>(flat) * capacity;
   __half* out = reinterpret_cast<__half*>(a.scores) + static_cast<int64_t>(flat) * capacity;
 
-  for (; current < last_group; current += kThreads / 32) {
-    float x[4][16];
+  auto score_one = [&](uint4 (&raw)[4], int current) {
+    // The narrow path widens e4m3 to bf16 with integer operations and feeds
+    // mixed-precision FMAs (bf16 x bf16 + fp32, one rounding: the same value as
+    // the fp32 FMA of the widened operands); the wide path widens to fp32.
+    uint32_t xb[kNarrow ? 4 : 1][8];
+    float x[kNarrow ? 1 : 4][16];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      fp8x4_to_float(raw[i].x, x[i] + 0);
-      fp8x4_to_float(raw[i].y, x[i] + 4);
-      fp8x4_to_float(raw[i].z, x[i] + 8);
-      fp8x4_to_float(raw[i].w, x[i] + 12);
+      if constexpr (kNarrow) {
+        e4m3x4_to_bf16x2(raw[i].x, xb[i][0], xb[i][1]);
+        e4m3x4_to_bf16x2(raw[i].y, xb[i][2], xb[i][3]);
+        e4m3x4_to_bf16x2(raw[i].z, xb[i][4], xb[i][5]);
+        e4m3x4_to_bf16x2(raw[i].w, xb[i][6], xb[i][7]);
+      } else {
+        fp8x4_to_float(raw[i].x, x[i] + 0);
+        fp8x4_to_float(raw[i].y, x[i] + 4);
+        fp8x4_to_float(raw[i].z, x[i] + 8);
+        fp8x4_to_float(raw[i].w, x[i] + 12);
+      }
     }
-    const int next = current + kThreads / 32;
+    const int next = current + 2 * kStride;  // this buffer's next group
     if (next < last_group) {
       load_group(table, next * 16, quad, slice, capacity, raw);
     }
@@ -107,49 +144,78 @@ __device__ __forceinline__ void score_groups(const ckv_layer_args& a, int flat, 
       size = __ldg(sizes + row);
     }
 
-    float best = -INFINITY;
-    // two heads per pass: eight independent accumulation chains per lane
-    for (int g = 0; g < group; g += 2) {
-      const bool pair = g + 1 < group;
-      float qa[16], qb[16];
-      const float4* qp = reinterpret_cast<const float4*>(q_s) + g * 32 + slice;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float4 v = qp[k * 8];
-        const float4 w = pair ? qp[32 + k * 8] : v;
-        qa[4 * k + 0] = v.x; qa[4 * k + 1] = v.y; qa[4 * k + 2] = v.z; qa[4 * k + 3] = v.w;
-        qb[4 * k + 0] = w.x; qb[4 * k + 1] = w.y; qb[4 * k + 2] = w.z; qb[4 * k + 3] = w.w;
-      }
-      float pa[4], pb[4];
+    float best;
+    if constexpr (kNarrow) {
+      // four independent chains (one per head) of 16 sequential FMAs per row;
+      // starting from -0 makes the first step the plain product, sign included
+      float per_head[4][4];  // [head][row]
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        float acc_a = __fmul_rn(x[i][0], qa[0]);
-        float acc_b = __fmul_rn(x[i][0], qb[0]);
+        float acc[4] = {-0.0f, -0.0f, -0.0f, -0.0f};
 #pragma unroll
-        for (int k = 1; k < 16; ++k) {
-          acc_a = __fmaf_rn(x[i][k], qa[k], acc_a);
-          acc_b = __fmaf_rn(x[i][k], qb[k], acc_b);
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            acc[h] = fma2_bf16(xb[i][j], q_bf16[h][j], acc[h]);
+          }
         }
-        pa[i] = acc_a;
-        pb[i] = acc_b;
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          per_head[h][i] = acc[h];
+        }
       }
-      // Sum the eight slices of each row: (j, j^4), then (j, j^2), then (j, j^1),
-      // folding the four rows onto the lanes on the way (a transposing butterfly).
-      float keep0_a = up_a ? pa[2] : pa[0], keep1_a = up_a ? pa[3] : pa[1];
-      float keep0_b = up_a ? pb[2] : pb[0], keep1_b = up_a ? pb[3] : pb[1];
-      keep0_a = __fadd_rn(keep0_a, __shfl_xor_sync(0xffffffffu, up_a ? pa[0] : pa[2], 4));
-      keep1_a = __fadd_rn(keep1_a, __shfl_xor_sync(0xffffffffu, up_a ? pa[1] : pa[3], 4));
-      keep0_b = __fadd_rn(keep0_b, __shfl_xor_sync(0xffffffffu, up_a ? pb[0] : pb[2], 4));
-      keep1_b = __fadd_rn(keep1_b, __shfl_xor_sync(0xffffffffu, up_a ? pb[1] : pb[3], 4));
-      float keep_a = up_b ? keep1_a : keep0_a;
-      float keep_b = up_b ? keep1_b : keep0_b;
-      keep_a = __fadd_rn(keep_a, __shfl_xor_sync(0xffffffffu, up_b ? keep0_a : keep1_a, 2));
-      keep_b = __fadd_rn(keep_b, __shfl_xor_sync(0xffffffffu, up_b ? keep0_b : keep1_b, 2));
-      keep_a = __fadd_rn(keep_a, __shfl_xor_sync(0xffffffffu, keep_a, 1));
-      keep_b = __fadd_rn(keep_b, __shfl_xor_sync(0xffffffffu, keep_b, 1));
-      best = fmaxf(best, keep_a);
-      if (pair) {
-        best = fmaxf(best, keep_b);
+      best = -INFINITY;
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        // Sum the eight slices of each row: (j, j^4), then (j, j^2), then (j, j^1),
+        // folding the four rows onto the lanes on the way (a transposing butterfly).
+        const float* pa = per_head[h];
+        float keep0 = up_a ? pa[2] : pa[0], keep1 = up_a ? pa[3] : pa[1];
+        keep0 = __fadd_rn(keep0, __shfl_xor_sync(0xffffffffu, up_a ? pa[0] : pa[2], 4));
+        keep1 = __fadd_rn(keep1, __shfl_xor_sync(0xffffffffu, up_a ? pa[1] : pa[3], 4));
+        float keep = up_b ? keep1 : keep0;
+        keep = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, up_b ? keep0 : keep1, 2));
+        keep = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, keep, 1));
+        best = fmaxf(best, keep);
+      }
+    } else {
+      // Rows (0,1) and (2,3) of this lane ride together in packed fp32 pairs: one
+      // two-wide FMA advances both rows' chains (each half rounds like a scalar FMA).
+      uint64_t x01[16], x23[16];
+  #pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        x01[k] = pack_f32x2(x[0][k], x[1][k]);
+        x23[k] = pack_f32x2(x[2][k], x[3][k]);
+      }
+      best = -INFINITY;
+      for (int g = 0; g < group; ++g) {
+        // {q, q} pairs of this lane's 16 dimensions, two dimensions per 16-byte read
+        const ulonglong2* qp = reinterpret_cast<const ulonglong2*>(q_s) + g * 64 + slice;
+        ulonglong2 q2 = qp[0];
+        uint64_t acc01 = mul_f32x2(x01[0], q2.x);
+        uint64_t acc23 = mul_f32x2(x23[0], q2.x);
+        acc01 = fma_f32x2(x01[1], q2.y, acc01);
+        acc23 = fma_f32x2(x23[1], q2.y, acc23);
+  #pragma unroll
+        for (int k2 = 1; k2 < 8; ++k2) {
+          q2 = qp[k2 * 8];
+          acc01 = fma_f32x2(x01[2 * k2], q2.x, acc01);
+          acc23 = fma_f32x2(x23[2 * k2], q2.x, acc23);
+          acc01 = fma_f32x2(x01[2 * k2 + 1], q2.y, acc01);
+          acc23 = fma_f32x2(x23[2 * k2 + 1], q2.y, acc23);
+        }
+        float pa[4];
+        unpack_f32x2(acc01, pa[0], pa[1]);
+        unpack_f32x2(acc23, pa[2], pa[3]);
+        // Sum the eight slices of each row: (j, j^4), then (j, j^2), then (j, j^1),
+        // folding the four rows onto the lanes on the way (a transposing butterfly).
+        float keep0 = up_a ? pa[2] : pa[0], keep1 = up_a ? pa[3] : pa[1];
+        keep0 = __fadd_rn(keep0, __shfl_xor_sync(0xffffffffu, up_a ? pa[0] : pa[2], 4));
+        keep1 = __fadd_rn(keep1, __shfl_xor_sync(0xffffffffu, up_a ? pa[1] : pa[3], 4));
+        float keep = up_b ? keep1 : keep0;
+        keep = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, up_b ? keep0 : keep1, 2));
+        keep = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, keep, 1));
+        best = fmaxf(best, keep);
       }
     }
     if ((slice & 1) == 0 && row < limit) {
@@ -166,6 +232,23 @@ __device__ __forceinline__ void score_groups(const ckv_layer_args& a, int flat, 
         }
       }
     }
+  };
+  for (; current < last_group; current += 2 * kStride) {
+    score_one(raw_even, current);
+    if (current + kStride < last_group) {
+      score_one(raw_odd, current + kStride);
+    }
+  }
+}
+
+template <int kThreads>
+__device__ __forceinline__ void score_groups(const ckv_layer_args& a, int flat, int first_group,
+                                             int last_group, float* q_s,
+                                             const ScoreSlice* slice_out = nullptr) {
+  if (a.group_size <= 4) {
+    score_groups_impl<kThreads, true>(a, flat, first_group, last_group, q_s, slice_out);
+  } else {
+    score_groups_impl<kThreads, false>(a, flat, first_group, last_group, q_s, slice_out);
   }
 }
 
@@ -596,7 +679,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 
 struct ClusterSelectSmem {
-  alignas(16) float query[16 * kHeadDim];  // staged query group (read with 16-byte loads)
+  alignas(16) float query[2 * 16 * kHeadDim];  // staged query group, every value twice
   uint16_t key[kStash];   // this CTA's slice
   int size[kStash];
   int hist_mass[256];     // slice histograms, read by the other CTAs

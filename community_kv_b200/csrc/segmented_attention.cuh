@@ -21,21 +21,6 @@ struct AttnSmem {
   static constexpr int kTotal = kTopOffset + kAttnWarps * kKappa * 8;
 };
 
-// acc += a.lo*b.lo ; acc += a.hi*b.hi  with bf16 operands, fp32 accumulate, each
-// step rounded once (the product of two bf16 values is exact in fp32).
-__device__ __forceinline__ float fma2_bf16(uint32_t a, uint32_t b, float acc) {
-  asm("{\n"
-      ".reg .b16 al, ah, bl, bh;\n"
-      "mov.b32 {al, ah}, %1;\n"
-      "mov.b32 {bl, bh}, %2;\n"
-      "fma.rn.f32.bf16 %0, al, bl, %0;\n"
-      "fma.rn.f32.bf16 %0, ah, bh, %0;\n"
-      "}\n"
-      : "+f"(acc)
-      : "r"(a), "r"(b));
-  return acc;
-}
-
 __device__ __forceinline__ float dot16_bf16(const uint8_t* row, const uint8_t* q) {
   const uint4 r0 = *reinterpret_cast<const uint4*>(row);
   const uint4 r1 = *reinterpret_cast<const uint4*>(row + 16);
