@@ -19,6 +19,7 @@ the reference's algorithm on the host cores instead.
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -38,6 +39,8 @@ QUERY_HEADS = 32
 KV_HEADS = 8
 HEAD_DIM = 128
 CONTEXT = 131072
+# ncu: DRAM bytes of one decode_cluster_kernel launch at 8 sequences x 8 KV heads
+LAYER_TRAFFIC_BYTES = 97258496
 BUDGET = 2048
 NUM_SINK = 10
 COMMUNITIES = (1024, 4096)
@@ -288,7 +291,7 @@ def run_b200(args: argparse.Namespace) -> None:
     batch = per_gpu * world
     total_steps = args.warmup + args.steps
     e2e_steps = max(3, min(args.steps, 10))
-    extra_steps = 4 + e2e_steps + 3
+    extra_steps = 4 + e2e_steps + 3 + 3  # e2e steps, then three event-timed passes over the layers
     max_decode = total_steps + extra_steps + 8
 
     build_begin = time.perf_counter()
@@ -382,7 +385,25 @@ def run_b200(args: argparse.Namespace) -> None:
     ms_per_step = float(elapsed_ms) / args.steps
     work.runtime.assert_no_overflow()
 
-    # ---- dominant kernel alone: gather + segmented attention, per-launch events ----
+    # ---- dominant kernel: the per-layer launch(es), event-timed one layer at a time ----
+    layer_ms = []
+    with torch.cuda.stream(stream):
+        for repeat in range(3):
+            events = []
+            for launch in range(launches):
+                first, second = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                first.record()
+                native.call("ckv_decode_layer", packed[launch], stream.cuda_stream)
+                second.record()
+                events.append((first, second))
+            stream.synchronize()
+            if repeat > 0:
+                layer_ms.extend(a.elapsed_time(b) for a, b in events)
+    layer_launch_ms = statistics.mean(layer_ms)
+    kernels_per_layer = int(native.library().ckv_decode_layer_kernels(ctypes.byref(packed[0])))
+    work.runtime.assert_no_overflow()
+
+    # ---- the gather + attention kernel alone, same way ----
     attn_args = []
     for launch in range(launches):
         clone = native.LayerArgs.from_buffer_copy(packed[launch])
@@ -443,6 +464,8 @@ def run_b200(args: argparse.Namespace) -> None:
     attention_gbs = units_per_launch * kv_bytes_per_unit / (attention_ms * 1e-3) / 1e9
     centroid_bytes = sum(work.community_counts) * HEAD_DIM
     step_bytes = centroid_bytes + launches * units_per_launch * kv_bytes_per_unit
+    layer_bytes = step_bytes // launches  # centroids + selected KV of one launch (mean over layers)
+    layer_gbs = layer_bytes / (layer_launch_ms * 1e-3) / 1e9
     step_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
 
     if rank != 0:
@@ -464,16 +487,30 @@ def run_b200(args: argparse.Namespace) -> None:
         "data": "synthetic",
         "config": workload_config(args, batch=batch, world=world),
         "roofline": {
-            "kernel": "attention_kernel (KV gather + segmented flash-decode)",
+            "kernel": (
+                "decode_cluster_kernel (one launch per layer: centroid scoring, selection, KV gather + "
+                "segmented flash-decode, split merge, online update)"
+                if kernels_per_layer == 1 else
+                "score_kernel + select_kernel + attention_kernel + merge_update_kernel (one layer)"
+            ),
             "bound": "hbm",
-            "achieved": attention_gbs,
+            "achieved": layer_gbs,
             "peak": peak,
             "unit": "GB/s",
-            "frac": attention_gbs / peak,
+            "frac": layer_gbs / peak,
             "peak_source": peak_source,
-            "traffic": None,
-            "algorithmic_bytes_per_launch": units_per_launch * kv_bytes_per_unit,
-            "launch_ms": attention_ms,
+            "traffic": LAYER_TRAFFIC_BYTES if (kernels_per_layer == 1 and units_per_launch == 64) else None,
+            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at this size "
+                              "(profiles/decode_cluster_kernel_b8_ctx131072.md)",
+            "algorithmic_bytes_per_launch": layer_bytes,
+            "launch_ms": layer_launch_ms,
+            "kernels_per_layer": kernels_per_layer,
+            "attention_kernel_alone": {
+                "achieved": attention_gbs,
+                "frac": attention_gbs / peak,
+                "algorithmic_bytes_per_launch": units_per_launch * kv_bytes_per_unit,
+                "launch_ms": attention_ms,
+            },
         },
         "step_roofline": {
             "bytes_per_step_per_gpu": step_bytes,
@@ -489,7 +526,7 @@ def run_b200(args: argparse.Namespace) -> None:
             "h2d_bytes_per_step": int(pinned_q[0].numel() * 2 + pinned_kv[0].numel() * 2),
             "d2h_bytes_per_step": int(pinned_out.numel() * 2),
         },
-        "gpu_launches": args.steps * launches * 4,
+        "gpu_launches": args.steps * launches * kernels_per_layer,
         "cuda_graph": use_graph,
         "clocks": clocks,
         "build_seconds": build_seconds,

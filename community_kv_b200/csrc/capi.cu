@@ -166,6 +166,12 @@ int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream) {
   return ckv::launched(ckv::launch_merge_update(*args, stream));
 }
 
+int ckv_decode_layer_kernels(const ckv_layer_args* args) {
+  if (args == nullptr) return CKV_ERR_NULL;
+  if (ckv::fused_layer_supported(*args)) return 1;
+  return (args->retrieval_heads != args->graphs && !(args->flags & CKV_FLAG_SKIP_UPDATE)) ? 5 : 4;
+}
+
 int ckv_online_update(const ckv_layer_args* args, void* cuda_stream) {
   const int common = ckv::check_common(args);
   if (common != CKV_OK) return common;

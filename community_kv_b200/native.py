@@ -160,6 +160,7 @@ ENTRY_POINTS = (
     "ckv_select_descriptors",
     "ckv_segmented_attention",
     "ckv_decode_layer",
+    "ckv_decode_layer_kernels",
     "ckv_attention_smem_bytes",
     "ckv_segmented_attention_static",
     "ckv_prefill_topk",
@@ -195,6 +196,8 @@ def library() -> ctypes.CDLL:
         function = getattr(lib, name)
         function.restype = ctypes.c_int
         function.argtypes = [ctypes.POINTER(LayerArgs), ctypes.c_void_p]
+    lib.ckv_decode_layer_kernels.restype = ctypes.c_int
+    lib.ckv_decode_layer_kernels.argtypes = [ctypes.POINTER(LayerArgs)]
     lib.ckv_prefill_topk.restype = ctypes.c_int
     lib.ckv_prefill_topk.argtypes = [ctypes.POINTER(PrefillArgs), ctypes.c_void_p]
     return lib

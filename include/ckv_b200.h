@@ -198,8 +198,17 @@ int ckv_select_descriptors(const ckv_layer_args* args, void* cuda_stream);
  * CKV_FLAG_SKIP_UPDATE) performs the online assignment and state update. */
 int ckv_segmented_attention(const ckv_layer_args* args, void* cuda_stream);
 
-/* A1..A5 back to back: the whole per-layer decode transition. */
+/* A1..A5 back to back: the whole per-layer decode transition.  With one graph per
+ * retrieval head, at most eight splits and descriptors that fit the selection's
+ * shared-memory list, this is ONE launch: a thread-block cluster per (sequence,
+ * retrieval head) scores, selects, attends, merges and updates, synchronising
+ * through cluster barriers.  Otherwise (or with CKV_FLAG_UNFUSED) the four
+ * stand-alone kernels run back to back.  Results are identical either way. */
 int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream);
+
+/* How many kernels ckv_decode_layer launches for these arguments (1, 4 or 5);
+ * no reference counterpart, used for launch accounting. */
+int ckv_decode_layer_kernels(const ckv_layer_args* args);
 
 /* A5 alone.  Applies the online assignment and centroid update from the
  * `lse`, `topk_scores` and `topk_positions` already in the workspace (for
