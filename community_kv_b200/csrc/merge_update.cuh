@@ -7,6 +7,7 @@
 namespace ckv {
 
 constexpr int kMergeThreads = 128;
+constexpr int kMaxSplitsInFlight = 8;  // split rows a merging lane fetches at once
 
 struct UpdateDecision {
   int assigned;      // community id the new token joins (clamped to capacity-1)
@@ -14,6 +15,7 @@ struct UpdateDecision {
   int current;       // cache row of the new token
   int apply;         // 1 when sizes/centroid/labels are to be written
   int valid_position;
+  int candidates[kKappa + 1];  // communities the token may join (-1: none), known before the decision
 };
 
 // Warps 0 .. merge_warps-1 merge the split partials; warp `merge_warps` is the update
@@ -44,6 +46,13 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
   float old_total = 0.f;
   float old_weight = 0.f;
   int current = 0;
+  // Graph state of the community this lane's neighbour belongs to (lanes 0-7) or of
+  // the next unused community id (lane 8), fetched before the assignment is known:
+  // one of these nine is the community the new token will join.
+  int spec_community = -1;
+  int spec_size = 0, spec_delta = 0, spec_tail = -1;
+  int spec_chunk_size = 0, spec_chunk_capacity = 0, spec_chunk_start = 0;
+  int free_chunk = 0, free_position = 0;
   // key element of the new token, fetched early by the merging threads
   float key_value = 0.f;
 
@@ -76,6 +85,15 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
     __nv_bfloat16* output = reinterpret_cast<__nv_bfloat16*>(a.output) +
                             static_cast<int64_t>(flat) * group * kHeadDim;
     for (int g = warp; g < group && !update_only; g += merge_warps) {
+      // the accumulator rows do not depend on the (max, sum) pairs: fetch both at once
+      float4 rows[kMaxSplitsInFlight];
+#pragma unroll
+      for (int s = 0; s < kMaxSplitsInFlight; ++s) {
+        if (s < splits) {
+          rows[s] = __ldcg(reinterpret_cast<const float4*>(
+              partial + (s * group + g) * kPartialStride + 4 * lane));
+        }
+      }
       float my_max = -INFINITY;
       float my_sum = 0.f;
       if (lane < splits) {
@@ -97,8 +115,17 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
         denominator += __shfl_xor_sync(0xffffffffu, denominator, offset);
       }
       float4 numerator = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-      for (int s = 0; s < splits; ++s) {
+#pragma unroll
+      for (int s = 0; s < kMaxSplitsInFlight; ++s) {
+        if (s < splits) {
+          const float w = __shfl_sync(0xffffffffu, weight, s);
+          numerator.x += rows[s].x * w;
+          numerator.y += rows[s].y * w;
+          numerator.z += rows[s].z * w;
+          numerator.w += rows[s].w * w;
+        }
+      }
+      for (int s = kMaxSplitsInFlight; s < splits; ++s) {
         const float w = __shfl_sync(0xffffffffu, weight, s);
         const float4 v = __ldcg(reinterpret_cast<const float4*>(
             partial + (s * group + g) * kPartialStride + 4 * lane));
@@ -146,6 +173,8 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
       active = a.community_counts[flat];
       old_total = a.total_weight[graph_slot];
       current = a.current_position[graph_slot];
+      free_chunk = a.next_free_chunk[graph_slot];
+      free_position = a.next_free_position[graph_slot];
     }
     for (int k = 0; k < kKappa && !update_only; ++k) {
       uint64_t local = 0ull;
@@ -182,9 +211,39 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
       if (valid && community >= 0 && community < capacity) {
         old_weight = a.community_weight[graph_slot * capacity + community];
       }
+      spec_community = lane < kKappa ? community : (lane == kKappa ? active : -1);
+      if (spec_community >= 0 && spec_community < capacity) {
+        const int64_t table = graph_slot * capacity + spec_community;
+        spec_size = a.community_sizes[static_cast<int64_t>(flat) * capacity + spec_community];
+        spec_delta = a.delta_sizes[table];
+        spec_tail = a.community_tail[table];
+        if (spec_tail >= 0) {
+          const int64_t chunk_base = graph_slot * a.chunks_per_graph;
+          spec_chunk_size = a.chunk_size[chunk_base + spec_tail];
+          spec_chunk_capacity = a.chunk_capacity[chunk_base + spec_tail];
+          spec_chunk_start = a.chunk_start[chunk_base + spec_tail];
+        }
+      } else {
+        spec_community = -1;
+      }
+    }
+    if (lane <= kKappa) {
+      decision.candidates[lane] = spec_community;
     }
   }
   __syncthreads();
+  // Centroid bytes of every community the token may join, fetched while the update
+  // warp decides: the running-mean update below then needs no further round trip.
+  uint8_t centroid_byte[kKappa + 1];
+  if (leader && threadIdx.x < kHeadDim) {
+    const uint8_t* table = reinterpret_cast<const uint8_t*>(a.centroids) +
+                           static_cast<int64_t>(flat) * capacity * kHeadDim + threadIdx.x;
+#pragma unroll
+    for (int j = 0; j <= kKappa; ++j) {
+      const int c = decision.candidates[j];
+      centroid_byte[j] = c >= 0 ? table[static_cast<int64_t>(c) * kHeadDim] : 0;
+    }
+  }
 
   if (warp == merge_warps && leader) {
     // lanes 0..7 hold rank `lane`; sums run over the ranks in order on every lane
@@ -243,6 +302,16 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
       a.community_weight[graph_slot * capacity + community] = __fadd_rn(old_weight, increment);
     }
     __syncwarp();
+    // the lane that fetched the chosen community's state hands it to lane 0
+    const unsigned holders = __ballot_sync(0xffffffffu, spec_community == safe_assigned);
+    const int holder = holders ? __ffs(holders) - 1 : 0;
+    const bool fetched = holders != 0u && !community_overflow;
+    const int got_size = __shfl_sync(0xffffffffu, spec_size, holder);
+    const int got_delta = __shfl_sync(0xffffffffu, spec_delta, holder);
+    const int got_tail = __shfl_sync(0xffffffffu, spec_tail, holder);
+    const int got_chunk_size = __shfl_sync(0xffffffffu, spec_chunk_size, holder);
+    const int got_chunk_capacity = __shfl_sync(0xffffffffu, spec_chunk_capacity, holder);
+    const int got_chunk_start = __shfl_sync(0xffffffffu, spec_chunk_start, holder);
     if (lane == 0) {
       if (!community_overflow) {
         if (!join) {
@@ -260,21 +329,20 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
       if (!community_overflow) {
         const int64_t table = graph_slot * capacity + safe_assigned;
         const int64_t chunk_base = graph_slot * a.chunks_per_graph;
-        // independent reads first
-        old_size = a.community_sizes[static_cast<int64_t>(flat) * capacity + safe_assigned];
-        const int delta_size = a.delta_sizes[table];
-        const int old_tail = a.community_tail[table];
-        const int free_chunk = a.next_free_chunk[graph_slot];
-        const int free_position = a.next_free_position[graph_slot];
+        // normally already in registers (fetched before the decision)
+        old_size = fetched ? got_size
+                           : a.community_sizes[static_cast<int64_t>(flat) * capacity + safe_assigned];
+        const int delta_size = fetched ? got_delta : a.delta_sizes[table];
+        const int old_tail = fetched ? got_tail : a.community_tail[table];
         a.community_sizes[static_cast<int64_t>(flat) * capacity + safe_assigned] = old_size + 1;
         if (valid_position && current < a.token_capacity) {
           a.token_communities[graph_slot * a.token_capacity + current] = assigned;
         }
         int old_chunk_size = 0, old_chunk_capacity = 0, old_chunk_start = 0;
         if (old_tail >= 0) {
-          old_chunk_size = a.chunk_size[chunk_base + old_tail];
-          old_chunk_capacity = a.chunk_capacity[chunk_base + old_tail];
-          old_chunk_start = a.chunk_start[chunk_base + old_tail];
+          old_chunk_size = fetched ? got_chunk_size : a.chunk_size[chunk_base + old_tail];
+          old_chunk_capacity = fetched ? got_chunk_capacity : a.chunk_capacity[chunk_base + old_tail];
+          old_chunk_start = fetched ? got_chunk_start : a.chunk_start[chunk_base + old_tail];
         }
         const bool allocate = old_tail < 0 || old_chunk_size >= old_chunk_capacity;
         const int new_capacity = old_tail < 0 ? 1 : old_chunk_capacity * 2;
@@ -330,7 +398,19 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
         (static_cast<int64_t>(flat) * capacity + decision.assigned) * kHeadDim;
     float updated = key_value;
     if (decision.old_size > 0) {
-      const __half_raw raw = __nv_cvt_fp8_to_halfraw(centroid[d], __NV_E4M3);
+      uint8_t stored = 0;
+      bool have = false;
+#pragma unroll
+      for (int j = 0; j <= kKappa; ++j) {
+        if (!have && decision.candidates[j] == decision.assigned) {
+          stored = centroid_byte[j];
+          have = true;
+        }
+      }
+      if (!have) {
+        stored = centroid[d];
+      }
+      const __half_raw raw = __nv_cvt_fp8_to_halfraw(stored, __NV_E4M3);
       const float old_value = __half2float(*reinterpret_cast<const __half*>(&raw));
       const float n = static_cast<float>(decision.old_size);
       updated = __fdiv_rn(__fadd_rn(__fmul_rn(old_value, n), key_value),
