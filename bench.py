@@ -40,7 +40,7 @@ KV_HEADS = 8
 HEAD_DIM = 128
 CONTEXT = 131072
 # ncu: DRAM bytes of one decode_cluster_kernel launch at 8 sequences x 8 KV heads
-LAYER_TRAFFIC_BYTES = 97258496
+LAYER_TRAFFIC_BYTES = 98176000
 BUDGET = 2048
 NUM_SINK = 10
 COMMUNITIES = (1024, 4096)
@@ -291,7 +291,7 @@ def run_b200(args: argparse.Namespace) -> None:
     batch = per_gpu * world
     total_steps = args.warmup + args.steps
     e2e_steps = max(3, min(args.steps, 10))
-    extra_steps = 4 + e2e_steps + 3 + 3  # e2e steps, then three event-timed passes over the layers
+    extra_steps = 4 + e2e_steps + 3 + 4  # e2e steps, three event-timed passes, one phase-stamped pass
     max_decode = total_steps + extra_steps + 8
 
     build_begin = time.perf_counter()
@@ -402,6 +402,34 @@ def run_b200(args: argparse.Namespace) -> None:
     layer_launch_ms = statistics.mean(layer_ms)
     kernels_per_layer = int(native.library().ckv_decode_layer_kernels(ctypes.byref(packed[0])))
     work.runtime.assert_no_overflow()
+
+    # ---- where a layer launch spends its time: per-CTA phase timestamps (one extra pass) ----
+    phases_us = None
+    if kernels_per_layer == 1:
+        units = slots * heads_local
+        stamps = torch.zeros((launches, units, 8, 16), dtype=torch.int64, device=device)
+        with torch.cuda.stream(stream):
+            for launch in range(launches):
+                clone = native.LayerArgs.from_buffer_copy(packed[launch])
+                clone.phase_times = stamps[launch].data_ptr()
+                native.call("ckv_decode_layer", clone, stream.cuda_stream)
+            stream.synchronize()
+        t = stamps[:, :, : packed[0].splits, :10].cpu().numpy().astype("float64") / 1e3
+        t0 = t[..., 0].min(axis=(1, 2), keepdims=True)
+        span = lambda a, b, ranks=slice(None): (t[:, :, ranks, b] - t[:, :, ranks, a])
+        stat = lambda x: {"mean": round(float(x.mean()), 2), "max": round(float(x.max(axis=(1, 2)).mean()), 2)}
+        phases_us = {
+            "score": stat(span(0, 1)),
+            "select_wait_for_cluster": stat(span(1, 2)),
+            "select_exchanges": stat(span(2, 5)),
+            "resolve_positions": stat(span(5, 6)),
+            "gather_attention": stat(span(6, 7)),
+            "wait_for_cluster": stat(span(7, 8, slice(0, 1))),
+            "merge_update": stat(span(8, 9, slice(0, 1))),
+            "launch_total": stat((t[:, :, 0:1, 9] - t0)),
+            "note": "per CTA, microseconds; max = slowest CTA of a launch, averaged over the layers",
+        }
+        work.runtime.assert_no_overflow()
 
     # ---- the gather + attention kernel alone, same way ----
     attn_args = []
@@ -526,6 +554,7 @@ def run_b200(args: argparse.Namespace) -> None:
             "h2d_bytes_per_step": int(pinned_q[0].numel() * 2 + pinned_kv[0].numel() * 2),
             "d2h_bytes_per_step": int(pinned_out.numel() * 2),
         },
+        "phases_us": phases_us,
         "gpu_launches": args.steps * launches * kernels_per_layer,
         "cuda_graph": use_graph,
         "clocks": clocks,

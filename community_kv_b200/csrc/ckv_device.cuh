@@ -120,6 +120,15 @@ __device__ __forceinline__ float fma2_bf16(uint32_t a, uint32_t b, float acc) {
   return acc;
 }
 
+// Optional phase timestamps of the single-launch decode path (see ckv_layer_args).
+__device__ __forceinline__ void phase_stamp(const ckv_layer_args& a, int flat, int rank, int slot) {
+  if (a.phase_times != nullptr && threadIdx.x == 0) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    a.phase_times[(static_cast<int64_t>(flat) * 8 + rank) * 16 + slot] = now;
+  }
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* pointer) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
 }

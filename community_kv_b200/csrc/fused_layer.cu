@@ -55,12 +55,14 @@ __global__ void __launch_bounds__(kFusedThreads, 3) decode_cluster_kernel(const 
   const int groups = (score_limit(a, flat) + 15) / 16;
   const int first_group = static_cast<int>(static_cast<int64_t>(split) * groups / a.splits);
   const int last_group = static_cast<int>(static_cast<int64_t>(split + 1) * groups / a.splits);
+  phase_stamp(a, flat, split, 0);
   cluster_select_begin<kFusedThreads>(sm);
   {
     const ScoreSlice slice = {sm.key, sm.size, sm.hist_mass, sm.hist_count, first_group * 16};
     score_groups<kFusedThreads>(a, flat, first_group, last_group, sm.query, &slice);
   }
   __syncthreads();
+  phase_stamp(a, flat, split, 1);
 
   // ---- 2. selection across the cluster, then this split's cache rows ----
   {
@@ -73,18 +75,23 @@ __global__ void __launch_bounds__(kFusedThreads, 3) decode_cluster_kernel(const 
                                   step_begin * kStepTokens, step_end * kStepTokens);
   }
   __syncthreads();  // positions written above are read by other threads of this CTA
+  phase_stamp(a, flat, split, 6);
 
   // ---- 3. gather + attention over this split ----
   attention_split<kBlocks>(a, flat, split, smem);
+  phase_stamp(a, flat, split, 7);
   __threadfence();
   cluster_arrive();
   if (split != 0) {
     return;
   }
   cluster_wait();
+  phase_stamp(a, flat, split, 8);
 
   // ---- 4. merge, output, online update ----
   merge_update_unit(a, flat, kFusedThreads / 32 - 1, decision, lse_s);
+  __syncthreads();
+  phase_stamp(a, flat, split, 9);
 }
 
 bool fused_layer_supported(const ckv_layer_args& a) {

@@ -745,6 +745,7 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
   }
   rows = max(0, min(rows, active - row0));
   cluster_sync_all();  // every slice's first-pass histogram is complete
+  phase_stamp(a, flat, rank, 2);
 
   // Sum a pair of 256-bin histograms over the cluster.  Each thread owns
   // 256 / kThreads bins and keeps every slice's values in registers: once the
@@ -822,6 +823,7 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
     }
   }
   cluster_sync_all();
+  phase_stamp(a, flat, rank, 3);
   gather(sm.low_mass, sm.low_count);
   if (tid < 32) {
     find_threshold_bin(sm.sum_mass, sm.sum_count, budget, limit, mass_above, count_above, &sm.bin,
@@ -922,6 +924,7 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
     }
   }
   cluster_sync_all();  // the lists are complete everywhere
+  phase_stamp(a, flat, rank, 4);
   if (tid == 0) {
     const int descriptors = min(a.descriptor_capacity, total_high_count + sm.stored_equal);
     sm.descriptors = descriptors;
@@ -934,6 +937,7 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
   }
   __syncthreads();
   const int descriptors = sm.descriptors;
+  phase_stamp(a, flat, rank, 5);
   const int32_t* search_ends = sm.desc_end;
   const int32_t* search_comm = sm.desc_comm;
 

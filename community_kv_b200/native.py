@@ -97,6 +97,7 @@ class LayerArgs(ctypes.Structure):
         ("kv_row_count", _i32),
         ("merged", _ptr),
         ("current_key", _ptr),
+        ("phase_times", _ptr),
     ]
 
 

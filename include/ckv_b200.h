@@ -147,6 +147,12 @@ typedef struct ckv_layer_args {
   const void* current_key;     /* optional bf16 [batch, R, 128]: key of the token being decoded
                                   (row of each retrieval head's KV head), used for the centroid
                                   update instead of a cache read */
+  uint64_t* phase_times;       /* optional diagnostic [batch*R, 8, 16]: nanosecond timestamps
+                                  (%globaltimer) that thread 0 of every CTA of the single-launch
+                                  path writes at its phase boundaries: 0 start, 1 scored,
+                                  2..4 after the selection's three cluster exchanges, 5 descriptors
+                                  known, 6 cache rows resolved, 7 attended, 8 partials of the whole
+                                  cluster visible (rank 0), 9 merged and updated (rank 0) */
 } ckv_layer_args;
 
 /* Arguments of the prefill score-graph kernel.  Q, K, V, O are bf16 with a
