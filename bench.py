@@ -63,6 +63,11 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--cpu-seconds", type=float, default=15.0)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                        help="N>1: head outputs by in-kernel peer stores (default) or an NCCL all-gather per layer")
+    parser.add_argument("--peer-wait", choices=["node", "launch"], default="node",
+                        help="peer exchange: wait for the peers' rows in a one-thread kernel after each layer "
+                             "(node) or inside the layer launch itself (launch)")
     parser.add_argument("--workload", choices=["decode", "prefill"], default="decode",
                         help="prefill: the score-graph emission kernel at S=16384 (a second, separate line)")
     parser.add_argument("--prefill-length", type=int, default=16384)
@@ -173,7 +178,7 @@ def run_reference(args: argparse.Namespace) -> None:
     print(json.dumps(line), flush=True)
 
 
-def workload_config(args: argparse.Namespace, *, batch: int, world: int) -> dict:
+def workload_config(args: argparse.Namespace, *, batch: int, world: int, exchange_mode: str = "none") -> dict:
     return {
         "workload": (
             "batched long-context decode (Qwen3-8B attention shapes): "
@@ -184,6 +189,7 @@ def workload_config(args: argparse.Namespace, *, batch: int, world: int) -> dict
         "context": args.context,
         "token_budget": BUDGET,
         "parallelism": f"kv-head shard x{world}",
+        "exchange": exchange_mode,
         "layers_per_launch": args.layers_per_launch,
         "splits": args.splits,
         "l2": "inputs larger than L2 (each step gathers rows scattered over the whole KV cache)",
@@ -306,11 +312,35 @@ def run_b200(args: argparse.Namespace) -> None:
     launches, slots = work.launches, work.slots
 
     # One contiguous output arena so that a step's result is a single tensor.
-    out_local = torch.zeros((launches, slots, query_local, HEAD_DIM), dtype=torch.bfloat16, device=device)
-    out_full = (
-        torch.zeros((launches, world, slots, query_local, HEAD_DIM), dtype=torch.bfloat16, device=device)
-        if world > 1 else None
-    )
+    exchange = None
+    exchange_mode = "none"
+    if world > 1 and args.exchange == "peer":
+        try:
+            from community_kv_b200.distributed import PeerOutputExchange
+
+            exchange = PeerOutputExchange(launches=launches, slots=slots, heads=query_local, head_dim=HEAD_DIM,
+                                          units=slots * heads_local, device=device)
+            ok = torch.ones((1,), device=device)
+        except Exception as error:  # symmetric memory unavailable: every rank falls back together
+            print(f"[bench] rank {rank}: peer exchange unavailable ({error!r}); using NCCL", file=sys.stderr)
+            ok = torch.zeros((1,), device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok) == 0.0:
+            exchange = None
+    if world > 1:
+        exchange_mode = (
+            "peer stores from the merge phase; wait for the peers' rows: " + args.peer_wait
+            if exchange else "nccl all-gather per layer"
+        )
+    if exchange is not None:
+        out_full = exchange.gathered
+        out_local = None
+    else:
+        out_local = torch.zeros((launches, slots, query_local, HEAD_DIM), dtype=torch.bfloat16, device=device)
+        out_full = (
+            torch.zeros((launches, world, slots, query_local, HEAD_DIM), dtype=torch.bfloat16, device=device)
+            if world > 1 else None
+        )
     q_cur = torch.zeros((launches, slots, query_local, HEAD_DIM), dtype=torch.bfloat16, device=device)
     generator = torch.Generator(device=device).manual_seed(args.seed + 17 + rank)
     stream = torch.cuda.Stream(device)
@@ -318,17 +348,24 @@ def run_b200(args: argparse.Namespace) -> None:
     with torch.cuda.stream(stream):
         for launch in range(launches):
             state = work.state(launch)
-            state.workspace.attention.output = out_local[launch]
+            state.workspace.attention.output = (
+                exchange.local_output(launch) if exchange is not None else out_local[launch]
+            )
             packed.append(
                 work.runtime.pack(launch, query=q_cur[launch], key=work.key[launch],
                                   value=work.value[launch], softmax_scale=SCALE)
             )
+            if exchange is not None:
+                exchange.attach(packed[-1], launch, wait_in_kernel=args.peer_wait == "launch")
 
     def enqueue_step() -> None:
         handle = stream.cuda_stream
         for launch in range(launches):
             native.call("ckv_decode_layer", packed[launch], handle)
-            if world > 1:
+            if exchange is not None:
+                if args.peer_wait == "node":
+                    exchange.wait(launch, handle)  # the next consumer needs every rank's heads
+            elif world > 1:
                 dist.all_gather_into_tensor(out_full[launch], out_local[launch])
 
     def new_queries(count: int) -> "torch.Tensor":
@@ -347,6 +384,15 @@ def run_b200(args: argparse.Namespace) -> None:
             q_cur.copy_(q_all[step])
             enqueue_step()
     barrier()
+    if exchange is not None:
+        # the rows the peers stored here must be exactly what a collective would deliver
+        exchange.check()
+        mine = exchange.gathered[:, rank].contiguous()
+        reference = torch.empty_like(exchange.gathered).transpose(0, 1).contiguous()
+        dist.all_gather_into_tensor(reference, mine)
+        if not torch.equal(reference.transpose(0, 1), exchange.gathered):
+            raise RuntimeError("peer-stored head outputs differ from an all-gather of the local outputs")
+        barrier()
     graph = torch.cuda.CUDAGraph()
     use_graph = True
     try:
@@ -387,13 +433,19 @@ def run_b200(args: argparse.Namespace) -> None:
 
     # ---- dominant kernel: the per-layer launch(es), event-timed one layer at a time ----
     layer_ms = []
+    solo = []  # the same launches without the cross-GPU stores: these passes are not synchronised
+    for launch in range(launches):
+        clone = native.LayerArgs.from_buffer_copy(packed[launch])
+        clone.peer_count = 0
+        clone.peer_wait_flag = None
+        solo.append(clone)
     with torch.cuda.stream(stream):
         for repeat in range(3):
             events = []
             for launch in range(launches):
                 first, second = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 first.record()
-                native.call("ckv_decode_layer", packed[launch], stream.cuda_stream)
+                native.call("ckv_decode_layer", solo[launch], stream.cuda_stream)
                 second.record()
                 events.append((first, second))
             stream.synchronize()
@@ -410,7 +462,7 @@ def run_b200(args: argparse.Namespace) -> None:
         stamps = torch.zeros((launches, units, 8, 16), dtype=torch.int64, device=device)
         with torch.cuda.stream(stream):
             for launch in range(launches):
-                clone = native.LayerArgs.from_buffer_copy(packed[launch])
+                clone = native.LayerArgs.from_buffer_copy(solo[launch])
                 clone.phase_times = stamps[launch].data_ptr()
                 native.call("ckv_decode_layer", clone, stream.cuda_stream)
             stream.synchronize()
@@ -434,7 +486,7 @@ def run_b200(args: argparse.Namespace) -> None:
     # ---- the gather + attention kernel alone, same way ----
     attn_args = []
     for launch in range(launches):
-        clone = native.LayerArgs.from_buffer_copy(packed[launch])
+        clone = native.LayerArgs.from_buffer_copy(solo[launch])
         clone.flags = native.FLAG_ATTENTION_ONLY | native.FLAG_SKIP_UPDATE
         attn_args.append(clone)
     kernel_ms = []
@@ -479,6 +531,8 @@ def run_b200(args: argparse.Namespace) -> None:
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     e2e_ms_per_step = float(e2e_ms) / e2e_steps
     work.runtime.assert_no_overflow()
+    if exchange is not None:
+        exchange.check()
 
     # ---- roofline ----
     peaks_path = ROOT / "MEASURED_PEAKS.json"
@@ -513,7 +567,7 @@ def run_b200(args: argparse.Namespace) -> None:
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic",
-        "config": workload_config(args, batch=batch, world=world),
+        "config": workload_config(args, batch=batch, world=world, exchange_mode=exchange_mode),
         "roofline": {
             "kernel": (
                 "decode_cluster_kernel (one launch per layer: centroid scoring, selection, KV gather + "

@@ -8,6 +8,7 @@ cudaError_t launch_select(const ckv_layer_args& a, cudaStream_t stream);
 cudaError_t launch_resolve(const ckv_layer_args& a, cudaStream_t stream);
 cudaError_t launch_attention(const ckv_layer_args& a, cudaStream_t stream);
 cudaError_t launch_merge_update(const ckv_layer_args& a, cudaStream_t stream);
+cudaError_t launch_wait_peers(uint32_t* flag, uint32_t expected, uint32_t* status, cudaStream_t stream);
 bool fused_layer_supported(const ckv_layer_args& a);
 cudaError_t launch_fused_layer(const ckv_layer_args& a, cudaStream_t stream);
 int attention_smem_bytes();
@@ -26,6 +27,10 @@ int check_common(const ckv_layer_args* a) {
   if (a->num_sink < 0 || a->num_sink + 1 >= a->token_budget) return CKV_ERR_SHAPE;
   if (static_cast<int64_t>(a->batch) * a->retrieval_heads > 65535) return CKV_ERR_CAPACITY;
   if (a->retrieval_to_graph == nullptr || a->retrieval_to_kv == nullptr) return CKV_ERR_NULL;
+  if (a->peer_count < 0 || a->peer_count > CKV_MAX_PEERS) return CKV_ERR_SHAPE;
+  for (int p = 0; p < a->peer_count; ++p) {
+    if (a->peer_output[p] == nullptr || a->peer_flag[p] == nullptr) return CKV_ERR_NULL;
+  }
   return CKV_OK;
 }
 
@@ -164,6 +169,13 @@ int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream) {
   status = ckv::launched(ckv::launch_attention(*args, stream));
   if (status != CKV_OK) return status;
   return ckv::launched(ckv::launch_merge_update(*args, stream));
+}
+
+int ckv_wait_peers(uint32_t* flag, uint32_t expected, uint32_t* status, void* cuda_stream) {
+  if (flag == nullptr) return CKV_ERR_NULL;
+  if (expected == 0) return CKV_OK;
+  return ckv::launched(
+      ckv::launch_wait_peers(flag, expected, status, static_cast<cudaStream_t>(cuda_stream)));
 }
 
 int ckv_decode_layer_kernels(const ckv_layer_args* args) {

@@ -92,6 +92,9 @@ __global__ void __launch_bounds__(kFusedThreads, 3) decode_cluster_kernel(const 
   merge_update_unit(a, flat, kFusedThreads / 32 - 1, decision, lse_s);
   __syncthreads();
   phase_stamp(a, flat, split, 9);
+  if (flat == 0) {
+    wait_for_peer_rows(a);
+  }
 }
 
 bool fused_layer_supported(const ckv_layer_args& a) {

@@ -16,6 +16,9 @@ __global__ void __launch_bounds__(kMergeThreads + 32) merge_update_kernel(const 
   pdl_release_dependents();
   pdl_wait_for_predecessor();  // partials and candidates come from the attention kernel
   merge_update_unit(a, blockIdx.x, kMergeThreads / 32, decision, lse_s);
+  if (blockIdx.x == 0) {
+    wait_for_peer_rows(a);
+  }
 }
 
 // Follower heads of a graph shared by several retrieval heads: apply the
@@ -60,6 +63,30 @@ __global__ void __launch_bounds__(kMergeThreads) sync_shared_kernel(const ckv_la
     }
     centroid[d] = __nv_cvt_float_to_fp8(updated, __NV_SATFINITE, __NV_E4M3);
   }
+}
+
+// One thread polls this GPU's counter a bounded number of times.
+__global__ void wait_peers_kernel(uint32_t* flag, uint32_t expected, uint32_t* status) {
+  constexpr uint32_t kPolls = 1u << 22;  // about two seconds with the back-off below
+  for (uint32_t poll = 0; poll < kPolls; ++poll) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+    if (seen >= expected) {
+      atomicSub(flag, expected);
+      return;
+    }
+    if (poll > 256) {
+      __nanosleep(500);
+    }
+  }
+  if (status != nullptr) {
+    atomicOr(status, CKV_DEV_WAIT_TIMEOUT);
+  }
+}
+
+cudaError_t launch_wait_peers(uint32_t* flag, uint32_t expected, uint32_t* status, cudaStream_t stream) {
+  wait_peers_kernel<<<1, 1, 0, stream>>>(flag, expected, status);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_merge_update(const ckv_layer_args& a, cudaStream_t stream) {

@@ -18,6 +18,30 @@ struct UpdateDecision {
   int candidates[kKappa + 1];  // communities the token may join (-1: none), known before the decision
 };
 
+// Polls this GPU's arrival counter until the peers' head outputs of this call are
+// here (one thread, bounded, system-scope acquire), then takes the count back off.
+__device__ __forceinline__ void wait_for_peer_rows(const ckv_layer_args& a) {
+  if (a.peer_wait_flag == nullptr || a.peer_wait_expected <= 0 || threadIdx.x != 0) {
+    return;
+  }
+  const uint32_t expected = static_cast<uint32_t>(a.peer_wait_expected);
+  constexpr uint32_t kPolls = 1u << 22;  // about two seconds with the back-off below
+  for (uint32_t poll = 0; poll < kPolls; ++poll) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.peer_wait_flag) : "memory");
+    if (seen >= expected) {
+      atomicSub(a.peer_wait_flag, expected);
+      return;
+    }
+    if (poll > 256) {
+      __nanosleep(500);
+    }
+  }
+  if (a.status != nullptr) {
+    atomicOr(a.status, CKV_DEV_WAIT_TIMEOUT);
+  }
+}
+
 // Warps 0 .. merge_warps-1 merge the split partials; warp `merge_warps` is the update
 // warp: it merges the neighbour candidates and fetches everything the online
 // assignment needs while the other warps are still merging, then applies the
@@ -150,6 +174,12 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
       packed.x = *reinterpret_cast<const uint32_t*>(&lo);
       packed.y = *reinterpret_cast<const uint32_t*>(&hi);
       *reinterpret_cast<uint2*>(output + g * kHeadDim + 4 * lane) = packed;
+      // the same row, straight into every peer GPU's gathered tensor
+      for (int p = 0; p < a.peer_count; ++p) {
+        __nv_bfloat16* remote = reinterpret_cast<__nv_bfloat16*>(a.peer_output[p]) +
+                                static_cast<int64_t>(flat) * group * kHeadDim;
+        *reinterpret_cast<uint2*>(remote + g * kHeadDim + 4 * lane) = packed;
+      }
       const float lse = best + logf(denominator);
       if (lane == 0) {
         a.lse[static_cast<int64_t>(flat) * group + g] = lse;
@@ -232,6 +262,13 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
     }
   }
   __syncthreads();
+  if (a.peer_count > 0 && threadIdx.x == 0 && !update_only) {
+    // all output rows of this unit were stored before the barrier: publish them
+    __threadfence_system();
+    for (int p = 0; p < a.peer_count; ++p) {
+      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.peer_flag[p]) : "memory");
+    }
+  }
   // Centroid bytes of every community the token may join, fetched while the update
   // warp decides: the running-mean update below then needs no further round trip.
   uint8_t centroid_byte[kKappa + 1];

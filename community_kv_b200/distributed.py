@@ -14,14 +14,25 @@ Two decompositions follow from the independence of (sequence, layer, head) units
   and the ranks combine their partial ``(max, sum, out)`` triples with the
   log-sum-exp rule.
 
-Everything here is plain ``torch.distributed`` on tensors, so the logic also
+Everything above is plain ``torch.distributed`` on tensors, so the logic also
 runs on CPU with the ``gloo`` backend (that is how it is tested without GPUs).
+
+``PeerOutputExchange`` replaces the per-layer all-gather of head outputs by stores
+from inside the decode kernel: every rank's gathered tensor lives in symmetric
+memory, the merging CTA of each unit writes its output rows into every peer's
+tensor over NVLink and bumps a per-layer counter there, and the consumer waits
+for the counter (``ckv_wait_peers``) instead of running a collective.
 """
 
 from __future__ import annotations
 
+import ctypes
+import os
+
 import torch
 import torch.distributed as dist
+
+from community_kv_b200 import native
 
 
 def head_shard(kv_heads: int, world: int, rank: int) -> range:
@@ -133,3 +144,77 @@ __all__ = [
     "merge_topk",
     "sequence_shard",
 ]
+
+
+class PeerOutputExchange:
+    """Head outputs of all ranks, written by the decode kernels themselves.
+
+    ``gathered[launch, rank]`` (shape ``[slots, heads_local * G, 128]`` each) is this
+    rank's copy of everybody's outputs of one launch.  ``attach`` points a launch's
+    ``ckv_layer_args`` at the peers' slots and counters; ``wait`` enqueues the
+    bounded wait for the peers' rows of that launch.  No NVLink multicast object is
+    created (plain peer mappings only).
+    """
+
+    def __init__(self, *, launches: int, slots: int, heads: int, head_dim: int, units: int,
+                 device: torch.device, group: dist.ProcessGroup | None = None) -> None:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world - 1 > native.MAX_PEERS:
+            raise ValueError("at most %d peers" % native.MAX_PEERS)
+        self.units = units
+        self.gathered = symm_mem.empty(
+            (launches, self.world, slots, heads, head_dim), dtype=torch.bfloat16, device=device
+        )
+        self.flags = symm_mem.empty((max(launches, 4),), dtype=torch.int32, device=device)
+        self.gathered.zero_()
+        self.flags.zero_()
+        self.status = torch.zeros((1,), dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        outputs = symm_mem.rendezvous(self.gathered, group)
+        counters = symm_mem.rendezvous(self.flags, group)
+        self._output_ptrs = [int(p) for p in outputs.buffer_ptrs]
+        self._flag_ptrs = [int(p) for p in counters.buffer_ptrs]
+        self._slot_bytes = slots * heads * head_dim * 2
+        dist.barrier(group)
+
+    def local_output(self, launch: int) -> torch.Tensor:
+        """Where this rank's own kernels write: its slot of its own gathered tensor."""
+
+        return self.gathered[launch, self.rank]
+
+    def attach(self, args: "native.LayerArgs", launch: int, *, wait_in_kernel: bool = True) -> None:
+        """Point ``args`` at the peers.  With ``wait_in_kernel`` the launch itself ends
+        only when the peers' rows of this launch have arrived (no ``wait`` needed)."""
+
+        peers = [p for p in range(self.world) if p != self.rank]
+        if wait_in_kernel:
+            args.peer_wait_flag = self.flags.data_ptr() + 4 * launch
+            args.peer_wait_expected = (self.world - 1) * self.units
+            args.status = self.status.data_ptr()
+        args.peer_count = len(peers)
+        for index, peer in enumerate(peers):
+            args.peer_output[index] = self._output_ptrs[peer] + (launch * self.world + self.rank) * self._slot_bytes
+            args.peer_flag[index] = self._flag_ptrs[peer] + 4 * launch
+
+    def wait(self, launch: int, stream: int) -> None:
+        """Enqueue the wait for the peers' rows of ``launch`` (bounded; see ``check``)."""
+
+        status = native.library().ckv_wait_peers(
+            ctypes.c_void_p(self.flags.data_ptr() + 4 * launch),
+            ctypes.c_uint32((self.world - 1) * self.units),
+            ctypes.c_void_p(self.status.data_ptr()),
+            ctypes.c_void_p(stream),
+        )
+        if status:
+            raise native.NativeError(native.library().ckv_status_string(status).decode())
+
+    def check(self) -> None:
+        """Raise if any wait gave up (a peer never delivered its rows)."""
+
+        if int(self.status.item()) != 0:
+            raise RuntimeError("a bounded wait for peer head outputs timed out")

@@ -21,6 +21,9 @@ _f32 = ctypes.c_float
 _ptr = ctypes.c_void_p
 
 
+MAX_PEERS = 7  # CKV_MAX_PEERS
+
+
 class LayerArgs(ctypes.Structure):
     """Field-for-field mirror of ``struct ckv_layer_args``."""
 
@@ -97,6 +100,11 @@ class LayerArgs(ctypes.Structure):
         ("kv_row_count", _i32),
         ("merged", _ptr),
         ("current_key", _ptr),
+        ("peer_count", _i32),
+        ("peer_wait_expected", _i32),
+        ("peer_output", _ptr * MAX_PEERS),
+        ("peer_flag", _ptr * MAX_PEERS),
+        ("peer_wait_flag", _ptr),
         ("phase_times", _ptr),
     ]
 
@@ -166,6 +174,7 @@ ENTRY_POINTS = (
     "ckv_segmented_attention_static",
     "ckv_prefill_topk",
     "ckv_online_update",
+    "ckv_wait_peers",
 )
 
 
@@ -199,6 +208,8 @@ def library() -> ctypes.CDLL:
         function.argtypes = [ctypes.POINTER(LayerArgs), ctypes.c_void_p]
     lib.ckv_decode_layer_kernels.restype = ctypes.c_int
     lib.ckv_decode_layer_kernels.argtypes = [ctypes.POINTER(LayerArgs)]
+    lib.ckv_wait_peers.restype = ctypes.c_int
+    lib.ckv_wait_peers.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p]
     lib.ckv_prefill_topk.restype = ctypes.c_int
     lib.ckv_prefill_topk.argtypes = [ctypes.POINTER(PrefillArgs), ctypes.c_void_p]
     return lib
@@ -235,6 +246,7 @@ __all__ = [
     "FLAG_UNFUSED",
     "FLAG_UPDATE_ONLY",
     "LayerArgs",
+    "MAX_PEERS",
     "NativeError",
     "PARTIAL_STRIDE",
     "PrefillArgs",

@@ -56,6 +56,8 @@ typedef enum ckv_status {
 /* bits OR-ed into *status by the kernels */
 #define CKV_DEV_WAIT_TIMEOUT 1u /* a bounded mbarrier wait gave up */
 
+#define CKV_MAX_PEERS 7
+
 /* flags */
 #define CKV_FLAG_SKIP_UPDATE 1    /* attention only: leave the graph state untouched */
 #define CKV_FLAG_UPDATE_ONLY 4    /* ckv_online_update: take lse / topk_scores / topk_positions
@@ -147,6 +149,22 @@ typedef struct ckv_layer_args {
   const void* current_key;     /* optional bf16 [batch, R, 128]: key of the token being decoded
                                   (row of each retrieval head's KV head), used for the centroid
                                   update instead of a cache read */
+  /* ---- head-output exchange between GPUs (peer_count 0: none) ----
+   * With KV heads sharded over GPUs every GPU needs all heads' outputs.  Instead of a
+   * collective after the layer, the merging CTA stores its output rows straight into
+   * each peer's buffer over NVLink (peer_output[p] points at THIS GPU's slot of peer
+   * p's gathered tensor, same [batch, R, G, 128] layout as `output`) and then adds 1
+   * to peer_flag[p] with system-scope release.  The peer consumes the rows after
+   * ckv_wait_peers has seen (its peers' units) increments. */
+  int32_t peer_count;
+  int32_t peer_wait_expected;  /* with peer_wait_flag: increments this GPU expects per call */
+  void* peer_output[CKV_MAX_PEERS];
+  uint32_t* peer_flag[CKV_MAX_PEERS];
+  uint32_t* peer_wait_flag;    /* optional: THIS GPU's counter.  The CTA that merges unit 0 then
+                                  polls it (bounded, system-scope acquire) after its own work
+                                  until the peers' rows of this call have arrived and subtracts
+                                  peer_wait_expected, so that the launch completes only when the
+                                  gathered tensor is complete: no separate wait is needed */
   uint64_t* phase_times;       /* optional diagnostic [batch*R, 8, 16]: nanosecond timestamps
                                   (%globaltimer) that thread 0 of every CTA of the single-launch
                                   path writes at its phase boundaries: 0 start, 1 scored,
@@ -211,6 +229,14 @@ int ckv_segmented_attention(const ckv_layer_args* args, void* cuda_stream);
  * through cluster barriers.  Otherwise (or with CKV_FLAG_UNFUSED) the four
  * stand-alone kernels run back to back.  Results are identical either way. */
 int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream);
+
+/* Waits (on the stream, in a one-thread kernel with a bounded number of polls)
+ * until *flag >= expected, then subtracts `expected` from it.  `flag` is this GPU's
+ * counter that its peers' ckv_decode_layer calls increment once per unit after
+ * storing that unit's head outputs here.  On a timeout the kernel ORs
+ * CKV_DEV_WAIT_TIMEOUT into *status (which may be null) and returns.  No reference
+ * counterpart: the reference runs on one GPU. */
+int ckv_wait_peers(uint32_t* flag, uint32_t expected, uint32_t* status, void* cuda_stream);
 
 /* How many kernels ckv_decode_layer launches for these arguments (1, 4 or 5);
  * no reference counterpart, used for launch accounting. */
