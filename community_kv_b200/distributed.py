@@ -174,6 +174,7 @@ class PeerOutputExchange:
         self.gathered.zero_()
         self.flags.zero_()
         self.status = torch.zeros((1,), dtype=torch.int32, device=device)
+        self.done = torch.zeros((max(launches, 4),), dtype=torch.int32, device=device)  # local unit counters
         torch.cuda.synchronize(device)
         outputs = symm_mem.rendezvous(self.gathered, group)
         counters = symm_mem.rendezvous(self.flags, group)
@@ -192,9 +193,10 @@ class PeerOutputExchange:
         only when the peers' rows of this launch have arrived (no ``wait`` needed)."""
 
         peers = [p for p in range(self.world) if p != self.rank]
+        args.peer_done = self.done.data_ptr() + 4 * launch
         if wait_in_kernel:
             args.peer_wait_flag = self.flags.data_ptr() + 4 * launch
-            args.peer_wait_expected = (self.world - 1) * self.units
+            args.peer_wait_expected = self.world - 1
             args.status = self.status.data_ptr()
         args.peer_count = len(peers)
         for index, peer in enumerate(peers):
@@ -206,7 +208,7 @@ class PeerOutputExchange:
 
         status = native.library().ckv_wait_peers(
             ctypes.c_void_p(self.flags.data_ptr() + 4 * launch),
-            ctypes.c_uint32((self.world - 1) * self.units),
+            ctypes.c_uint32(self.world - 1),
             ctypes.c_void_p(self.status.data_ptr()),
             ctypes.c_void_p(stream),
         )

@@ -104,6 +104,7 @@ class LayerArgs(ctypes.Structure):
         ("peer_wait_expected", _i32),
         ("peer_output", _ptr * MAX_PEERS),
         ("peer_flag", _ptr * MAX_PEERS),
+        ("peer_done", _ptr),
         ("peer_wait_flag", _ptr),
         ("phase_times", _ptr),
     ]

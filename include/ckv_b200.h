@@ -160,6 +160,11 @@ typedef struct ckv_layer_args {
   int32_t peer_wait_expected;  /* with peer_wait_flag: increments this GPU expects per call */
   void* peer_output[CKV_MAX_PEERS];
   uint32_t* peer_flag[CKV_MAX_PEERS];
+  uint32_t* peer_done;         /* optional: a counter in THIS GPU's memory (zero before the first
+                                  call).  When set, units count themselves here and only the last
+                                  unit of the call signals the peers: one increment per peer and
+                                  call instead of one per unit (remote atomics on one word are
+                                  slow), so the consumer expects (number of peers) per call */
   uint32_t* peer_wait_flag;    /* optional: THIS GPU's counter.  The CTA that merges unit 0 then
                                   polls it (bounded, system-scope acquire) after its own work
                                   until the peers' rows of this call have arrived and subtracts
