@@ -804,6 +804,13 @@ __global__ void __launch_bounds__(128) exact_edges_kernel(const ckv_prefill_args
   const __nv_bfloat16* k_base = reinterpret_cast<const __nv_bfloat16*>(a.key) +
                                 batch * a.k_batch_stride + kv_head * a.k_head_stride;
   const int candidates = group * kExactKeep;  // <= 128
+  // the position's query rows, staged once per warp (every candidate reuses them)
+  __shared__ uint4 q_stage[4][8 * 16];
+  for (int index = lane; index < group * 16; index += 32) {
+    q_stage[warp][index] = *reinterpret_cast<const uint4*>(q_base + (index >> 4) * a.q_head_stride +
+                                                           (index & 15) * 8);
+  }
+  __syncwarp();
   uint64_t best_key[4];
   float best_dropped = -INFINITY;  // best approximate score among the keys turned away
   if (lane < group) {
@@ -824,21 +831,32 @@ __global__ void __launch_bounds__(128) exact_edges_kernel(const ckv_prefill_args
       continue;
     }
     const int j = static_cast<int>(0xffffffffu - static_cast<uint32_t>(packed));
-    const __nv_bfloat16* k_row = k_base + static_cast<int64_t>(j) * a.k_row_stride;
+    const uint4* k_row = reinterpret_cast<const uint4*>(k_base + static_cast<int64_t>(j) * a.k_row_stride);
+    uint4 k_reg[16];
+#pragma unroll
+    for (int piece = 0; piece < 16; ++piece) {
+      k_reg[piece] = k_row[piece];
+    }
     float score = -INFINITY;
     for (int g = 0; g < group; ++g) {
-      const __nv_bfloat16* q_row = q_base + g * a.q_head_stride;
+      // eight slices of 16 sequential mixed-precision FMAs (bf16 x bf16 + fp32, one
+      // rounding each), combined in the fixed order
       float part[8];
 #pragma unroll
       for (int piece = 0; piece < 8; ++piece) {
+        const uint4 q0 = q_stage[warp][g * 16 + 2 * piece];
+        const uint4 q1 = q_stage[warp][g * 16 + 2 * piece + 1];
+        const uint4 k0 = k_reg[2 * piece];
+        const uint4 k1 = k_reg[2 * piece + 1];
         float acc = 0.f;
-#pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          const uint32_t kk = *reinterpret_cast<const uint32_t*>(k_row + piece * 16 + e);
-          const uint32_t qq = *reinterpret_cast<const uint32_t*>(q_row + piece * 16 + e);
-          acc = __fmaf_rn(bf16_lo(kk), bf16_lo(qq), acc);
-          acc = __fmaf_rn(bf16_hi(kk), bf16_hi(qq), acc);
-        }
+        acc = fma2_bf16(k0.x, q0.x, acc);
+        acc = fma2_bf16(k0.y, q0.y, acc);
+        acc = fma2_bf16(k0.z, q0.z, acc);
+        acc = fma2_bf16(k0.w, q0.w, acc);
+        acc = fma2_bf16(k1.x, q1.x, acc);
+        acc = fma2_bf16(k1.y, q1.y, acc);
+        acc = fma2_bf16(k1.z, q1.z, acc);
+        acc = fma2_bf16(k1.w, q1.w, acc);
         part[piece] = acc;
       }
       const float even = __fadd_rn(__fadd_rn(part[0], part[4]), __fadd_rn(part[2], part[6]));
@@ -876,45 +894,82 @@ __global__ void __launch_bounds__(128) exact_edges_kernel(const ckv_prefill_args
     }
   }
   if (lane == 0 && a.edge_flags != nullptr) {
-    a.edge_flags[(static_cast<int64_t>(batch) * a.kv_heads + kv_head) * rows + (pos - skip)] =
-        (best_dropped + a.exact_slack >= last_score) ? 1 : 0;
+    const int flagged = (best_dropped + a.exact_slack >= last_score) ? 1 : 0;
+    a.edge_flags[item] = flagged;
+    if (flagged && a.rescan_list != nullptr) {
+      const int slot = atomicAdd(a.rescan_list, 1);
+      a.rescan_list[1 + slot] = static_cast<int>(item);
+    }
   }
 }
 
-// Brute-force exact top-m of flagged rows (rare): one CTA per (batch, kv head, row).
+// Exact top-m of the rows whose short list could not be proven complete, by a full
+// scan of the row's keys.  256 threads per row: every thread scores the keys
+// j = tid, tid + 256, ... in the fixed fp32 order and keeps its own sorted top-m; the
+// 256 lists are then merged m times by a block-wide maximum.  CTAs take rows from the
+// queue exact_edges_kernel filled (or, without a queue, poll every row's flag).
 __global__ void __launch_bounds__(256) exact_rescan_kernel(const ckv_prefill_args a, int group) {
-  __shared__ uint64_t s_best[256];
+  __shared__ uint4 q_stage[8 * 16];
+  __shared__ uint64_t lists[256 * kExactKeep];
+  __shared__ uint64_t warp_best[8];
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
   const int length = a.seq_len;
   const int skip = a.num_sink + a.edges_per_row - 1;
   const int rows = length - skip;
-  const int64_t item = blockIdx.x;
-  if (a.edge_flags[item] == 0) {
-    return;
-  }
-  const int pos = skip + static_cast<int>(item % rows);
-  const int kv_head = static_cast<int>((item / rows) % a.kv_heads);
-  const int batch = static_cast<int>(item / (static_cast<int64_t>(rows) * a.kv_heads));
-  const __nv_bfloat16* q_base = reinterpret_cast<const __nv_bfloat16*>(a.query) +
-                                batch * a.q_batch_stride + static_cast<int64_t>(pos) * a.q_row_stride +
-                                kv_head * group * a.q_head_stride;
-  const __nv_bfloat16* k_base = reinterpret_cast<const __nv_bfloat16*>(a.key) +
-                                batch * a.k_batch_stride + kv_head * a.k_head_stride;
-  const int64_t out_base = item * a.edges_per_row;
-  uint64_t previous = ~0ull;
-  for (int rank = 0; rank < a.edges_per_row; ++rank) {
-    uint64_t local = 0ull;
-    for (int j = a.num_sink + threadIdx.x; j <= pos; j += 256) {
-      const __nv_bfloat16* k_row = k_base + static_cast<int64_t>(j) * a.k_row_stride;
+  const int64_t total = static_cast<int64_t>(a.batch) * a.kv_heads * rows;
+  const bool queued = a.rescan_list != nullptr;
+  const int64_t work = queued ? a.rescan_list[0] : total;
+  for (int64_t w = blockIdx.x; w < work; w += gridDim.x) {
+    const int64_t item = queued ? a.rescan_list[1 + w] : w;
+    if (!queued && a.edge_flags[item] == 0) {
+      continue;
+    }
+    const int pos = skip + static_cast<int>(item % rows);
+    const int kv_head = static_cast<int>((item / rows) % a.kv_heads);
+    const int batch = static_cast<int>(item / (static_cast<int64_t>(rows) * a.kv_heads));
+    const __nv_bfloat16* q_base = reinterpret_cast<const __nv_bfloat16*>(a.query) +
+                                  batch * a.q_batch_stride + static_cast<int64_t>(pos) * a.q_row_stride +
+                                  kv_head * group * a.q_head_stride;
+    const __nv_bfloat16* k_base = reinterpret_cast<const __nv_bfloat16*>(a.key) +
+                                  batch * a.k_batch_stride + kv_head * a.k_head_stride;
+    __syncthreads();  // the previous row's shared memory is no longer read
+    for (int index = tid; index < group * 16; index += 256) {
+      q_stage[index] = *reinterpret_cast<const uint4*>(q_base + (index >> 4) * a.q_head_stride +
+                                                       (index & 15) * 8);
+    }
+    __syncthreads();
+    uint64_t mine[kExactKeep];
+#pragma unroll
+    for (int k = 0; k < kExactKeep; ++k) {
+      mine[k] = 0ull;
+    }
+    for (int j = a.num_sink + tid; j <= pos; j += 256) {
+      const uint4* k_row = reinterpret_cast<const uint4*>(k_base + static_cast<int64_t>(j) * a.k_row_stride);
+      uint4 k_reg[16];
+#pragma unroll
+      for (int piece = 0; piece < 16; ++piece) {
+        k_reg[piece] = k_row[piece];
+      }
       float score = -INFINITY;
       for (int g = 0; g < group; ++g) {
-        const __nv_bfloat16* q_row = q_base + g * a.q_head_stride;
         float part[8];
+#pragma unroll
         for (int piece = 0; piece < 8; ++piece) {
+          const uint4 q0 = q_stage[g * 16 + 2 * piece];
+          const uint4 q1 = q_stage[g * 16 + 2 * piece + 1];
+          const uint4 k0 = k_reg[2 * piece];
+          const uint4 k1 = k_reg[2 * piece + 1];
           float acc = 0.f;
-          for (int e = 0; e < 16; ++e) {
-            acc = __fmaf_rn(__bfloat162float(k_row[piece * 16 + e]),
-                            __bfloat162float(q_row[piece * 16 + e]), acc);
-          }
+          acc = fma2_bf16(k0.x, q0.x, acc);
+          acc = fma2_bf16(k0.y, q0.y, acc);
+          acc = fma2_bf16(k0.z, q0.z, acc);
+          acc = fma2_bf16(k0.w, q0.w, acc);
+          acc = fma2_bf16(k1.x, q1.x, acc);
+          acc = fma2_bf16(k1.y, q1.y, acc);
+          acc = fma2_bf16(k1.z, q1.z, acc);
+          acc = fma2_bf16(k1.w, q1.w, acc);
           part[piece] = acc;
         }
         const float even = __fadd_rn(__fadd_rn(part[0], part[4]), __fadd_rn(part[2], part[6]));
@@ -923,26 +978,336 @@ __global__ void __launch_bounds__(256) exact_rescan_kernel(const ckv_prefill_arg
       }
       const uint64_t packed = (static_cast<uint64_t>(ordered_key32(score)) << 32) |
                               (0xffffffffu - static_cast<uint32_t>(j));
-      if (packed < previous && packed > local) {
-        local = packed;
+      if (packed > mine[kExactKeep - 1]) {
+        queue_insert64(mine, packed);
       }
     }
-    s_best[threadIdx.x] = local;
-    __syncthreads();
-    for (int stride = 128; stride > 0; stride >>= 1) {
-      if (threadIdx.x < stride && s_best[threadIdx.x + stride] > s_best[threadIdx.x]) {
-        s_best[threadIdx.x] = s_best[threadIdx.x + stride];
+#pragma unroll
+    for (int k = 0; k < kExactKeep; ++k) {
+      lists[tid * kExactKeep + k] = mine[k];
+    }
+    int head = 0;  // next unused entry of this thread's (sorted) list
+    const int64_t out_base = item * a.edges_per_row;
+    for (int rank = 0; rank < a.edges_per_row; ++rank) {
+      const uint64_t offer = head < kExactKeep ? lists[tid * kExactKeep + head] : 0ull;
+      const uint64_t best_in_warp = warp_max_u64(offer);
+      if (lane == 0) {
+        warp_best[warp] = best_in_warp;
+      }
+      __syncthreads();
+      uint64_t winner = warp_best[0];
+#pragma unroll
+      for (int other = 1; other < 8; ++other) {
+        winner = warp_best[other] > winner ? warp_best[other] : winner;
+      }
+      if (winner != 0ull && offer == winner) {
+        head += 1;  // keys are distinct, so exactly one thread advances
+      }
+      if (tid == 0) {
+        a.edge_idx[out_base + rank] =
+            winner == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(winner));
+        a.edge_score[out_base + rank] =
+            winner == 0ull ? -INFINITY : key32_to_float(static_cast<uint32_t>(winner >> 32));
       }
       __syncthreads();
     }
-    previous = s_best[0];
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      a.edge_idx[out_base + rank] =
-          previous == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(previous));
-      a.edge_score[out_base + rank] =
-          previous == 0ull ? -INFINITY : key32_to_float(static_cast<uint32_t>(previous >> 32));
+  }
+}
+
+
+// ---- candidate lists for the exact top-m, as a kernel of its own (G = 2 or 4) ----
+//
+// The exact edges rank keys by the maximum of the G heads' scores.  In the attention
+// kernel above a row is one (position, head) pair, so that maximum needs a
+// reduction across lanes for every key.  Here a row is a POSITION: the G heads of a
+// KV head are G separate Q tiles (128 positions x 128 dims each) multiplied against
+// the same K tile, their score tiles sit side by side in tensor memory, and the
+// thread that owns a position reads the same columns of all G tiles and takes the
+// maximum in registers.  No softmax, no P.V: half the tensor work of attention and a
+// handful of CUDA-core instructions per key.
+//
+// 288 threads.  Warp 8 (one lane) is the producer: Q and K tiles by TMA, the
+// tcgen05.mma chains, tcgen05.commit onto mbarriers.  Keys are processed in
+// sub-blocks of 64; the two worker warpgroups (warps 0-3, 4-7) take even and odd
+// sub-blocks, each with its own score buffer in tensor memory (G x 64 columns), so
+// the tensor cores fill one buffer while the other is being read.  Every worker
+// thread keeps the 16 best (score, key) pairs of its position and its sub-blocks in
+// registers, plus the best score it turned away; the two threads of a position tell
+// each other their 16th score through shared memory (the position's 16th best is at
+// least the larger of the two, so anything clearly below it is turned away at once);
+// the two lists go to the candidate array that exact_edges_kernel re-scores.
+constexpr int kEdgeThreads = 288;
+constexpr int kEdgeSub = 64;  // keys per sub-block
+
+__device__ __forceinline__ uint32_t instruction_descriptor_n64() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((kEdgeSub >> 3) << 17) | ((kPfRows >> 4) << 24);
+}
+
+__device__ __forceinline__ void tmem_load16_issue(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int kKeep>
+__device__ __forceinline__ uint64_t list_insert(uint64_t (&list)[kKeep], uint64_t candidate) {
+#pragma unroll
+  for (int k = 0; k < kKeep; ++k) {
+    const uint64_t resident = list[k];
+    const bool greater = candidate > resident;
+    list[k] = greater ? candidate : resident;
+    candidate = greater ? resident : candidate;
+  }
+  return candidate;
+}
+
+struct EdgeSmem {
+  static constexpr int kQ = 0;                       // kGroup tiles
+  static constexpr int kBarBytes = 128 + 2 * kPfRows * 4;  // barriers, then the floors
+  static constexpr int total(int group) { return (group + 2) * kTileBytes + kBarBytes; }
+};
+
+template <int kGroup>
+__global__ void __launch_bounds__(kEdgeThreads, 1)
+    edge_candidates_kernel(const ckv_prefill_args a, const __grid_constant__ CUtensorMap map_q,
+                           const __grid_constant__ CUtensorMap map_k) {
+  static_assert(kGroup == 2 || kGroup == 4, "two or four heads per KV head");
+  constexpr int kKeep = kExactKeep;               // per thread; two threads per position
+  constexpr int kBufferColumns = kGroup * kEdgeSub;  // tensor-memory columns of one score buffer
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* s_q = smem;
+  uint8_t* s_k = smem + kGroup * kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (kGroup + 2) * kTileBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile float* floors = reinterpret_cast<volatile float*>(bars + 16);  // [2][128]
+  const uint32_t bar_q = smem_u32(bars);           // Q tiles landed
+  const uint32_t bar_k_full = smem_u32(bars + 1);  // two: K buffer filled
+  const uint32_t bar_k_free = smem_u32(bars + 3);  // two: every MMA reading the K buffer is done
+  const uint32_t bar_s_full = smem_u32(bars + 5);  // two: score buffer written
+  const uint32_t bar_s_free = smem_u32(bars + 7);  // two: score buffer read by its 128 workers
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int tile = gridDim.x - 1 - blockIdx.x;  // longest tiles first
+  const int kv_head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int length = a.seq_len;
+  const int pos0 = tile * kPfRows;
+  const int last_pos = min(length, pos0 + kPfRows) - 1;
+  const int key_blocks = last_pos / kPfKeys + 1;
+  const int sub_total = last_pos / kEdgeSub + 1;
+
+  if (tid < 2 * kPfRows) {
+    floors[tid] = -INFINITY;
+  }
+  if (tid == 0) {
+    mbar_init(bar_q, 1);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_k_full + 8 * i, 1);
+      mbar_init(bar_k_free + 8 * i, 1);
+      mbar_init(bar_s_full + 8 * i, 1);
+      mbar_init(bar_s_free + 8 * i, 128);
     }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  bool failed = false;
+
+  if (warp == 8) {
+    // ---- producer: one lane ----
+    if (tid == 256) {
+      mbar_expect_tx(bar_q, kGroup * kTileBytes);
+#pragma unroll
+      for (int h = 0; h < kGroup; ++h) {
+        asm volatile(
+            "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+            "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(smem_u32(s_q) + h * kTileBytes),
+            "l"(&map_q), "r"(0), "r"(pos0), "r"(0), "r"(kv_head * kGroup + h), "r"(batch), "r"(bar_q)
+            : "memory");
+      }
+      tma_load_tile(smem_u32(s_k), &map_k, bar_k_full, 0, kv_head, batch);
+      if (key_blocks > 1) {
+        tma_load_tile(smem_u32(s_k) + kTileBytes, &map_k, bar_k_full + 8, kPfKeys, kv_head, batch);
+      }
+      const uint32_t idesc = instruction_descriptor_n64();
+      failed = !mbar_wait(bar_q, 0);
+      for (int sb = 0; sb < sub_total && !failed; ++sb) {
+        const int kb = sb >> 1;
+        const int kbuf = kb & 1;
+        const int sbuf = sb & 1;
+        if ((sb & 1) == 0) {
+          // tile kb+1 goes where tile kb-1 was, once the MMAs that read it are done
+          if (kb >= 1 && kb + 1 < key_blocks) {
+            if (!mbar_wait(bar_k_free + 8 * (kbuf ^ 1), ((kb - 1) >> 1) & 1)) {
+              failed = true;
+              break;
+            }
+            tma_load_tile(smem_u32(s_k) + (kbuf ^ 1) * kTileBytes, &map_k, bar_k_full + 8 * (kbuf ^ 1),
+                          (kb + 1) * kPfKeys, kv_head, batch);
+          }
+          if (!mbar_wait(bar_k_full + 8 * kbuf, (kb >> 1) & 1)) {
+            failed = true;
+            break;
+          }
+        }
+        if (sb >= 2 && !mbar_wait(bar_s_free + 8 * sbuf, ((sb >> 1) - 1) & 1)) {
+          failed = true;
+          break;
+        }
+        tc_fence_after();
+        // keys [64 * (sb & 1), +64) of the K tile: rows are 16 bytes apart inside a chunk
+        const uint32_t k_base = smem_u32(s_k) + kbuf * kTileBytes + (sb & 1) * kEdgeSub * 16;
+#pragma unroll
+        for (int h = 0; h < kGroup; ++h) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t desc_q =
+                smem_descriptor(smem_u32(s_q) + h * kTileBytes + ks * 4096, 2048, 128);
+            const uint64_t desc_k = smem_descriptor(k_base + ks * 4096, 2048, 128);
+            umma(tmem + sbuf * kBufferColumns + h * kEdgeSub, desc_q, desc_k, idesc, ks > 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(bar_s_full + 8 * sbuf);
+        if ((sb & 1) == 1 || sb == sub_total - 1) {
+          umma_commit(bar_k_free + 8 * kbuf);
+        }
+      }
+      if (failed && a.status != nullptr) {
+        atomicOr(a.status, CKV_DEV_WAIT_TIMEOUT);
+      }
+    }
+  } else {
+    // ---- workers: warpgroup `wg` reads score buffer `wg` (sub-blocks wg, wg+2, ...) ----
+    const int wg = warp >> 2;
+    const int row = tid & (kPfRows - 1);
+    const int row_pos = pos0 + row;
+    const bool row_live = row_pos < length;
+    const uint32_t lane_base = tmem + (((warp & 3) * 32u) << 16) + wg * kBufferColumns;
+    uint64_t list[kKeep];
+#pragma unroll
+    for (int k = 0; k < kKeep; ++k) {
+      list[k] = 0ull;
+    }
+    float dropped = -INFINITY;
+    for (int sb = wg; sb < sub_total; sb += 2) {
+      if (!mbar_wait(bar_s_full + 8 * wg, (sb >> 1) & 1)) {
+        failed = true;
+        break;
+      }
+      tc_fence_after();
+      const int key0 = sb * kEdgeSub;
+      const bool plain = key0 + kEdgeSub - 1 <= pos0 && key0 >= a.num_sink;  // no mask, no sinks
+      const uint64_t last = list[kKeep - 1];
+      const float own_floor =
+          last == 0ull ? -INFINITY : key32_to_float(static_cast<uint32_t>(last >> 32));
+      floors[wg * kPfRows + row] = own_floor;
+      // the other list's 16th score, a little low (any earlier value is also valid)
+      const float partner_floor = floors[(wg ^ 1) * kPfRows + row] - 2.0f * a.exact_slack;
+      float floor_score = fmaxf(own_floor, partner_floor);
+#pragma unroll 1
+      for (int c0 = 0; c0 < kEdgeSub; c0 += 16) {
+        uint32_t raw[kGroup][16];
+#pragma unroll
+        for (int h = 0; h < kGroup; ++h) {
+          tmem_load16_issue(lane_base + h * kEdgeSub + c0, raw[h]);
+        }
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        float best[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float m = __uint_as_float(raw[0][i]);
+#pragma unroll
+          for (int h = 1; h < kGroup; ++h) {
+            m = fmaxf(m, __uint_as_float(raw[h][i]));
+          }
+          const int j = key0 + c0 + i;
+          const bool visible = plain || (j <= row_pos && j >= a.num_sink);
+          best[i] = visible ? m * a.softmax_scale : -INFINITY;
+        }
+        // Columns that beat the floor, as a bit mask.  The lanes then insert in
+        // rounds: in every round each lane that still has such a column inserts its
+        // next one, so a chunk costs as many passes over the insertion code as the
+        // busiest lane has columns, not as many as there are columns with a taker.
+        uint32_t takers = 0u;
+        float rejected = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const bool take = row_live && best[i] > floor_score;
+          takers |= (take ? 1u : 0u) << i;
+          rejected = fmaxf(rejected, take ? -INFINITY : best[i]);
+        }
+        dropped = fmaxf(dropped, rejected);
+        while (__any_sync(0xffffffffu, takers != 0u)) {
+          if (takers != 0u) {
+            const int i = __ffs(takers) - 1;
+            takers &= takers - 1;
+            float v = best[0];
+#pragma unroll
+            for (int k = 1; k < 16; ++k) {
+              v = i == k ? best[k] : v;
+            }
+            if (v > floor_score) {
+              const uint64_t candidate = (static_cast<uint64_t>(ordered_key32(v)) << 32) |
+                                         (0xffffffffu - static_cast<uint32_t>(key0 + c0 + i));
+              const uint64_t lost = list_insert<kKeep>(list, candidate);
+              if (lost != 0ull) {
+                dropped = fmaxf(dropped, key32_to_float(static_cast<uint32_t>(lost >> 32)));
+              }
+              const uint64_t tail = list[kKeep - 1];
+              floor_score = fmaxf(
+                  partner_floor,
+                  tail == 0ull ? -INFINITY : key32_to_float(static_cast<uint32_t>(tail >> 32)));
+            } else {
+              dropped = fmaxf(dropped, v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_s_free + 8 * wg);
+    }
+    if (row_live && !failed) {
+      // [batch, kv head, position, G lanes, 16 kept + best dropped]: this thread's list
+      // is lane `wg` (the other lanes stay empty)
+      uint64_t* out = a.candidates +
+                      ((static_cast<int64_t>(batch) * gridDim.y + kv_head) * length + row_pos) *
+                          kGroup * (kExactKeep + 1);
+#pragma unroll
+      for (int k = 0; k < kKeep; ++k) {
+        out[wg * (kExactKeep + 1) + k] = list[k];
+      }
+      out[wg * (kExactKeep + 1) + kExactKeep] =
+          dropped != -INFINITY ? static_cast<uint64_t>(ordered_key32(dropped)) << 32 : 0ull;
+    }
+    if (failed && a.status != nullptr) {
+      atomicOr(a.status, CKV_DEV_WAIT_TIMEOUT);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512)
+                 : "memory");
   }
 }
 
@@ -967,8 +1332,8 @@ PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
 // K or V [batch, rows, kv heads, 128] bf16 seen as (8 elements, rows, 16 chunks of
 // 16 bytes, kv heads, batch): one box of (8, 128, 16, 1, 1) lands in shared memory as
 // 16 chunks of 128 rows x 16 bytes, which is the tensor-core operand layout.
-bool tile_map(CUtensorMap* map, const void* base, const ckv_prefill_args& a, int64_t row_stride,
-              int64_t head_stride, int64_t batch_stride) {
+bool tile_map(CUtensorMap* map, const void* base, const ckv_prefill_args& a, int heads,
+              int64_t row_stride, int64_t head_stride, int64_t batch_stride) {
   const auto encoder = tensor_map_encoder();
   if (encoder == nullptr || (reinterpret_cast<uintptr_t>(base) & 15u) != 0) {
     return false;
@@ -976,14 +1341,14 @@ bool tile_map(CUtensorMap* map, const void* base, const ckv_prefill_args& a, int
   const uint64_t row_bytes = static_cast<uint64_t>(row_stride) * 2;
   // a dimension of extent 1 never uses its stride; give it a legal one
   const uint64_t head_bytes =
-      a.kv_heads > 1 ? static_cast<uint64_t>(head_stride) * 2 : static_cast<uint64_t>(kHeadDim) * 2;
+      heads > 1 ? static_cast<uint64_t>(head_stride) * 2 : static_cast<uint64_t>(kHeadDim) * 2;
   const uint64_t batch_bytes =
       a.batch > 1 ? static_cast<uint64_t>(batch_stride) * 2 : row_bytes * static_cast<uint64_t>(a.seq_len);
   if (row_stride <= 0 || (row_bytes & 15u) || (head_bytes & 15u) || (batch_bytes & 15u)) {
     return false;
   }
   const cuuint64_t extent[5] = {8, static_cast<cuuint64_t>(a.seq_len), 16,
-                                static_cast<cuuint64_t>(a.kv_heads), static_cast<cuuint64_t>(a.batch)};
+                                static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(a.batch)};
   const cuuint64_t strides[4] = {row_bytes, 16, head_bytes, batch_bytes};
   const cuuint32_t box[5] = {8, kPfKeys, 16, 1, 1};
   const cuuint32_t steps[5] = {1, 1, 1, 1, 1};
@@ -997,8 +1362,8 @@ cudaError_t launch_for_group(const ckv_prefill_args& a, cudaStream_t stream) {
   constexpr int kSmem = PrefillSmem::kTotal;
   const dim3 grid((a.seq_len + kPfRows / kGroup - 1) / (kPfRows / kGroup), a.kv_heads, a.batch);
   CUtensorMap map_k, map_v;
-  if (!tile_map(&map_k, a.key, a, a.k_row_stride, a.k_head_stride, a.k_batch_stride) ||
-      !tile_map(&map_v, a.value, a, a.v_row_stride, a.v_head_stride, a.v_batch_stride)) {
+  if (!tile_map(&map_k, a.key, a, a.kv_heads, a.k_row_stride, a.k_head_stride, a.k_batch_stride) ||
+      !tile_map(&map_v, a.value, a, a.kv_heads, a.v_row_stride, a.v_head_stride, a.v_batch_stride)) {
     return cudaErrorInvalidValue;
   }
   auto run = [&](auto kernel) -> cudaError_t {
@@ -1014,9 +1379,34 @@ cudaError_t launch_for_group(const ckv_prefill_args& a, cudaStream_t stream) {
 
 }  // namespace
 
+// Exact edges with two or four heads per KV head: attention by itself, then the
+// candidate lists from the position-per-row kernel.
+template <int kGroup>
+cudaError_t launch_candidates(const ckv_prefill_args& a, cudaStream_t stream) {
+  ckv_prefill_args attention = a;
+  attention.mode = 0;
+  cudaError_t err = launch_for_group<kGroup>(attention, stream);
+  if (err != cudaSuccess) return err;
+  CUtensorMap map_q, map_k;
+  if (!tile_map(&map_q, a.query, a, a.query_heads, a.q_row_stride, a.q_head_stride, a.q_batch_stride) ||
+      !tile_map(&map_k, a.key, a, a.kv_heads, a.k_row_stride, a.k_head_stride, a.k_batch_stride)) {
+    return cudaErrorInvalidValue;
+  }
+  constexpr int kSmem = EdgeSmem::total(kGroup);
+  err = cudaFuncSetAttribute(edge_candidates_kernel<kGroup>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  if (err != cudaSuccess) return err;
+  const dim3 grid((a.seq_len + kPfRows - 1) / kPfRows, a.kv_heads, a.batch);
+  edge_candidates_kernel<kGroup><<<grid, kEdgeThreads, kSmem, stream>>>(a, map_q, map_k);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_prefill(const ckv_prefill_args& a, cudaStream_t stream) {
   const int group = a.query_heads / a.kv_heads;
   cudaError_t err;
+  if (a.mode == 2 && (group == 2 || group == 4)) {
+    err = group == 2 ? launch_candidates<2>(a, stream) : launch_candidates<4>(a, stream);
+  } else
   switch (group) {
     case 1: err = launch_for_group<1>(a, stream); break;
     case 2: err = launch_for_group<2>(a, stream); break;
@@ -1037,7 +1427,8 @@ cudaError_t launch_prefill(const ckv_prefill_args& a, cudaStream_t stream) {
   if (err != cudaSuccess || a.edge_flags == nullptr) {
     return err;
   }
-  exact_rescan_kernel<<<static_cast<unsigned>(items), 256, 0, stream>>>(a, group);
+  const long long rescan_grid = a.rescan_list != nullptr ? (items < 148 * 4 ? items : 148 * 4) : items;
+  exact_rescan_kernel<<<static_cast<unsigned>(rescan_grid), 256, 0, stream>>>(a, group);
   return cudaGetLastError();
 }
 

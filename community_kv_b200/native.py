@@ -148,6 +148,7 @@ class PrefillArgs(ctypes.Structure):
         ("edge_score", _ptr),
         ("edge_flags", _ptr),
         ("status", _ptr),
+        ("rescan_list", _ptr),
     ]
 
 

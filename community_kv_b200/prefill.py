@@ -136,12 +136,14 @@ def prefill_attention_edges(
     edge_idx = torch.full((batch, kv_heads, rows, edges_per_row), -1, dtype=torch.int32, device=device)
     edge_score = torch.zeros((batch, kv_heads, rows, edges_per_row), dtype=torch.float32, device=device)
     flags = torch.zeros((batch, kv_heads, rows), dtype=torch.int32, device=device)
+    rescan_list = torch.zeros((1 + batch * kv_heads * rows,), dtype=torch.int32, device=device)
     native.fill(
         args,
         candidates=candidates.data_ptr(),
         edge_idx=edge_idx.data_ptr(),
         edge_score=edge_score.data_ptr(),
         edge_flags=flags.data_ptr(),
+        rescan_list=rescan_list.data_ptr(),
     )
     native.call("ckv_prefill_topk", args, native.current_stream(device))
     del keep

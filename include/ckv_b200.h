@@ -209,6 +209,10 @@ typedef struct ckv_prefill_args {
   float* edge_score;       /* mode 2: same shape, scaled scores */
   int32_t* edge_flags;     /* mode 2, optional: [batch, kv_heads, rows]; 1 = row was re-scanned */
   uint32_t* status;        /* one device word, may be null */
+  int32_t* rescan_list;    /* mode 2, optional scratch: [1 + batch*kv_heads*rows] int32, element 0
+                              zero on entry.  Rows whose short list cannot be proven complete are
+                              queued here and re-ranked by a full scan; without it every row's
+                              flag is polled instead (slower) */
 } ckv_prefill_args;
 
 /* Library version: major*10000 + minor*100 + patch. */
