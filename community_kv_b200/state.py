@@ -46,9 +46,18 @@ def choose_splits(token_budget: int, units: int, requested: int | None = None) -
     By default the (sequence, head) units of one launch share a single wave of
     resident CTAs; a head's tokens are cut into 16-token steps, so at most
     ``token_budget // 16`` (and never more than 32) CTAs can work on one head.
+    With few units the default stops at eight, the largest thread-block cluster,
+    so that ``ckv_decode_layer`` stays a single launch.
     """
 
-    wanted = requested if requested else max(1, RESIDENT_ATTENTION_CTAS // max(units, 1))
+    if requested:
+        wanted = requested
+    else:
+        wanted = max(1, RESIDENT_ATTENTION_CTAS // max(units, 1))
+        # Up to eight splits the whole layer is one cluster launch; more only pay off when
+        # a split would otherwise have to walk through more than 512 tokens.
+        if wanted > 8 and token_budget // 8 <= 512:
+            wanted = 8
     return max(1, min(wanted, 32, token_budget // 16))
 
 

@@ -94,7 +94,9 @@ def test_selection_workspace_contract():
     assert batched.selection.scores.shape == (3, 2, 32)
     assert batched.attention.output.shape == (3, 8, 128)
     assert batched.attention.partials.shape[-1] == native.PARTIAL_STRIDE
-    assert choose_splits(2048, 64) == 6 and choose_splits(2048, 1) == 32 and choose_splits(64, 8, 9) == 4
+    assert choose_splits(2048, 64) == 6 and choose_splits(64, 8, 9) == 4
+    # few units: eight (one cluster launch) unless a split would exceed 512 tokens
+    assert choose_splits(2048, 1) == 8 and choose_splits(8192, 8) == 32 and choose_splits(2048, 1, 32) == 32
 
 
 def test_operators_validate_before_launch_and_refuse_cpu():
