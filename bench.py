@@ -68,7 +68,8 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--peer-wait", choices=["node", "launch"], default="node",
                         help="peer exchange: wait for the peers' rows in a one-thread kernel after each layer "
                              "(node) or inside the layer launch itself (launch)")
-    parser.add_argument("--workload", choices=["decode", "prefill"], default="decode",
+    parser.add_argument("--sweep-context", type=int, default=1_048_576)
+    parser.add_argument("--workload", choices=["decode", "prefill", "sweep"], default="decode",
                         help="prefill: the score-graph emission kernel at S=16384 (a second, separate line)")
     parser.add_argument("--prefill-length", type=int, default=16384)
     return parser.parse_args()
@@ -715,10 +716,155 @@ def run_prefill(args: argparse.Namespace) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_sweep(args: argparse.Namespace) -> None:
+    """Sequence-sharded single-layer stress (BASELINE config 5): one sequence of 1M tokens,
+    32/8 heads, 16384 planted clusters, budget 8192, K/V rows split across the GPUs."""
+
+    import torch
+    import torch.distributed as dist
+
+    from community_kv_b200 import distributed as ckv_dist
+    from community_kv_b200.config import CommunityKVConfig
+    from community_kv_b200.sequence_shard import SequenceShardedLayer, decode_emulated
+    from community_kv_b200.workload import build_planted_layer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    clusters, budget, sinks = 16384, 8192, NUM_SINK
+    steps_total = args.warmup + args.steps + 2
+    converted, key, value = build_planted_layer(
+        seq_len=args.sweep_context, clusters=clusters, kv_heads=KV_HEADS, group_size=QUERY_HEADS // KV_HEADS,
+        num_sink=sinks, max_decode_tokens=steps_total + 4, device=device, seed=args.seed,
+    )
+    total_rows = key.shape[1]
+    begin, end = ckv_dist.sequence_shard(total_rows, world, rank)
+    config = CommunityKVConfig(token_budget=budget, num_sink=sinks, lam=0.5, aggregation="query_group")
+    layer = SequenceShardedLayer(
+        converted=converted, key_shard=key[:, begin:end].contiguous(), value_shard=value[:, begin:end].contiguous(),
+        row_begin=begin, total_rows=total_rows, config=config, splits=args.splits or None,
+    )
+    del key, value
+    torch.cuda.empty_cache()
+    generator = torch.Generator(device=device).manual_seed(args.seed + 99)  # same on every rank
+    queries = torch.randn((steps_total, QUERY_HEADS, HEAD_DIM), generator=generator, device=device).to(torch.bfloat16)
+    new_keys = (torch.randn((steps_total, KV_HEADS, HEAD_DIM), generator=generator, device=device) * SCALE).to(torch.bfloat16)
+
+    q_cur = torch.zeros_like(queries[0])
+    k_cur = torch.zeros_like(new_keys[0])
+    stream = torch.cuda.Stream(device)
+
+    def enqueue() -> "torch.Tensor":
+        if world > 1:
+            return layer.decode(q_cur, k_cur, SCALE)
+        return decode_emulated([layer], q_cur, k_cur, SCALE)
+
+    graph = None
+
+    def step(index: int) -> None:
+        with torch.cuda.stream(stream):
+            q_cur.copy_(queries[index])
+            k_cur.copy_(new_keys[index])
+            if graph is not None:
+                graph.replay()
+            else:
+                enqueue()
+
+    def barrier() -> None:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(device.index or 0) if rank == 0 else None
+    for index in range(args.warmup):
+        step(index)
+    barrier()
+    # the whole step (kernels, the small combining tensor ops, the collectives) as one CUDA graph
+    use_graph = True
+    try:
+        candidate = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(candidate, stream=stream):
+            enqueue()
+        graph = candidate
+    except Exception as error:  # pragma: no cover - depends on capture support
+        use_graph = False
+        if rank == 0:
+            print(f"[bench] graph capture unavailable ({type(error).__name__}: {error}); direct launches", file=sys.stderr)
+    barrier()
+    if sampler:
+        sampler.start()
+    first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        first.record()
+    for index in range(args.warmup, args.warmup + args.steps):
+        step(index)
+    with torch.cuda.stream(stream):
+        last.record()
+    barrier()
+    elapsed = torch.tensor([first.elapsed_time(last)], device=device)
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    ms_per_step = float(elapsed) / args.steps
+    clocks = sampler.stop() if sampler else {}
+    layer.converted.mutable  # keep alive
+    if int(layer.workspace.update.overflow.max()) != 0:
+        raise RuntimeError("overflow during the sweep")
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_path.read_text())["hbm_gbs"]) if peaks_path.exists() else 6650.0
+    centroid_bytes = int(converted.mutable.community_counts.sum()) * HEAD_DIM
+    kv_bytes = KV_HEADS * 2 * budget * HEAD_DIM * 2
+    bytes_per_gpu = centroid_bytes + kv_bytes // world  # centroids are replicated, selected rows are split
+    if rank != 0:
+        finish(world, dist)
+        return
+    line = {
+        "metric": "sequence-sharded sparse decode, microseconds per step (1 sequence, one layer, ctx %d, budget %d)"
+                  % (args.sweep_context, budget),
+        "value": ms_per_step * 1e3,
+        "unit": "us",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_per_step,
+        "higher_is_better": False,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {
+            "workload": f"sequence-sharded single-layer decode: batch 1, 32 Q / 8 KV heads, ctx {args.sweep_context}, "
+                        f"{clusters} planted clusters per head, budget {budget}, rows split x{world}",
+            "exchange": "NCCL all-gather of (max, sum, acc) triples and top-8 candidates" if world > 1 else "none",
+            "l2": "inputs larger than L2 (each step gathers rows scattered over the whole KV cache)",
+        },
+        "roofline": {
+            "kernel": "score_kernel + select_kernel + attention_kernel + merge_update_kernel (one sharded layer step)",
+            "bound": "hbm",
+            "achieved": bytes_per_gpu / (ms_per_step * 1e-3) / 1e9,
+            "peak": peak,
+            "unit": "GB/s",
+            "frac": bytes_per_gpu / (ms_per_step * 1e-3) / 1e9 / peak,
+            "traffic": None,
+            "algorithmic_bytes_per_launch": bytes_per_gpu,
+        },
+        "gpu_launches": args.steps * 6,
+        "cuda_graph": use_graph,
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    finish(world, dist)
+
+
 def main() -> None:
     args = parse_args()
     if args.workload == "prefill" and args.impl != "reference":
         run_prefill(args)
+        return
+    if args.workload == "sweep" and args.impl != "reference":
+        run_sweep(args)
         return
     if args.impl == "reference":
         run_reference(args)

@@ -130,9 +130,10 @@ def merge_topk(packed: torch.Tensor, k: int = 8) -> torch.Tensor:
     ranks, heads, width = packed.shape
     flat = packed.permute(1, 0, 2).reshape(heads, ranks * width)
     # order as unsigned: flip the sign bit, sort signed, flip back
-    flipped = flat ^ torch.tensor(-(2**63), dtype=torch.int64, device=packed.device)
+    # (a Python scalar operand, not a tensor built on the host: the step stays capturable)
+    flipped = torch.bitwise_xor(flat, -(2**63))
     top = torch.sort(flipped, dim=1, descending=True).values[:, :k]
-    return top ^ torch.tensor(-(2**63), dtype=torch.int64, device=packed.device)
+    return torch.bitwise_xor(top, -(2**63))
 
 
 __all__ = [

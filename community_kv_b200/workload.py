@@ -172,4 +172,74 @@ def build_decode_workload(
     )
 
 
-__all__ = ["DecodeWorkload", "build_decode_workload"]
+def build_planted_layer(
+    *,
+    seq_len: int,
+    clusters: int,
+    kv_heads: int,
+    group_size: int,
+    num_sink: int,
+    max_decode_tokens: int,
+    device: torch.device,
+    seed: int = 0,
+    noise: float = 0.3,
+):
+    """One single-sequence layer with planted key clusters, built on ``device``.
+
+    Keys are cluster centres ~N(0, 1) plus ``noise``-scaled Gaussian noise, times
+    ``1/sqrt(128)``; the community of a token is its cluster (per KV head), sinks are
+    isolated.  Returns ``(converted state, key [Hkv, rows, 128], value)`` with
+    ``rows = seq_len + max_decode_tokens + 1``.  Every rank of a sequence-sharded
+    run builds the same layer from the same seed and keeps its slice of the rows.
+    """
+
+    rows = seq_len + max_decode_tokens + 1
+    key = torch.empty((kv_heads, rows, HEAD_DIM), dtype=torch.bfloat16, device=device)
+    value = torch.empty_like(key)
+    labels = torch.zeros((kv_heads, seq_len), dtype=torch.int32, device=device)
+    for head in range(kv_heads):
+        generator = _unit_generator(seed, 0, 0, head, device)
+        centres = torch.randn((clusters, HEAD_DIM), generator=generator, device=device)
+        cluster = torch.randint(0, clusters, (rows,), generator=generator, device=device)
+        cluster[:clusters] = torch.randperm(clusters, generator=generator, device=device)  # none empty
+        for begin in range(0, rows, 1 << 18):  # bounded temporaries
+            end = min(rows, begin + (1 << 18))
+            chunk = centres[cluster[begin:end]]
+            chunk += noise * torch.randn(chunk.shape, generator=generator, device=device)
+            key[head, begin:end] = (chunk * HEAD_DIM**-0.5).to(torch.bfloat16)
+            value[head, begin:end] = (
+                torch.randn(chunk.shape, generator=generator, device=device) * HEAD_DIM**-0.5
+            ).to(torch.bfloat16)
+        # sinks carry labels of their own behind the planted ones
+        labels[head, num_sink:] = cluster[num_sink:seq_len].to(torch.int32)
+        labels[head, :num_sink] = clusters + torch.arange(num_sink, dtype=torch.int32, device=device)
+    assembled = assemble_layer(
+        labels,
+        key[:, :seq_len],
+        aggregation=GraphAggregation.QUERY_GROUP,
+        query_heads=kv_heads * group_size,
+        num_sink=num_sink,
+        max_decode_tokens=max_decode_tokens,
+    )
+    converted = convert_prefill_tensors(
+        member_offsets=assembled.member_offsets,
+        member_positions=assembled.member_positions,
+        num_communities=assembled.num_communities,
+        centroids=assembled.centroids,
+        community_sizes=assembled.community_sizes,
+        community_weight=assembled.community_weight,
+        total_weight=assembled.total_weight,
+        token_communities=assembled.token_communities,
+        retrieval_to_graph=assembled.retrieval_to_graph,
+        retrieval_to_kv=assembled.retrieval_to_kv,
+        prefill_seq_len=seq_len,
+        max_decode_tokens=max_decode_tokens,
+        group_size=group_size,
+        aggregation=GraphAggregation.QUERY_GROUP,
+        query_heads=kv_heads * group_size,
+        kv_heads=kv_heads,
+    )
+    return converted, key, value
+
+
+__all__ = ["DecodeWorkload", "build_decode_workload", "build_planted_layer"]
