@@ -494,15 +494,34 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         const float gate = (row_floor >> 17) == 0u
                                ? -3.0e38f
                                : (static_cast<float>(row_floor >> 17) - 0.75f) * (1.0f / 256.0f) - 48.0f;
-        if (half_max >= gate) {
+        // Class by class (16 of this thread's 64 columns each): the columns that reach
+        // the gate as a bit mask, then insertion in rounds - every lane with a pending
+        // column inserts its next one per round - so that the divergent insertion code
+        // runs as often as the busiest lane needs, not once per column with a taker.
+        if (__any_sync(0xffffffffu, half_max >= gate)) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) {
-            if (s[c] >= gate) {
-              const uint32_t candidate = (quantised_key(s[c]) << 17) |
-                                         (static_cast<uint32_t>(key0 + col0 + c) & 0x1ffffu);
-              uint32_t(&queue)[kLocalK] = q32[(c & 7) >> 1];
-              if (candidate > queue[kLocalK - 1]) {
-                queue_insert<kLocalK>(queue, candidate);
+          for (int cls = 0; cls < 4; ++cls) {
+            uint32_t takers = 0u;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int c = (i >> 1) * 8 + cls * 2 + (i & 1);
+              takers |= (s[c] >= gate ? 1u : 0u) << i;
+            }
+            while (__any_sync(0xffffffffu, takers != 0u)) {
+              if (takers != 0u) {
+                const int i = __ffs(takers) - 1;
+                takers &= takers - 1;
+                float v = s[cls * 2];
+#pragma unroll
+                for (int k = 1; k < 16; ++k) {
+                  v = i == k ? s[(k >> 1) * 8 + cls * 2 + (k & 1)] : v;
+                }
+                const int c = (i >> 1) * 8 + cls * 2 + (i & 1);
+                const uint32_t candidate = (quantised_key(v) << 17) |
+                                           (static_cast<uint32_t>(key0 + col0 + c) & 0x1ffffu);
+                if (candidate > q32[cls][kLocalK - 1]) {
+                  queue_insert<kLocalK>(q32[cls], candidate);
+                }
               }
             }
           }
