@@ -21,7 +21,9 @@ import numpy as np
 import torch
 
 HERE = Path(__file__).resolve().parent
-REFERENCE = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py <path to a checkout of the reference project>")
+REFERENCE = Path(sys.argv[1])
 sys.path.insert(0, str(REFERENCE))
 
 from community_kv.graph.partition import (  # noqa: E402
