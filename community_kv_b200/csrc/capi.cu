@@ -160,7 +160,10 @@ int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream) {
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (ckv::fused_layer_supported(*args)) {
     // one cluster launch per layer: scoring, selection, attention, merge and update
-    return ckv::launched(ckv::launch_fused_layer(*args, stream));
+    if (ckv::launch_fused_layer(*args, stream) == cudaSuccess) return CKV_OK;
+    // the cluster shape could not be scheduled on this device: clear the error and
+    // run the four kernels instead (same results)
+    (void)cudaGetLastError();
   }
   status = ckv::launched(ckv::launch_score(*args, stream));
   if (status != CKV_OK) return status;
