@@ -47,6 +47,20 @@ __global__ void __launch_bounds__(kFusedThreads, 3) decode_cluster_kernel(const 
   const int flat = blockIdx.y;
   const int split = blockIdx.x;  // == rank in the cluster
   pdl_release_dependents();
+  // This CTA's share of the centroid table does not come from the kernel before it in
+  // the stream (that one produces the query): ask for it in L2 while that kernel is
+  // still finishing, before the wait below.
+  {
+    const int limit = score_limit(a, flat);
+    const int groups = (limit + 15) / 16;
+    const int first_row = 16 * static_cast<int>(static_cast<int64_t>(split) * groups / a.splits);
+    const int last_row = min(limit, 16 * static_cast<int>(static_cast<int64_t>(split + 1) * groups / a.splits));
+    const uint8_t* rows = reinterpret_cast<const uint8_t*>(a.centroids) +
+                          (static_cast<int64_t>(flat) * a.community_capacity + first_row) * kHeadDim;
+    for (int row = threadIdx.x; row < last_row - first_row; row += kFusedThreads) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(rows + static_cast<int64_t>(row) * kHeadDim));
+    }
+  }
   pdl_wait_for_predecessor();  // the query and last step's state come from upstream
 
   // ---- 1. centroid scores: this CTA's share of the unit's 16-row groups; the keys
