@@ -374,6 +374,103 @@ __device__ __forceinline__ void find_threshold_bin(const int* hist_mass, const i
   }
 }
 
+// Tail of a selection, shared by the one-CTA and the cluster variant: the first
+// descriptor of every 64-token tile (when `report_tiles`), then logical tokens
+// [token_begin, token_end) -> cache rows, four per thread and pass so that the
+// dependent global reads of each overlap.  `search_ends` / `search_comm` hold the
+// `descriptors` descriptors (shared or global memory).
+template <int kThreads>
+__device__ __forceinline__ void resolve_tokens(const ckv_layer_args& a, int flat, const Unit& u,
+                                               const int32_t* search_ends, const int32_t* search_comm,
+                                               int descriptors, bool report_tiles, int token_begin,
+                                               int token_end) {
+  const int tid = threadIdx.x;
+  const int capacity = a.community_capacity;
+  const int tile_count = a.token_budget / kTile;
+  // First descriptor of every 64-token tile.
+  for (int tile = tid; report_tiles && tile < tile_count; tile += kThreads) {
+    const int offset = max(tile * kTile - a.num_sink, 0);
+    int low = 0;
+    int high = descriptors;
+    while (low < high) {
+      const int middle = (low + high) >> 1;
+      if (search_ends[middle] <= offset) {
+        low = middle + 1;
+      } else {
+        high = middle;
+      }
+    }
+    a.tile_descriptors[static_cast<int64_t>(flat) * tile_count + tile] =
+        max(0, min(low, descriptors - 1));
+  }
+
+  // This CTA's logical tokens -> cache rows (four per thread and pass, so that the
+  // dependent global reads of each overlap).
+  int32_t* positions = a.positions + static_cast<int64_t>(flat) * a.token_budget;
+  const int64_t graph_slot = static_cast<int64_t>(u.batch) * a.graphs + u.graph;
+  const int32_t* delta_sizes = a.delta_sizes + graph_slot * capacity;
+  const int32_t* offsets = a.member_offsets + graph_slot * (capacity + 1);
+  const int32_t* members = a.member_positions + graph_slot * a.member_capacity;
+  for (int base = token_begin; base < token_end; base += 4 * kThreads) {
+    int logical[4], community[4], member[4], direct[4];
+    bool lookup[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      logical[i] = base + i * kThreads + tid;
+      lookup[i] = false;
+      direct[i] = -1;
+      community[i] = 0;
+      member[i] = 0;
+      if (logical[i] >= token_end) {
+        continue;
+      }
+      if (logical[i] < a.num_sink) {
+        direct[i] = a.sink_positions[logical[i]];
+      } else if (logical[i] == a.token_budget - 1) {
+        direct[i] = a.current_position[graph_slot];
+      } else {
+        const int offset = logical[i] - a.num_sink;
+        int low = 0;
+        int high = descriptors;
+        while (low < high) {
+          const int middle = (low + high) >> 1;
+          if (search_ends[middle] <= offset) {
+            low = middle + 1;
+          } else {
+            high = middle;
+          }
+        }
+        if (low < descriptors) {
+          lookup[i] = true;
+          community[i] = search_comm[low];
+          member[i] = offset - (low > 0 ? search_ends[low - 1] : 0);
+        }
+      }
+    }
+    int delta_count[4], start[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      delta_count[i] = lookup[i] ? delta_sizes[community[i]] : 0;
+      start[i] = lookup[i] ? offsets[community[i]] : 0;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (lookup[i] && member[i] >= delta_count[i]) {
+        direct[i] = members[start[i] + member[i] - delta_count[i]];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (lookup[i] && member[i] < delta_count[i]) {
+        direct[i] = delta_member_position(a, graph_slot, community[i], member[i]);
+      }
+      if (logical[i] < token_end) {
+        positions[logical[i]] = direct[i];
+      }
+    }
+  }
+}
+
 // Shared memory of one selection.
 struct SelectSmem {
   uint16_t stash_key[kStash];
@@ -399,7 +496,6 @@ __device__ __forceinline__ void select_unit(const ckv_layer_args& a, int flat, S
   const int tid = threadIdx.x;
   const int capacity = a.community_capacity;
   const int active = max(0, min(capacity, a.community_counts[flat]));
-  const int tile_count = a.token_budget / kTile;
   const int budget = a.token_budget - a.num_sink - 1;
   const int limit = a.max_communities;
   const uint16_t* score_bits =
@@ -564,89 +660,8 @@ __device__ __forceinline__ void select_unit(const ckv_layer_args& a, int flat, S
   const int32_t* search_ends = in_smem ? sm.desc_end : out_ends;
   const int32_t* search_comm = in_smem ? sm.desc_comm : out_comm;
 
-  // First descriptor of every 64-token tile.
-  for (int tile = tid; write_outputs && tile < tile_count; tile += kThreads) {
-    const int offset = max(tile * kTile - a.num_sink, 0);
-    int low = 0;
-    int high = descriptors;
-    while (low < high) {
-      const int middle = (low + high) >> 1;
-      if (search_ends[middle] <= offset) {
-        low = middle + 1;
-      } else {
-        high = middle;
-      }
-    }
-    a.tile_descriptors[static_cast<int64_t>(flat) * tile_count + tile] =
-        max(0, min(low, descriptors - 1));
-  }
-
-  // Resolve every logical token of the budget to its cache row.
-  // Two logical tokens per thread and pass, so that the two dependent global
-  // reads of each (community tables, then the member list) overlap.
-  int32_t* positions = a.positions + static_cast<int64_t>(flat) * a.token_budget;
-  const int64_t graph_slot = static_cast<int64_t>(u.batch) * a.graphs + u.graph;
-  const int32_t* delta_sizes = a.delta_sizes + graph_slot * capacity;
-  const int32_t* offsets = a.member_offsets + graph_slot * (capacity + 1);
-  const int32_t* members = a.member_positions + graph_slot * a.member_capacity;
-  for (int base = token_begin; base < token_end; base += 2 * kThreads) {
-    int logical[2], community[2], member[2], direct[2];
-    bool lookup[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      logical[i] = base + i * kThreads + tid;
-      lookup[i] = false;
-      direct[i] = -1;
-      community[i] = 0;
-      member[i] = 0;
-      if (logical[i] >= token_end) {
-        continue;
-      }
-      if (logical[i] < a.num_sink) {
-        direct[i] = a.sink_positions[logical[i]];
-      } else if (logical[i] == a.token_budget - 1) {
-        direct[i] = a.current_position[graph_slot];
-      } else {
-        const int offset = logical[i] - a.num_sink;
-        int low = 0;
-        int high = descriptors;
-        while (low < high) {
-          const int middle = (low + high) >> 1;
-          if (search_ends[middle] <= offset) {
-            low = middle + 1;
-          } else {
-            high = middle;
-          }
-        }
-        if (low < descriptors) {
-          lookup[i] = true;
-          community[i] = search_comm[low];
-          member[i] = offset - (low > 0 ? search_ends[low - 1] : 0);
-        }
-      }
-    }
-    int delta_count[2], start[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      delta_count[i] = lookup[i] ? delta_sizes[community[i]] : 0;
-      start[i] = lookup[i] ? offsets[community[i]] : 0;
-    }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      if (lookup[i] && member[i] >= delta_count[i]) {
-        direct[i] = members[start[i] + member[i] - delta_count[i]];
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      if (lookup[i] && member[i] < delta_count[i]) {
-        direct[i] = delta_member_position(a, graph_slot, community[i], member[i]);
-      }
-      if (logical[i] < token_end) {
-        positions[logical[i]] = direct[i];
-      }
-    }
-  }
+  resolve_tokens<kThreads>(a, flat, u, search_ends, search_comm, descriptors, write_outputs, token_begin,
+                           token_end);
 }
 
 
@@ -723,7 +738,6 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
   const int tid = threadIdx.x;
   const int capacity = a.community_capacity;
   const int active = max(0, min(capacity, a.community_counts[flat]));
-  const int tile_count = a.token_budget / kTile;
   const int budget = a.token_budget - a.num_sink - 1;
   const int limit = a.max_communities;
   // the last slice also takes any active rows beyond the scored cover
@@ -941,88 +955,8 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
   const int32_t* search_ends = sm.desc_end;
   const int32_t* search_comm = sm.desc_comm;
 
-  // First descriptor of every 64-token tile (one CTA reports them).
-  for (int tile = tid; rank == 0 && tile < tile_count; tile += kThreads) {
-    const int offset = max(tile * kTile - a.num_sink, 0);
-    int low = 0;
-    int high = descriptors;
-    while (low < high) {
-      const int middle = (low + high) >> 1;
-      if (search_ends[middle] <= offset) {
-        low = middle + 1;
-      } else {
-        high = middle;
-      }
-    }
-    a.tile_descriptors[static_cast<int64_t>(flat) * tile_count + tile] =
-        max(0, min(low, descriptors - 1));
-  }
-
-  // This CTA's logical tokens -> cache rows (four per thread and pass, so that the
-  // dependent global reads of each overlap).
-  int32_t* positions = a.positions + static_cast<int64_t>(flat) * a.token_budget;
-  const int64_t graph_slot = static_cast<int64_t>(u.batch) * a.graphs + u.graph;
-  const int32_t* delta_sizes = a.delta_sizes + graph_slot * capacity;
-  const int32_t* offsets = a.member_offsets + graph_slot * (capacity + 1);
-  const int32_t* members = a.member_positions + graph_slot * a.member_capacity;
-  for (int base = token_begin; base < token_end; base += 4 * kThreads) {
-    int logical[4], community[4], member[4], direct[4];
-    bool lookup[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      logical[i] = base + i * kThreads + tid;
-      lookup[i] = false;
-      direct[i] = -1;
-      community[i] = 0;
-      member[i] = 0;
-      if (logical[i] >= token_end) {
-        continue;
-      }
-      if (logical[i] < a.num_sink) {
-        direct[i] = a.sink_positions[logical[i]];
-      } else if (logical[i] == a.token_budget - 1) {
-        direct[i] = a.current_position[graph_slot];
-      } else {
-        const int offset = logical[i] - a.num_sink;
-        int low = 0;
-        int high = descriptors;
-        while (low < high) {
-          const int middle = (low + high) >> 1;
-          if (search_ends[middle] <= offset) {
-            low = middle + 1;
-          } else {
-            high = middle;
-          }
-        }
-        if (low < descriptors) {
-          lookup[i] = true;
-          community[i] = search_comm[low];
-          member[i] = offset - (low > 0 ? search_ends[low - 1] : 0);
-        }
-      }
-    }
-    int delta_count[4], start[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      delta_count[i] = lookup[i] ? delta_sizes[community[i]] : 0;
-      start[i] = lookup[i] ? offsets[community[i]] : 0;
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (lookup[i] && member[i] >= delta_count[i]) {
-        direct[i] = members[start[i] + member[i] - delta_count[i]];
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (lookup[i] && member[i] < delta_count[i]) {
-        direct[i] = delta_member_position(a, graph_slot, community[i], member[i]);
-      }
-      if (logical[i] < token_end) {
-        positions[logical[i]] = direct[i];
-      }
-    }
-  }
+  resolve_tokens<kThreads>(a, flat, u, search_ends, search_comm, descriptors, rank == 0, token_begin,
+                           token_end);
 }
 
 }  // namespace ckv
