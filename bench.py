@@ -278,7 +278,7 @@ def run_b200(args: argparse.Namespace) -> None:
     import torch
     import torch.distributed as dist
 
-    from community_kv_b200 import native
+    from community_kv_b200 import native, ops
     from community_kv_b200.workload import build_decode_workload
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -520,8 +520,7 @@ def run_b200(args: argparse.Namespace) -> None:
         for step in range(e2e_steps):
             q_cur.copy_(pinned_q[step], non_blocking=True)
             new_kv.copy_(pinned_kv[step], non_blocking=True)
-            work.key[:, :, :, cursor + step].copy_(new_kv[0])
-            work.value[:, :, :, cursor + step].copy_(new_kv[1])
+            ops.append_kv(work.key, work.value, new_kv[0], new_kv[1], cursor + step)
             run_step()
             pinned_out.view(result.shape).copy_(result, non_blocking=True)
             stream.synchronize()  # the caller reads the step's output before the next token

@@ -65,6 +65,35 @@ __global__ void __launch_bounds__(kMergeThreads) sync_shared_kernel(const ckv_la
   }
 }
 
+// One warp per unit: lanes 0-15 copy the 256-byte key row, lanes 16-31 the value row.
+__global__ void __launch_bounds__(128) append_kv_kernel(uint4* key_cache, uint4* value_cache,
+                                                        const uint4* new_key, const uint4* new_value,
+                                                        int64_t units, int64_t unit_stride_vec,
+                                                        const int32_t* row_index, int64_t row) {
+  const int64_t unit = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (unit >= units) {
+    return;
+  }
+  const int lane = threadIdx.x & 31;
+  const int64_t target = row_index != nullptr ? row_index[unit] : row;
+  if (target < 0) {
+    return;
+  }
+  const int piece = lane & 15;
+  uint4* cache = lane < 16 ? key_cache : value_cache;
+  const uint4* fresh = lane < 16 ? new_key : new_value;
+  cache[unit * unit_stride_vec + target * (kHeadDim * 2 / 16) + piece] = fresh[unit * (kHeadDim * 2 / 16) + piece];
+}
+
+cudaError_t launch_append_kv(void* key_cache, void* value_cache, const void* new_key, const void* new_value,
+                             int64_t units, int64_t unit_stride, const int32_t* row_index, int64_t row,
+                             cudaStream_t stream) {
+  append_kv_kernel<<<static_cast<unsigned>((units + 3) / 4), 128, 0, stream>>>(
+      static_cast<uint4*>(key_cache), static_cast<uint4*>(value_cache), static_cast<const uint4*>(new_key),
+      static_cast<const uint4*>(new_value), units, unit_stride / 8, row_index, row);
+  return cudaGetLastError();
+}
+
 // One thread polls this GPU's counter a bounded number of times.
 __global__ void wait_peers_kernel(uint32_t* flag, uint32_t expected, uint32_t* status) {
   constexpr uint32_t kPolls = 1u << 22;  // about two seconds with the back-off below

@@ -576,7 +576,49 @@ def decode_layer(
     )
 
 
+def append_kv(
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    new_key: torch.Tensor,
+    new_value: torch.Tensor,
+    row: int | torch.Tensor,
+) -> None:
+    """``cache[..., row, :] = new[..., :]`` for both caches in one small launch.
+
+    The caches are bf16 ``[..., rows, 128]`` (contiguous), the new rows bf16 ``[..., 128]``
+    with the same leading shape; ``row`` is one index for all of them or an int32 tensor
+    with one index per leading entry (negative: skip).
+    """
+
+    if key_cache.shape != value_cache.shape or new_key.shape != new_value.shape:
+        raise ValueError("key and value must have the same shapes")
+    if key_cache.shape[-1] != HEAD_DIM or tuple(key_cache.shape[:-2]) != tuple(new_key.shape[:-1]):
+        raise ValueError("caches must be [..., rows, 128] and the new rows [..., 128]")
+    if not (key_cache.is_contiguous() and value_cache.is_contiguous()):
+        raise ValueError("the caches must be contiguous")
+    if key_cache.dtype != torch.bfloat16 or new_key.dtype != torch.bfloat16:
+        raise TypeError("caches and new rows must use BF16")
+    device = _require_cuda(key_cache, value_cache, new_key, new_value)
+    units = new_key.numel() // HEAD_DIM
+    index = None
+    if isinstance(row, torch.Tensor):
+        if row.dtype != torch.int32 or row.numel() != units:
+            raise ValueError("row must be int32 with one entry per cache row to write")
+        index = row.contiguous()
+    elif not 0 <= int(row) < key_cache.shape[-2]:
+        raise ValueError("row is outside the cache")
+    keep = (new_key.contiguous(), new_value.contiguous())
+    status = native.library().ckv_append_kv(
+        key_cache.data_ptr(), value_cache.data_ptr(), keep[0].data_ptr(), keep[1].data_ptr(), units,
+        key_cache.shape[-2] * HEAD_DIM, native.pointer(index), 0 if index is not None else int(row),
+        native.current_stream(device),
+    )
+    if status:
+        raise native.NativeError(native.library().ckv_status_string(status).decode())
+
+
 __all__ = [
+    "append_kv",
     "build_layer_args",
     "decode_layer",
     "score_and_select",

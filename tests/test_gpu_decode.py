@@ -260,3 +260,28 @@ def test_shape_errors_are_reported_before_launch():
     with pytest.raises(RuntimeError, match="not prepared"):
         runtime.decode(layer_idx=3, query=torch.zeros((1, 4, 1, 128), device=device, dtype=torch.bfloat16),
                        key=layer.key.to(device)[None], value=layer.value.to(device)[None], softmax_scale=SCALE)
+
+
+def test_append_kv_rows():
+    """ckv_append_kv: one row per (sequence, head) into both caches, scalar and per-unit index."""
+
+    device = torch.device("cuda", 0)
+    torch.manual_seed(5)
+    key = torch.randn((3, 2, 40, 128), device=device).to(torch.bfloat16)
+    value = torch.randn_like(key)
+    new_key = torch.randn((3, 2, 128), device=device).to(torch.bfloat16)
+    new_value = torch.randn_like(new_key)
+    want_key, want_value = key.clone(), value.clone()
+    want_key[:, :, 17] = new_key
+    want_value[:, :, 17] = new_value
+    ops.append_kv(key, value, new_key, new_value, 17)
+    assert torch.equal(key, want_key) and torch.equal(value, want_value)
+    rows = torch.tensor([0, 39, -1, 5, 5, 12], dtype=torch.int32, device=device)
+    for unit, row in enumerate(rows.tolist()):
+        if row >= 0:
+            want_key.view(6, 40, 128)[unit, row] = new_key.view(6, 128)[unit]
+            want_value.view(6, 40, 128)[unit, row] = new_value.view(6, 128)[unit]
+    ops.append_kv(key, value, new_key, new_value, rows)
+    assert torch.equal(key, want_key) and torch.equal(value, want_value)
+    with pytest.raises(ValueError):
+        ops.append_kv(key, value, new_key, new_value, 40)
