@@ -125,6 +125,20 @@ __device__ __forceinline__ void tmem_load64(uint32_t taddr, float (&v)[64]) {
   }
 }
 
+__device__ __forceinline__ void tmem_store64(uint32_t taddr, const float (&v)[64]) {
+  uint32_t r[64];
+#pragma unroll
+  for (int i = 0; i < 64; ++i) {
+    r[i] = __float_as_uint(v[i]);
+  }
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x64.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63,%64};\n" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(r[32]), "r"(r[33]), "r"(r[34]), "r"(r[35]), "r"(r[36]), "r"(r[37]), "r"(r[38]), "r"(r[39]), "r"(r[40]), "r"(r[41]), "r"(r[42]), "r"(r[43]), "r"(r[44]), "r"(r[45]), "r"(r[46]), "r"(r[47]), "r"(r[48]), "r"(r[49]), "r"(r[50]), "r"(r[51]), "r"(r[52]), "r"(r[53]), "r"(r[54]), "r"(r[55]), "r"(r[56]), "r"(r[57]), "r"(r[58]), "r"(r[59]), "r"(r[60]), "r"(r[61]), "r"(r[62]), "r"(r[63])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -378,14 +392,9 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     }
   }
 
-  float out[64];
-#pragma unroll
-  for (int d = 0; d < 64; ++d) {
-    out[d] = 0.f;
-  }
+  float out[64];  // filled from tensor memory after the last block
   float run_max = -INFINITY;  // of the raw (unscaled) scores, whole row
   float run_sum = 0.f;        // this thread's column half only
-  float pending_corr = 1.f;   // rescale that goes with the P.V result still in flight
   const float scale_log2 = a.softmax_scale * kLog2e;
   uint32_t q32[4][kLocalK];
   uint64_t q64[kExactKeep];
@@ -407,18 +416,14 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   }
   const int limit = row_live ? min(row_pos, length - 1) : -1;  // last visible key
 
-  auto fold_output = [&](int block) {
-    // O' of `block` is complete: add it to the running output row
+  // O accumulates in tensor memory over all key blocks (P.V with accumulate); the
+  // registers see it twice: when a row's running maximum moves by more than 2^8 (the
+  // row is then rescaled in place) and at the very end.
+  auto wait_output = [&](int block) {
     if (!mbar_wait(bar_o, block & 1)) {
       failed = true;
     }
     tc_fence_after();
-    float o[64];
-    tmem_load64(lane_base + 256u + col0, o);
-#pragma unroll
-    for (int c = 0; c < 64; ++c) {
-      out[c] = out[c] * pending_corr + o[c];
-    }
   };
 
   for (int block = 0; block < blocks; ++block) {
@@ -609,11 +614,18 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       }
     }
 
+    // The running maximum is only moved when the new one lies more than 2^8 above it
+    // (probabilities up to 256 are harmless in bf16 / fp32); moving it means rescaling
+    // the output row that sits in tensor memory.
     const float new_max = fmaxf(run_max, tile_max);
-    const float safe_max = new_max == -INFINITY ? 0.f : new_max;
-    const float corr = exp2f((run_max - safe_max) * scale_log2);
-    run_max = new_max;
-    run_sum *= corr;
+    const bool move = new_max > run_max && (new_max - run_max) * scale_log2 > 8.0f;
+    float corr = 1.f;
+    if (move) {
+      corr = run_max == -INFINITY ? 0.f : exp2f((run_max - new_max) * scale_log2);
+      run_max = new_max;
+      run_sum *= corr;
+    }
+    const float safe_max = run_max == -INFINITY ? 0.f : run_max;
 
     // ---- probabilities (bf16 pairs; masked keys are -inf and come out as 0) ----
     uint32_t packed[32];
@@ -627,9 +639,17 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     // P.V of block-1 ran under the work above; fold it in, which also frees the P tile
     // and that block's V buffer
     if (block > 0) {
-      fold_output(block - 1);
+      wait_output(block - 1);
+      if (__any_sync(0xffffffffu, move)) {
+        float o[64];
+        tmem_load64(lane_base + 256u + col0, o);
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          o[c] *= corr;
+        }
+        tmem_store64(lane_base + 256u + col0, o);
+      }
     }
-    pending_corr = corr;  // goes with this block's P.V result
     if (tid == 0 && block + 1 < blocks) {
       tma_load_tile(smem_u32(s_v) + (buffer ^ 1) * kTileBytes, &map_v, bar_v + 8 * (buffer ^ 1),
                     key0 + kPfKeys, kv_head, batch);
@@ -655,13 +675,14 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         const uint64_t desc_p = smem_descriptor(smem_u32(s_p) + ks * 4096, 2048, 128);
         const uint64_t desc_v =
             smem_descriptor(smem_u32(s_v) + buffer * kTileBytes + ks * 256, 128, 2048);
-        umma(tmem + 256u, desc_p, desc_v, idesc_pv, ks > 0 ? 1u : 0u);
+        umma(tmem + 256u, desc_p, desc_v, idesc_pv, (ks > 0 || block > 0) ? 1u : 0u);
       }
       umma_commit(bar_o);
     }
   }
   if (!failed) {
-    fold_output(blocks - 1);
+    wait_output(blocks - 1);
+    tmem_load64(lane_base + 256u + col0, out);
   }
   tc_fence_before();
   const int any_failed = __syncthreads_or(failed ? 1 : 0);
