@@ -115,6 +115,15 @@ def test_zipf_communities_full_context_unit():
     _run_sequence(layer, config, steps=2, seed=500)
 
 
+def test_config3_layer_with_online_assignment():
+    """BASELINE config 3 shape for one layer: ctx 32768, 512 Zipf(1.1) communities per KV head,
+    budget 2048, every decoded token assigned online (eight steps)."""
+
+    layer = make_layer(seed=7, seq_len=32768, communities=512, max_decode_tokens=12, zipf_exponent=1.1)
+    config = CommunityKVConfig(token_budget=2048, num_sink=10, lam=0.5, aggregation="query_group")
+    _run_sequence(layer, config, steps=8, seed=700)
+
+
 def test_batched_sequences_match_per_sequence_oracle():
     device = torch.device("cuda", 0)
     config = CommunityKVConfig(token_budget=512, num_sink=10, lam=0.5, aggregation="query_group")
