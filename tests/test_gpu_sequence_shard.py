@@ -62,3 +62,45 @@ def test_four_shards_match_the_unsharded_layer(aggregation):
             assert torch.equal(shard.workspace.update.assigned_communities.cpu(), want.assigned), where
             assert_state_equal(shard.converted.mutable, twin.state, where)
             assert torch.equal(shard.converted.current_position.cpu(), twin.current), where
+
+
+def test_large_context_shards_agree_with_one_gpu():
+    """BASELINE config 5 shape (scaled to 262144 tokens so that two replicas fit comfortably):
+    16384 planted clusters per head, budget 8192.  Two row shards against the whole cache in one
+    piece: same selection, same neighbours and labels bit for bit, outputs within 2e-2."""
+
+    import copy
+
+    from community_kv_b200.workload import build_planted_layer
+
+    device = torch.device("cuda", 0)
+    steps = 3
+    config = CommunityKVConfig(token_budget=8192, num_sink=10, lam=0.5, aggregation="query_group")
+    converted, key, value = build_planted_layer(
+        seq_len=262144, clusters=16384, kv_heads=8, group_size=4, num_sink=10,
+        max_decode_tokens=steps + 2, device=device, seed=3,
+    )
+    total_rows = key.shape[1]
+    whole = SequenceShardedLayer(converted=copy.deepcopy(converted), key_shard=key, value_shard=value,
+                                 row_begin=0, total_rows=total_rows, config=config)
+    shards = []
+    for rank in range(2):
+        begin, end = ckv_dist.sequence_shard(total_rows, 2, rank)
+        shards.append(SequenceShardedLayer(
+            converted=copy.deepcopy(converted), key_shard=key[:, begin:end].contiguous(),
+            value_shard=value[:, begin:end].contiguous(), row_begin=begin, total_rows=total_rows, config=config))
+    generator = torch.Generator(device=device).manual_seed(11)
+    for step in range(steps):
+        query = torch.randn((32, 128), generator=generator, device=device).to(torch.bfloat16)
+        new_key = (torch.randn((8, 128), generator=generator, device=device) * SCALE).to(torch.bfloat16)
+        one = decode_emulated([whole], query, new_key, SCALE).float().clone()
+        two = decode_emulated(shards, query, new_key, SCALE).float()
+        diff = (one - two).abs()
+        assert float(diff.max()) <= OUTPUT_MAX_ABS and float(diff.mean()) <= OUTPUT_MEAN_ABS, step
+        for shard in shards:
+            assert torch.equal(shard.workspace.selection.positions, whole.workspace.selection.positions), step
+            assert torch.equal(shard.workspace.attention.topk_positions, whole.workspace.attention.topk_positions), step
+            assert torch.equal(shard.workspace.update.assigned_communities, whole.workspace.update.assigned_communities), step
+            assert torch.equal(shard.converted.mutable.centroids.view(torch.uint8),
+                               whole.converted.mutable.centroids.view(torch.uint8)), step
+        assert int(whole.workspace.update.overflow.max()) == 0
