@@ -80,7 +80,10 @@ def test_reference_topk_rule():
     assert exact_rows / total_rows > 0.97, exact_rows / total_rows
 
 
-@pytest.mark.parametrize("length,heads,kv_heads,edges", [(384, 4, 1, 16), (300, 8, 2, 8), (260, 2, 2, 16)])
+@pytest.mark.parametrize(
+    "length,heads,kv_heads,edges",
+    [(384, 4, 1, 16), (300, 8, 2, 8), (260, 2, 2, 16), (320, 4, 2, 16), (272, 8, 1, 16), (700, 8, 2, 16)],
+)
 def test_exact_edges_are_bit_exact(length, heads, kv_heads, edges):
     sinks = 4
     q, k, v = _inputs(3, length, heads, kv_heads)
@@ -121,3 +124,44 @@ def test_batch_and_validation():
         prefill_attention(q.cuda().float(), k.cuda(), v.cuda(), softmax_scale=SCALE)
     with pytest.raises(ValueError):
         prefill_attention(q.cuda()[:, :, :3], k.cuda(), v.cuda(), softmax_scale=SCALE)
+
+
+def test_full_size_properties():
+    """BASELINE config 2 at full size (S = 16384, 32 / 8 heads, 256 planted clusters): sampled rows
+    against fp32 torch arithmetic - attention within tolerance; every edge's score is the group
+    maximum of that key, edges are sorted, and nothing outside the list beats the last edge."""
+
+    device = torch.device("cuda", 0)
+    length, heads, kv_heads, sinks, edges = 16384, 32, 8, 10, 16
+    generator = torch.Generator(device=device).manual_seed(9)
+    centres = torch.randn((kv_heads, 256, 128), generator=generator, device=device)
+    labels = torch.randint(0, 256, (length, kv_heads), generator=generator, device=device)
+    key = centres[torch.arange(kv_heads, device=device), labels] + 0.3 * torch.randn(
+        (length, kv_heads, 128), generator=generator, device=device)
+    key = (key * SCALE).to(torch.bfloat16)[None]
+    value = (torch.randn((1, length, kv_heads, 128), generator=generator, device=device) * SCALE).to(torch.bfloat16)
+    query = torch.randn((1, length, heads, 128), generator=generator, device=device).to(torch.bfloat16)
+    out, lse, edge_idx, edge_score, flags = prefill_attention_edges(
+        query, key, value, softmax_scale=SCALE, num_sink=sinks, edges_per_row=edges)
+    torch.cuda.synchronize()
+    skip = sinks + edges - 1
+    group = heads // kv_heads
+    rows = torch.randint(skip, length, (48,), generator=generator, device=device).tolist() + [skip, length - 1]
+    k32, v32 = key[0].float(), value[0].float()
+    for row in rows:
+        q_row = query[0, row].float()  # [heads, 128]
+        scores = torch.einsum("hd,jhd->hj", q_row.view(kv_heads, group, 128).reshape(heads, 128),
+                              k32[: row + 1].repeat_interleave(group, dim=1)) * SCALE
+        probabilities = torch.softmax(scores, dim=-1)
+        want = torch.einsum("hj,jhd->hd", probabilities, v32[: row + 1].repeat_interleave(group, dim=1))
+        assert float((out[0, row].float() - want).abs().max()) <= 2e-2, row
+        best = scores.view(kv_heads, group, row + 1).amax(dim=1)  # [kv, keys]
+        best[:, :sinks] = float("-inf")
+        got_idx = edge_idx[0, :, row - skip].long()
+        got_score = edge_score[0, :, row - skip]
+        assert bool((got_idx >= sinks).all()) and bool((got_idx <= row).all()), row
+        assert bool((got_score[:, :-1] >= got_score[:, 1:]).all()), row
+        torch.testing.assert_close(got_score, best.gather(1, got_idx), rtol=0, atol=2e-5)
+        rest = best.scatter(1, got_idx, float("-inf"))
+        assert bool((rest.amax(dim=1) <= got_score[:, -1] + 2e-5).all()), row
+    assert int(flags.sum()) <= flags.numel() // 100
