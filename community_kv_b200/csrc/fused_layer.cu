@@ -4,12 +4,13 @@
 // The CTAs of a cluster are co-scheduled, so they can hand work to one another
 // through the hardware cluster barrier instead of through kernel boundaries:
 //
-//   1. every CTA scores a 1/splits share of the unit's centroid rows and writes
-//      the fp16 scores to the workspace;                      -- cluster barrier --
-//   2. every CTA runs the (cheap, deterministic) budgeted selection over all of
-//      the unit's scores, so each one knows the descriptors without any further
-//      exchange; rank 0 reports them to the workspace; each CTA resolves only the
-//      logical tokens of its own attention split to cache rows;
+//   1. every CTA scores a 1/splits share of the unit's centroid rows, writes the
+//      fp16 scores to the workspace and keeps its slice's keys, sizes and weighted
+//      histogram in shared memory;
+//   2. the budgeted selection runs across the cluster (select_cluster: three
+//      cluster barriers, histograms and the descriptor list exchanged through
+//      distributed shared memory); each CTA then resolves only the logical tokens
+//      of its own attention split to cache rows;
 //   3. every CTA gathers and attends to its split and writes its partial
 //      (acc, max, sum) rows and neighbour candidates;         -- cluster barrier --
 //   4. rank 0 merges the partials, writes the output and applies the online

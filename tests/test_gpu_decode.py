@@ -294,3 +294,58 @@ def test_append_kv_rows():
     assert torch.equal(key, want_key) and torch.equal(value, want_value)
     with pytest.raises(ValueError):
         ops.append_kv(key, value, new_key, new_value, 40)
+
+
+def test_full_size_batch_one_launch_equals_four_kernels():
+    """BASELINE config 4 as far as one layer goes (8 sequences x 8 KV heads at ctx 131072,
+    1024-4096 Zipf communities, budget 2048): the single cluster launch and the four
+    stand-alone kernels, fed the same inputs for three steps, leave bit-identical
+    workspaces and graph state (one unit of this size is checked against the CPU oracle
+    by ``test_zipf_communities_full_context_unit``)."""
+
+    from dataclasses import fields
+
+    from community_kv_b200 import native
+    from community_kv_b200.workload import build_decode_workload
+
+    device = torch.device("cuda", 0)
+
+    def build():
+        return build_decode_workload(
+            layers=1, batch=8, kv_heads=8, group_size=4, seq_len=131072, communities=(1024, 4096),
+            token_budget=2048, num_sink=10, max_decode_tokens=8, device=device, seed=3, zipf_exponent=1.1)
+
+    fused, plain = build(), build()
+    generator = torch.Generator(device=device).manual_seed(1)
+    stream = native.current_stream(device)
+
+    def tensors(obj):
+        found = {}
+        for item in fields(obj):
+            value = getattr(obj, item.name)
+            if isinstance(value, torch.Tensor):
+                found[item.name] = value
+            elif hasattr(value, "__dataclass_fields__"):
+                found.update({f"{item.name}.{k}": v for k, v in tensors(value).items()})
+        return found
+
+    for step in range(3):
+        query = torch.randn((8, 32, 128), generator=generator, device=device).to(torch.bfloat16)
+        for work, flag in ((fused, 0), (plain, native.FLAG_UNFUSED)):
+            args = work.runtime.pack(0, query=query, key=work.key[0], value=work.value[0], softmax_scale=SCALE)
+            args.flags = (args.flags & ~native.FLAG_UNFUSED) | flag
+            assert native.library().ckv_decode_layer_kernels(args) == (4 if flag else 1)
+            native.call("ckv_decode_layer", args, stream)
+        torch.cuda.synchronize()
+        left, right = fused.state(0), plain.state(0)
+        for name, a in {**tensors(left.workspace), **tensors(left.mutable)}.items():
+            b = {**tensors(right.workspace), **tensors(right.mutable)}[name]
+            if name.endswith(("partials", "partial_topk_packed", "score_cover")) or not a.numel():
+                continue
+            same = torch.equal(a.view(torch.uint8) if a.dtype == torch.float8_e4m3fn else a, b.view(torch.uint8) if b.dtype == torch.float8_e4m3fn else b)
+            if not same and a.is_floating_point():  # NaN-free by construction; compare bits
+                same = torch.equal(a.contiguous().view(torch.int16 if a.element_size() == 2 else torch.int32),
+                                   b.contiguous().view(torch.int16 if b.element_size() == 2 else torch.int32))
+            assert same, f"step {step}: {name} differs between the two paths"
+        assert torch.equal(left.current_position, right.current_position)
+    fused.runtime.assert_no_overflow()
