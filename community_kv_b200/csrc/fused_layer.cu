@@ -95,8 +95,7 @@ __global__ void __launch_bounds__(kFusedThreads, 3) decode_cluster_kernel(const 
   // ---- 3. gather + attention over this split ----
   attention_split<kBlocks>(a, flat, split, smem);
   phase_stamp(a, flat, split, 7);
-  __threadfence();
-  cluster_arrive();
+  cluster_arrive();  // release at cluster scope: the partials above are visible to rank 0
   if (split != 0) {
     return;
   }

@@ -1264,14 +1264,16 @@ __global__ void __launch_bounds__(kEdgeThreads, 1)
       // the other list's 16th score, a little low (any earlier value is also valid)
       const float partner_floor = floors[(wg ^ 1) * kPfRows + row] - 2.0f * a.exact_slack;
       float floor_score = fmaxf(own_floor, partner_floor);
+      // the next chunk's scores are requested before this chunk's list work and waited
+      // for after it
+      uint32_t raw[kGroup][16];
+#pragma unroll
+      for (int h = 0; h < kGroup; ++h) {
+        tmem_load16_issue(lane_base + h * kEdgeSub, raw[h]);
+      }
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll 1
       for (int c0 = 0; c0 < kEdgeSub; c0 += 16) {
-        uint32_t raw[kGroup][16];
-#pragma unroll
-        for (int h = 0; h < kGroup; ++h) {
-          tmem_load16_issue(lane_base + h * kEdgeSub + c0, raw[h]);
-        }
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         float best[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -1283,6 +1285,12 @@ __global__ void __launch_bounds__(kEdgeThreads, 1)
           const int j = key0 + c0 + i;
           const bool visible = plain || (j <= row_pos && j >= a.num_sink);
           best[i] = visible ? m * a.softmax_scale : -INFINITY;
+        }
+        if (c0 + 16 < kEdgeSub) {
+#pragma unroll
+          for (int h = 0; h < kGroup; ++h) {
+            tmem_load16_issue(lane_base + h * kEdgeSub + c0 + 16, raw[h]);
+          }
         }
         // Columns that beat the floor, as a bit mask.  The lanes then insert in
         // rounds: in every round each lane that still has such a column inserts its
@@ -1322,6 +1330,7 @@ __global__ void __launch_bounds__(kEdgeThreads, 1)
             }
           }
         }
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       }
       tc_fence_before();
       mbar_arrive(bar_s_free + 8 * wg);
