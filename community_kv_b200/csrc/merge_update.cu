@@ -95,27 +95,42 @@ cudaError_t launch_append_kv(void* key_cache, void* value_cache, const void* new
 }
 
 // One thread polls this GPU's counter a bounded number of times.
+// Launched with programmatic stream serialisation: it may start (and poll) while the
+// kernel before it in the stream is still running, and it only ends once that kernel
+// has completed, so whatever follows sees both the local and the peers' rows.
 __global__ void wait_peers_kernel(uint32_t* flag, uint32_t expected, uint32_t* status) {
+  pdl_release_dependents();
   constexpr uint32_t kPolls = 1u << 22;  // about two seconds with the back-off below
+  bool arrived = false;
   for (uint32_t poll = 0; poll < kPolls; ++poll) {
     uint32_t seen;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
     if (seen >= expected) {
       atomicSub(flag, expected);
-      return;
+      arrived = true;
+      break;
     }
     if (poll > 256) {
       __nanosleep(500);
     }
   }
-  if (status != nullptr) {
+  if (!arrived && status != nullptr) {
     atomicOr(status, CKV_DEV_WAIT_TIMEOUT);
   }
+  pdl_wait_for_predecessor();
 }
 
 cudaError_t launch_wait_peers(uint32_t* flag, uint32_t expected, uint32_t* status, cudaStream_t stream) {
-  wait_peers_kernel<<<1, 1, 0, stream>>>(flag, expected, status);
-  return cudaGetLastError();
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(1);
+  config.blockDim = dim3(1);
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, wait_peers_kernel, flag, expected, status);
 }
 
 cudaError_t launch_merge_update(const ckv_layer_args& a, cudaStream_t stream) {
