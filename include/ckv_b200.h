@@ -27,6 +27,11 @@
  *   ckv_prefill_topk         torch.ops.flash_attn_3.fwd(..., exclude_sink_tokens=n)
  *                            community_kv/attention/flash_attention.py:23-51
  *                            (third_party/flash_attention/community-kv.patch)
+ *   ckv_append_kv            the cache layer's index_copy_ of the decoded token
+ *                            community_kv/attention/cache.py:29-36
+ * Without a counterpart in the (single-GPU) reference: ckv_online_update,
+ * ckv_wait_peers and the peer_* fields (KV heads or sequence rows sharded over GPUs),
+ * ckv_segmented_attention_static, ckv_decode_layer_kernels.
  */
 #ifndef CKV_B200_H_
 #define CKV_B200_H_
