@@ -39,8 +39,10 @@ QUERY_HEADS = 32
 KV_HEADS = 8
 HEAD_DIM = 128
 CONTEXT = 131072
-# ncu: DRAM bytes of one decode_cluster_kernel launch at 8 sequences x 8 KV heads
-LAYER_TRAFFIC_BYTES = 98176000
+# ncu DRAM bytes of one layer launch, written by the profiling step next to its summary
+TRAFFIC_FILE = ROOT / "profiles" / "decode_cluster_kernel.traffic.json"
+CPU_DECODE_CAPACITY = 4096  # decode slots of a CPU worker's unit (far more than the time bound allows)
+BLAS_THREAD_VARIABLES = ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS", "NUMEXPR_NUM_THREADS")
 BUDGET = 2048
 NUM_SINK = 10
 COMMUNITIES = (1024, 4096)
@@ -93,7 +95,7 @@ def _cpu_worker(task: tuple[int, int, float]) -> tuple[int, float]:
     count = int(torch.randint(COMMUNITIES[0], COMMUNITIES[1] + 1, (1,), generator=generator))
     layer = make_layer(
         seed=seed, kv_heads=1, group_size=4, seq_len=context, communities=count,
-        num_sink=NUM_SINK, max_decode_tokens=64, zipf_exponent=ZIPF,
+        num_sink=NUM_SINK, max_decode_tokens=CPU_DECODE_CAPACITY, zipf_exponent=ZIPF,
     )
     converted = convert_prefill_tensors(**layer.prepare_kwargs())
     sinks = torch.arange(NUM_SINK, dtype=torch.int32)
@@ -116,7 +118,7 @@ def _cpu_worker(task: tuple[int, int, float]) -> tuple[int, float]:
         )
         done += 1
         elapsed = time.perf_counter() - begin
-        if elapsed >= seconds or done >= 60:
+        if elapsed >= seconds or done >= CPU_DECODE_CAPACITY - 8:  # the second bound: decode slots of the sample
             return done, elapsed
 
 
@@ -125,17 +127,31 @@ def cpu_baseline(seconds: float, context: int, layers: int, seed: int = 0) -> di
 
     import multiprocessing
 
-    cores = os.cpu_count() or 1
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     context_for_sample = context
     tasks = [(seed * 1000 + worker, context_for_sample, seconds) for worker in range(cores)]
-    with ProcessPoolExecutor(max_workers=cores, mp_context=multiprocessing.get_context("spawn")) as pool:
-        results = list(pool.map(_cpu_worker, tasks))
+    # One process per core, each strictly single-threaded: the BLAS / OpenMP pools read
+    # these variables when the worker imports numpy and torch, so they are set before the
+    # workers are spawned (otherwise every worker starts a pool as wide as the machine and
+    # the processes fight over the cores).
+    saved = {name: os.environ.get(name) for name in BLAS_THREAD_VARIABLES}
+    os.environ.update({name: "1" for name in BLAS_THREAD_VARIABLES})
+    try:
+        with ProcessPoolExecutor(max_workers=cores, mp_context=multiprocessing.get_context("spawn")) as pool:
+            results = list(pool.map(_cpu_worker, tasks))
+    finally:
+        for name, value in saved.items():
+            if value is None:
+                os.environ.pop(name, None)
+            else:
+                os.environ[name] = value
     unit_rate = sum(done / elapsed for done, elapsed in results)
     units_per_token = layers * KV_HEADS
     return {
         "value": unit_rate / units_per_token,
         "unit": "tokens/s",
         "cores": cores,
+        "threads_per_process": 1,
         "kind": "port",
         "sample": (
             f"{cores} processes x one (sequence, layer, KV head) unit each at ctx {context_for_sample}, "
@@ -171,12 +187,23 @@ def run_reference(args: argparse.Namespace) -> None:
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic",
-        "config": workload_config(args, batch=1, world=1),
+        "config": workload_config(
+            args, batch=(args.batch_per_gpu or 8) * args.gpus, world=args.gpus,
+            exchange_mode=default_exchange_mode(args, args.gpus),
+        ),
         "cpu_baseline": {**last, "value": value},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def default_exchange_mode(args: argparse.Namespace, world: int) -> str:
+    if world == 1:
+        return "none"
+    if args.exchange == "nccl":
+        return "nccl all-gather per layer"
+    return "peer stores from the merge phase; wait for the peers' rows: " + args.peer_wait
 
 
 def workload_config(args: argparse.Namespace, *, batch: int, world: int, exchange_mode: str = "none") -> dict:
@@ -195,6 +222,27 @@ def workload_config(args: argparse.Namespace, *, batch: int, world: int, exchang
         "splits": args.splits,
         "l2": "inputs larger than L2 (each step gathers rows scattered over the whole KV cache)",
     }
+
+
+def measured_traffic(units_per_launch: int, kernels_per_layer: int) -> tuple[int | None, str | None]:
+    """DRAM bytes of one layer launch as the profiler counted them (None without a capture).
+
+    The capture is taken on a smaller launch (fewer units); traffic grows in proportion to
+    the units a launch processes, so it is scaled by the unit count.
+    """
+
+    if kernels_per_layer != 1 or not TRAFFIC_FILE.exists():
+        return None, None
+    try:
+        record = json.loads(TRAFFIC_FILE.read_text())
+        per_unit = float(record["dram_bytes_per_launch"]) / float(record["units_per_launch"])
+    except (ValueError, KeyError, ZeroDivisionError):
+        return None, None
+    source = (
+        "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch with "
+        f"{record['units_per_launch']} units, scaled to {units_per_launch} units"
+    )
+    return int(per_unit * units_per_launch), source
 
 
 # --------------------------------------------------------------------------- #
@@ -329,10 +377,7 @@ def run_b200(args: argparse.Namespace) -> None:
         if float(ok) == 0.0:
             exchange = None
     if world > 1:
-        exchange_mode = (
-            "peer stores from the merge phase; wait for the peers' rows: " + args.peer_wait
-            if exchange else "nccl all-gather per layer"
-        )
+        exchange_mode = default_exchange_mode(args, world) if exchange else "nccl all-gather per layer"
     if exchange is not None:
         out_full = exchange.gathered
         out_local = None
@@ -550,6 +595,7 @@ def run_b200(args: argparse.Namespace) -> None:
     layer_gbs = layer_bytes / (layer_launch_ms * 1e-3) / 1e9
     step_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
 
+    traffic, traffic_source = measured_traffic(units_per_launch, kernels_per_layer)
     if rank != 0:
         finish(world, dist)
         return
@@ -581,9 +627,8 @@ def run_b200(args: argparse.Namespace) -> None:
             "unit": "GB/s",
             "frac": layer_gbs / peak,
             "peak_source": peak_source,
-            "traffic": LAYER_TRAFFIC_BYTES if (kernels_per_layer == 1 and units_per_launch == 64) else None,
-            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at this size "
-                              "(profiles/decode_cluster_kernel_b8_ctx131072.md)",
+            "traffic": traffic,
+            "traffic_source": traffic_source,
             "algorithmic_bytes_per_launch": layer_bytes,
             "launch_ms": layer_launch_ms,
             "kernels_per_layer": kernels_per_layer,

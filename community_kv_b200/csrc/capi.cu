@@ -19,8 +19,6 @@ cudaError_t launch_prefill(const ckv_prefill_args& a, cudaStream_t stream);
 
 namespace {
 
-enum Need { kNeedScore = 1, kNeedSelect = 2, kNeedAttention = 4 };
-
 int check_common(const ckv_layer_args* a) {
   if (a == nullptr) return CKV_ERR_NULL;
   if (a->batch <= 0 || a->retrieval_heads <= 0 || a->graphs <= 0) return CKV_ERR_SHAPE;
@@ -37,6 +35,11 @@ int check_common(const ckv_layer_args* a) {
   return CKV_OK;
 }
 
+}  // namespace
+
+// Argument validation shared by every entry point that takes ckv_layer_args (also
+// the allocation-free one in static_scratch.cu): nothing is launched, and no CUDA
+// call is made, before this returns CKV_OK.
 int check(const ckv_layer_args* a, int need) {
   const int common = check_common(a);
   if (common != CKV_OK) return common;
@@ -84,6 +87,8 @@ int check(const ckv_layer_args* a, int need) {
   }
   return CKV_OK;
 }
+
+namespace {
 
 int select_device(const ckv_layer_args* a) {
   int current = -1;

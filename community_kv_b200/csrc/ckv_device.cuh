@@ -18,6 +18,10 @@ constexpr int kPartialStride = CKV_PARTIAL_STRIDE;
 constexpr int kMaxDeltaWalk = 32;
 constexpr float kLog2e = 1.4426950408889634f;
 
+// Host-side argument validation (capi.cu): which groups of fields an entry point needs.
+enum Need { kNeedScore = 1, kNeedSelect = 2, kNeedAttention = 4 };
+int check(const ckv_layer_args* a, int need);
+
 // One launch covers `batch * retrieval_heads` independent units.
 struct Unit {
   int batch;

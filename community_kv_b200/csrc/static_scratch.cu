@@ -36,7 +36,9 @@ constexpr size_t kScratchBytes = kPositionBytes + kPartialBytes + kTopkBytes;
 // code this name is only a handle for cudaGetSymbolAddress, never an address.
 static __device__ __align__(256) unsigned char g_attention_scratch[kScratchBytes];
 
-// Device address of the array, looked up once per device.
+// Device address of the array, looked up once per device.  Two host threads that make
+// their first call on a device at the same time both look the address up and store the
+// same value, so the table needs no lock.
 unsigned char* g_scratch_address[64] = {};
 
 int scratch_for_device(int device, unsigned char** out) {
@@ -60,41 +62,21 @@ int scratch_for_device(int device, unsigned char** out) {
 extern "C" int ckv_segmented_attention_static(const ckv_layer_args* args, void* cuda_stream) {
   if (args == nullptr) return CKV_ERR_NULL;
   const ckv_layer_args& in = *args;
-  if (in.batch <= 0 || in.retrieval_heads <= 0 || in.graphs <= 0) return CKV_ERR_SHAPE;
-  if (in.group_size < 1 || in.token_budget <= 0 || in.token_budget % CKV_TILE) return CKV_ERR_SHAPE;
-  if (in.num_sink < 0 || in.num_sink + 1 >= in.token_budget) return CKV_ERR_SHAPE;
-  if (in.splits <= 0 || in.splits > in.token_budget / 16) return CKV_ERR_SHAPE;
   // the fixed scratch bounds every extent
-  if (static_cast<int64_t>(in.batch) * in.retrieval_heads > kMaxUnits ||
-      in.token_budget > kMaxBudget || in.splits > kMaxSplits || in.group_size > kMaxGroup) {
+  if (in.batch > 0 && in.retrieval_heads > 0 &&
+      (static_cast<int64_t>(in.batch) * in.retrieval_heads > kMaxUnits ||
+       in.token_budget > kMaxBudget || in.splits > kMaxSplits || in.group_size > kMaxGroup)) {
     return CKV_ERR_CAPACITY;
   }
-  if (!in.retrieval_to_graph || !in.retrieval_to_kv || !in.query || !in.key || !in.value ||
-      !in.output || !in.lse || !in.topk_scores || !in.topk_positions || !in.communities ||
-      !in.cumulative_ends || !in.descriptor_counts || !in.member_offsets ||
-      !in.member_positions || !in.current_position || !in.delta_positions || !in.chunk_start ||
-      !in.chunk_size || !in.chunk_previous || !in.community_tail || !in.delta_sizes) {
-    return CKV_ERR_NULL;
-  }
-  if (in.num_sink > 0 && !in.sink_positions) return CKV_ERR_NULL;
-  if (in.member_capacity <= 0 || in.chunks_per_graph <= 0 || in.delta_position_capacity <= 0 ||
-      in.sequence_capacity <= 0 || in.token_capacity <= 0 || in.community_capacity <= 0 ||
-      in.descriptor_capacity <= 0) {
-    return CKV_ERR_SHAPE;
-  }
-  if ((in.key_row_stride % 8) || (in.value_row_stride % 8) || (in.key_head_stride % 8) ||
-      (in.value_head_stride % 8) || (in.key_batch_stride % 8) || (in.value_batch_stride % 8) ||
-      (reinterpret_cast<uintptr_t>(in.key) % 16) || (reinterpret_cast<uintptr_t>(in.value) % 16)) {
-    return CKV_ERR_ALIGN;
-  }
-  if (in.key_row_stride < CKV_HEAD_DIM || in.value_row_stride < CKV_HEAD_DIM) return CKV_ERR_SHAPE;
-  if (!(in.flags & CKV_FLAG_SKIP_UPDATE)) {
-    if (!in.centroids || !in.community_sizes || !in.community_counts || !in.community_weight ||
-        !in.total_weight || !in.token_communities || !in.chunk_capacity || !in.chunk_next ||
-        !in.community_head || !in.next_free_chunk || !in.next_free_position || !in.assigned ||
-        !in.overflow) {
-      return CKV_ERR_NULL;
-    }
+  {
+    // the same validation as ckv_segmented_attention (peer fields included), with the
+    // three scratch pointers - which this entry point supplies itself - marked present
+    ckv_layer_args probe = in;
+    probe.positions = reinterpret_cast<int32_t*>(sizeof(int32_t));
+    probe.partials = reinterpret_cast<float*>(sizeof(float));
+    probe.partial_topk = reinterpret_cast<uint64_t*>(sizeof(uint64_t));
+    const int status = ckv::check(&probe, ckv::kNeedAttention);
+    if (status != CKV_OK) return status;
   }
 
   unsigned char* scratch = nullptr;

@@ -315,3 +315,24 @@ def test_argument_errors_come_back_as_status_codes():
     assert lib.ckv_score_centroids(ctypes.byref(args), None) == -2
     with pytest.raises(native.NativeError, match="status -2"):
         native.call("ckv_decode_layer", args, 0)
+
+
+def test_static_entry_point_applies_the_shared_validation():
+    """The allocation-free entry point rejects what the regular one rejects, before any CUDA call:
+    a peer count beyond CKV_MAX_PEERS would otherwise index past the peer pointer arrays."""
+
+    lib = native.library()
+    keep = (ctypes.c_int32 * 4)()
+    address = ctypes.addressof(keep)
+    for entry in ("ckv_segmented_attention", "ckv_segmented_attention_static"):
+        args = native.LayerArgs()
+        native.fill(args, batch=1, retrieval_heads=1, graphs=1, group_size=4, community_capacity=4,
+                    token_budget=128, num_sink=1, splits=1, retrieval_to_graph=address,
+                    retrieval_to_kv=address, peer_count=native.MAX_PEERS + 1)
+        assert getattr(lib, entry)(ctypes.byref(args), None) == -2, entry
+        args.peer_count = 1  # in range, but the peer's pointers are missing
+        assert getattr(lib, entry)(ctypes.byref(args), None) == -1, entry
+    args = native.LayerArgs()
+    native.fill(args, batch=65, retrieval_heads=1, graphs=1, group_size=4, community_capacity=4,
+                token_budget=128, num_sink=1, splits=1)
+    assert lib.ckv_segmented_attention_static(ctypes.byref(args), None) == -7

@@ -74,6 +74,53 @@ def test_static_scratch_entry_point_matches_the_regular_one():
         assert not torch.isnan(static.attention.output.float()).any()
 
 
+def test_static_scratch_entry_point_updates_the_graph_like_the_regular_one():
+    """With the online update enabled the merge reads its neighbour candidates from the
+    built-in array: both entry points must leave identical graph state, three steps in a row."""
+
+    from tests.helpers import assert_state_equal, cpu_clone
+
+    device = torch.device("cuda", 0)
+    budget, sinks = 512, 6
+    layer = make_layer(seed=79, kv_heads=4, seq_len=4096, communities=80, max_decode_tokens=6).to(device)
+    sink_positions = torch.arange(sinks, dtype=torch.int32, device=device)
+    sides = []
+    for _ in range(2):
+        converted = convert_prefill_tensors(**layer.prepare_kwargs())
+        workspace = DecodeLayerWorkspace.allocate(
+            retrieval_head_count=4, graph_count=4, group_size=4,
+            community_capacity=converted.mutable.community_capacity, token_budget=budget, num_sink=sinks,
+            dtype=torch.bfloat16, device=device, splits=4,
+        )
+        sides.append((converted, workspace))
+    for step in range(3):
+        query = make_query(seed=950 + step, query_heads=16).to(device)
+        for index, (converted, workspace) in enumerate(sides):
+            state = converted.mutable
+            segments = ops.score_and_select(
+                query=query, centroids=state.centroids, community_sizes=state.community_sizes,
+                community_counts=state.community_counts, workspace=workspace.selection, csr=converted.csr,
+                state=state, sink_positions=sink_positions, current_position=converted.current_position,
+            )
+            call = ops.segmented_attention_static if index else ops.segmented_attention
+            call(
+                query=query, key=layer.key, value=layer.value, csr=converted.csr, deltas=state.deltas,
+                segments=segments, sink_positions=sink_positions, current_position=converted.current_position,
+                softmax_scale=128**-0.5, workspace=workspace.attention, update_state=state,
+                update_workspace=workspace.update, update_lam=0.5,
+            )
+        torch.cuda.synchronize()
+        (regular, regular_ws), (static, static_ws) = sides
+        where = f"step {step}"
+        assert torch.equal(static_ws.attention.output, regular_ws.attention.output), where
+        assert torch.equal(static_ws.update.assigned_communities, regular_ws.update.assigned_communities), where
+        assert torch.equal(static_ws.update.overflow, regular_ws.update.overflow), where
+        assert int(regular_ws.update.overflow.max()) == 0
+        _, want, current = cpu_clone(regular.csr, regular.mutable, regular.current_position)
+        assert_state_equal(static.mutable, want, where)
+        assert torch.equal(static.current_position.cpu(), current), where
+
+
 def test_static_scratch_entry_point_rejects_oversized_requests():
     device = torch.device("cuda", 0)
     layer = make_layer(seed=78, kv_heads=2, seq_len=2048, communities=40, max_decode_tokens=2)
