@@ -124,6 +124,21 @@ __device__ __forceinline__ float fma2_bf16(uint32_t a, uint32_t b, float acc) {
   return acc;
 }
 
+// Running mean of a centroid element, (old * n + key) / (n + 1), before it is stored
+// as e4m3.  `reference_division` selects the approximate division the reference's
+// compiled kernel uses; otherwise the division is IEEE round-to-nearest.
+__device__ __forceinline__ float centroid_mean(float old_value, int old_size, float key_value,
+                                               bool reference_division) {
+  const float numerator = __fadd_rn(__fmul_rn(old_value, static_cast<float>(old_size)), key_value);
+  const float denominator = static_cast<float>(old_size + 1);
+  if (reference_division) {
+    float quotient;
+    asm("div.full.f32 %0, %1, %2;" : "=f"(quotient) : "f"(numerator), "f"(denominator));
+    return quotient;
+  }
+  return __fdiv_rn(numerator, denominator);
+}
+
 // Optional phase timestamps of the single-launch decode path (see ckv_layer_args).
 __device__ __forceinline__ void phase_stamp(const ckv_layer_args& a, int flat, int rank, int slot) {
   if (a.phase_times != nullptr && threadIdx.x == 0) {

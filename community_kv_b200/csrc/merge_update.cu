@@ -58,8 +58,7 @@ __global__ void __launch_bounds__(kMergeThreads) sync_shared_kernel(const ckv_la
     if (old_size > 0) {
       const __half_raw raw = __nv_cvt_fp8_to_halfraw(centroid[d], __NV_E4M3);
       const float old_value = __half2float(*reinterpret_cast<const __half*>(&raw));
-      updated = __fdiv_rn(__fadd_rn(__fmul_rn(old_value, static_cast<float>(old_size)), key_value),
-                          static_cast<float>(old_size + 1));
+      updated = centroid_mean(old_value, old_size, key_value, (a.flags & CKV_FLAG_REFERENCE_DIVISION) != 0);
     }
     centroid[d] = __nv_cvt_float_to_fp8(updated, __NV_SATFINITE, __NV_E4M3);
   }

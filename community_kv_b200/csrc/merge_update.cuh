@@ -464,9 +464,8 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
       }
       const __half_raw raw = __nv_cvt_fp8_to_halfraw(stored, __NV_E4M3);
       const float old_value = __half2float(*reinterpret_cast<const __half*>(&raw));
-      const float n = static_cast<float>(decision.old_size);
-      updated = __fdiv_rn(__fadd_rn(__fmul_rn(old_value, n), key_value),
-                          static_cast<float>(decision.old_size + 1));
+      updated = centroid_mean(old_value, decision.old_size, key_value,
+                              (a.flags & CKV_FLAG_REFERENCE_DIVISION) != 0);
     }
     centroid[d] = __nv_cvt_float_to_fp8(updated, __NV_SATFINITE, __NV_E4M3);
   }

@@ -161,6 +161,7 @@ FLAG_ATTENTION_ONLY = 2
 FLAG_UPDATE_ONLY = 4
 # ckv_decode_layer: four stand-alone kernels instead of the single cluster launch
 FLAG_UNFUSED = 8
+FLAG_REFERENCE_DIVISION = 16  # centroid mean with the reference kernel's approximate division
 DEV_WAIT_TIMEOUT = 1
 PARTIAL_STRIDE = 132
 
@@ -249,6 +250,7 @@ __all__ = [
     "ENTRY_POINTS",
     "FLAG_ATTENTION_ONLY",
     "FLAG_SKIP_UPDATE",
+    "FLAG_REFERENCE_DIVISION",
     "FLAG_UNFUSED",
     "FLAG_UPDATE_ONLY",
     "LayerArgs",

@@ -487,11 +487,20 @@ def segmented_attention_static(
 
 
 def _layout_flags() -> int:
-    """``CKV_UNFUSED=1`` in the environment selects the four stand-alone kernels for
-    ``ckv_decode_layer`` instead of the single cluster launch (same results; a
-    debugging and A/B-timing switch)."""
+    """Process-wide switches read from the environment.
 
-    return native.FLAG_UNFUSED if os.environ.get("CKV_UNFUSED") == "1" else 0
+    ``CKV_UNFUSED=1`` selects the four stand-alone kernels for ``ckv_decode_layer``
+    instead of the single cluster launch (same results; a debugging and A/B-timing
+    switch).  ``CKV_REFERENCE_DIVISION=1`` makes the running centroid mean divide like
+    the reference's compiled Triton kernel (approximate ``div.full.f32``) instead of
+    like its CPU test helper (IEEE division): the stored e4m3 centroid then matches the
+    reference kernel bit for bit also when the exact quotient is a rounding tie.
+    """
+
+    flags = native.FLAG_UNFUSED if os.environ.get("CKV_UNFUSED") == "1" else 0
+    if os.environ.get("CKV_REFERENCE_DIVISION") == "1":
+        flags |= native.FLAG_REFERENCE_DIVISION
+    return flags
 
 
 def build_layer_args(

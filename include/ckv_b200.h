@@ -72,6 +72,13 @@ typedef enum ckv_status {
                                      position resolution, no merge); for kernel timing */
 #define CKV_FLAG_UNFUSED 8        /* ckv_decode_layer: run the four stand-alone kernels even when
                                      the single cluster launch is available (same results) */
+#define CKV_FLAG_REFERENCE_DIVISION 16 /* running centroid mean (old*n + key)/(n+1): divide with the
+                                     GPU's approximate full-range division (div.full.f32, at most 2 ulp
+                                     off), which is what the reference's Triton kernel compiles `/` to
+                                     (segmented_attention.py:708-713), instead of IEEE division, which is
+                                     what the reference's CPU test helper computes (tests/community_kv/
+                                     graph/test_state.py:32-132).  The two differ when the exact quotient
+                                     is a rounding tie of the e4m3 result. */
 
 typedef struct ckv_layer_args {
   /* ---- geometry ---- */

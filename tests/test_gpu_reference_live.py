@@ -55,6 +55,10 @@ def reference():
     if not (REF_ROOT / "community_kv").is_dir():
         pytest.skip("oracle/_ref is not prepared (python oracle/make_ref.py <reference checkout>)")
     sys.path.insert(0, str(REF_ROOT))
+    # the compiled reference kernel divides approximately in its centroid update
+    # (Triton lowers `/` to div.full.f32); ask this library for the same instruction
+    saved = os.environ.get("CKV_REFERENCE_DIVISION")
+    os.environ["CKV_REFERENCE_DIVISION"] = "1"
     try:
         runtime = importlib.import_module("community_kv.runtime")
         config = importlib.import_module("community_kv.config")
@@ -66,6 +70,10 @@ def reference():
         yield {"runtime": runtime, "config": config, "selection": selection}
     finally:
         sys.path.remove(str(REF_ROOT))
+        if saved is None:
+            os.environ.pop("CKV_REFERENCE_DIVISION", None)
+        else:
+            os.environ["CKV_REFERENCE_DIVISION"] = saved
         if os.environ.get("CKV_LIVE_REPORT") and REPORT:
             Path(os.environ["CKV_LIVE_REPORT"]).write_text(json.dumps(REPORT, indent=1))
 
@@ -108,6 +116,25 @@ def _states_equal(ours, theirs) -> list[str]:
     return bad
 
 
+def _centroid_detail(ours, theirs, before_centroids, before_sizes, key) -> str:
+    """The first few centroid bytes that differ, with the operands of their running-mean update."""
+
+    a = ours.converted.mutable.centroids.view(torch.uint8)
+    b = theirs.converted.mutable.centroids.view(torch.uint8)
+    where = (a != b).nonzero()
+    lines = [f"{where.shape[0]} bytes differ"]
+    row = int(theirs.converted.current_position[0]) - 1
+    for head, community, dim in where[:6].tolist():
+        kv = int(theirs.converted.mutable.retrieval_to_kv[head])
+        lines.append(
+            f"(head {head}, community {community}, dim {dim}): ours {float(ours.converted.mutable.centroids[head, community, dim].float())} "
+            f"theirs {float(theirs.converted.mutable.centroids[head, community, dim].float())} "
+            f"old {float(before_centroids[head, community, dim].float())} size {int(before_sizes[head, community])} "
+            f"key {float(key[kv, row, dim].float())}"
+        )
+    return "; ".join(lines)
+
+
 def _ulp_distance(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """Distance in fp16 units in the last place (0 where both are -inf)."""
 
@@ -133,14 +160,17 @@ def _run(reference, name, *, layer_kwargs, config_kwargs, steps, seed):
         **{**config_kwargs, "aggregation": reference["config"].GraphAggregation(GraphAggregation(aggregation).value)}
     )
     ref_rt = reference["runtime"].DecodeRuntime(ref_config)
-    kwargs = layer.prepare_kwargs()
-    ours = ours_rt.prepare_layer(0, **kwargs)
-    ref_kwargs = dict(kwargs)
-    ref_kwargs["aggregation"] = ref_config.aggregation
-    theirs = ref_rt.prepare_layer(0, **{k: (v.clone() if torch.is_tensor(v) else v) for k, v in ref_kwargs.items()})
+    def fresh(**override):
+        # conversion keeps some of the tensors it is given: every side gets its own copies
+        kwargs = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in layer.prepare_kwargs().items()}
+        kwargs.update(override)
+        return kwargs
+
+    ours = ours_rt.prepare_layer(0, **fresh())
+    theirs = ref_rt.prepare_layer(0, **fresh(aggregation=ref_config.aggregation))
     # a second library-side layer that is fed the reference's scores
     fed_rt = DecodeRuntime(CommunityKVConfig(**config_kwargs))
-    fed = fed_rt.prepare_layer(0, **kwargs)
+    fed = fed_rt.prepare_layer(0, **fresh())
     key, value = layer.key[None], layer.value[None]
     heads = ours.converted.mutable.retrieval_head_count
     lam = config_kwargs["lam"]
@@ -157,6 +187,8 @@ def _run(reference, name, *, layer_kwargs, config_kwargs, steps, seed):
         # every side starts this step from the reference's current state
         _copy_state(ours, theirs)
         _copy_state(fed, theirs)
+        before_centroids = theirs.converted.mutable.centroids.clone()
+        before_sizes = theirs.converted.mutable.community_sizes.clone()
         want_out = ref_rt.decode(layer_idx=0, query=q4, key=key, value=value, softmax_scale=SCALE).clone()
         ref_ws = theirs.workspace
         # ---- (1) own scores: the whole layer in one library call ----
@@ -207,7 +239,10 @@ def _run(reference, name, *, layer_kwargs, config_kwargs, steps, seed):
         assert float(diff.mean()) <= OUTPUT_MEAN_ABS, f"{where}: output mean-abs {float(diff.mean())}"
         torch.testing.assert_close(lse, ref_ws.attention.lse, rtol=0, atol=2e-3, msg=f"{where}: lse")
         same_top = True
-        for h in range(heads):
+        # only the head that leads a graph reports neighbours in the reference
+        # (segmented_attention.py:486: the other rows of its workspace are never written)
+        leaders = [h for h in range(heads) if int(fed.converted.mutable.retrieval_to_graph[h]) == h]
+        for h in leaders:
             a = sorted(top_positions[h].tolist())
             b = sorted(ref_ws.attention.topk_positions[h].tolist())
             if a != b:
@@ -216,22 +251,26 @@ def _run(reference, name, *, layer_kwargs, config_kwargs, steps, seed):
         if not torch.equal(fed.workspace.update.assigned_communities, ref_ws.update.assigned_communities):
             stats["label_differs"] += 1
         if same_top:
-            assert torch.equal(top_positions, ref_ws.attention.topk_positions), f"{where}: top-8 order"
-            torch.testing.assert_close(top_scores, ref_ws.attention.topk_scores, rtol=0, atol=1e-4,
-                                       msg=f"{where}: top-8 scores")
+            assert torch.equal(top_positions[leaders], ref_ws.attention.topk_positions[leaders]), \
+                f"{where}: top-8 order"
+            torch.testing.assert_close(top_scores[leaders], ref_ws.attention.topk_scores[leaders], rtol=0,
+                                       atol=1e-4, msg=f"{where}: top-8 scores")
             assert torch.equal(fed.workspace.update.assigned_communities, ref_ws.update.assigned_communities), \
                 f"{where}: online label"
             assert torch.equal(fed.workspace.update.overflow, ref_ws.update.overflow), f"{where}: overflow"
             bad = _states_equal(fed, theirs)
             stats["state_mismatch_fields"] += bad
-            assert not bad, f"{where}: graph state differs in {bad}"
+            detail = ""
+            if "centroids" in bad:
+                detail = _centroid_detail(fed, theirs, before_centroids, before_sizes, key[0])
+            assert not bad, f"{where}: graph state differs in {bad} {detail}"
     stats["score_ulp_nonzero_share"] = nonzero / max(scored, 1)
     stats["selection_flip_rate"] = stats["selection_flips_own_scores"] / (steps * heads)
     REPORT[name] = stats
     print(name, json.dumps(stats))
     # the tensor-core summation order may move a score by one unit in the last place
     assert stats["score_ulp_max"] <= 1, stats
-    assert stats["top8_set_differs"] <= max(1, (steps * heads) // 20), stats
+    assert stats["top8_set_differs"] <= max(1, (steps * len(leaders)) // 20), stats
     return stats
 
 

@@ -86,7 +86,10 @@ def test_static_scratch_entry_point_updates_the_graph_like_the_regular_one():
     sink_positions = torch.arange(sinks, dtype=torch.int32, device=device)
     sides = []
     for _ in range(2):
-        converted = convert_prefill_tensors(**layer.prepare_kwargs())
+        # conversion keeps some of the tensors it is given: each side gets its own copies
+        converted = convert_prefill_tensors(
+            **{k: (v.clone() if torch.is_tensor(v) else v) for k, v in layer.prepare_kwargs().items()}
+        )
         workspace = DecodeLayerWorkspace.allocate(
             retrieval_head_count=4, graph_count=4, group_size=4,
             community_capacity=converted.mutable.community_capacity, token_budget=budget, num_sink=sinks,
