@@ -70,6 +70,9 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--peer-wait", choices=["node", "launch"], default="node",
                         help="peer exchange: wait for the peers' rows in a one-thread kernel after each layer "
                              "(node) or inside the layer launch itself (launch)")
+    parser.add_argument("--update", choices=["inline", "deferred"], default="inline",
+                        help="online graph update inside the layer launch (inline), or as its own launch on a "
+                             "second stream that runs beside the next layer's launch (deferred)")
     parser.add_argument("--sweep-context", type=int, default=1_048_576)
     parser.add_argument("--workload", choices=["decode", "prefill", "sweep"], default="decode",
                         help="prefill: the score-graph emission kernel at S=16384 (a second, separate line)")
@@ -220,6 +223,7 @@ def workload_config(args: argparse.Namespace, *, batch: int, world: int, exchang
         "exchange": exchange_mode,
         "layers_per_launch": args.layers_per_launch,
         "splits": args.splits,
+        "update": args.update,
         "l2": "inputs larger than L2 (each step gathers rows scattered over the whole KV cache)",
     }
 
@@ -404,15 +408,42 @@ def run_b200(args: argparse.Namespace) -> None:
             if exchange is not None:
                 exchange.attach(packed[-1], launch, wait_in_kernel=args.peer_wait == "launch")
 
+    # Deferred update: the layer launch stops after the head outputs, the neighbour
+    # candidates and the log-sum-exp are written; the online assignment of that layer runs
+    # as a second launch on a side stream (nothing downstream of the attention output
+    # depends on it) and is joined before the step ends, i.e. before the layer's next step.
+    deferred = args.update == "deferred"
+    side = torch.cuda.Stream(device) if deferred else None
+    attend_args, update_args = [], []
+    for launch in range(launches if deferred else 0):
+        attend = native.LayerArgs.from_buffer_copy(packed[launch])
+        attend.flags |= native.FLAG_SKIP_UPDATE
+        attend_args.append(attend)
+        update = native.LayerArgs.from_buffer_copy(packed[launch])
+        update.peer_count = 0
+        update.peer_wait_flag = None
+        update_args.append(update)
+
     def enqueue_step() -> None:
         handle = stream.cuda_stream
         for launch in range(launches):
-            native.call("ckv_decode_layer", packed[launch], handle)
+            if deferred:
+                native.call("ckv_decode_layer", attend_args[launch], handle)
+                attended = torch.cuda.Event()
+                attended.record(stream)
+                side.wait_event(attended)
+                native.call("ckv_online_update", update_args[launch], side.cuda_stream)
+            else:
+                native.call("ckv_decode_layer", packed[launch], handle)
             if exchange is not None:
                 if args.peer_wait == "node":
                     exchange.wait(launch, handle)  # the next consumer needs every rank's heads
             elif world > 1:
                 dist.all_gather_into_tensor(out_full[launch], out_local[launch])
+        if deferred:
+            updated = torch.cuda.Event()
+            updated.record(side)
+            stream.wait_event(updated)
 
     def new_queries(count: int) -> "torch.Tensor":
         return torch.randn((count, launches, slots, query_local, HEAD_DIM), generator=generator,
@@ -520,6 +551,7 @@ def run_b200(args: argparse.Namespace) -> None:
             "score": stat(span(0, 1)),
             "select_wait_for_cluster": stat(span(1, 2)),
             "select_exchanges": stat(span(2, 5)),
+            "select_detail": {"2_3": stat(span(2, 3)), "3_4": stat(span(3, 4)), "4_5": stat(span(4, 5))},
             "resolve_positions": stat(span(5, 6)),
             "gather_attention": stat(span(6, 7)),
             "wait_for_cluster": stat(span(7, 8, slice(0, 1))),
@@ -654,7 +686,7 @@ def run_b200(args: argparse.Namespace) -> None:
             "d2h_bytes_per_step": int(pinned_out.numel() * 2),
         },
         "phases_us": phases_us,
-        "gpu_launches": args.steps * launches * kernels_per_layer,
+        "gpu_launches": args.steps * launches * (kernels_per_layer + (1 if deferred else 0)),
         "cuda_graph": use_graph,
         "clocks": clocks,
         "build_seconds": build_seconds,

@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(kFusedThreads, 3) decode_cluster_kernel(const 
   cluster_select_begin<kFusedThreads>(sm);
   {
     const ScoreSlice slice = {sm.key, sm.size, sm.hist_mass, sm.hist_count, first_group * 16};
-    score_groups<kFusedThreads>(a, flat, first_group, last_group, sm.query, &slice);
+    score_groups<kFusedThreads, kClusterStageBytes>(a, flat, first_group, last_group, sm.query, &slice);
   }
   __syncthreads();
   phase_stamp(a, flat, split, 1);

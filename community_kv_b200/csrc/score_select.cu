@@ -17,8 +17,11 @@
 namespace ckv {
 
 __global__ void __launch_bounds__(kScoreThreads, 2) score_kernel(const ckv_layer_args a) {
-  // query group as fp32, every value stored twice (see score_groups)
-  __shared__ __align__(16) float q_s[2 * 16 * kHeadDim];
+  // query group as fp32, every value stored twice, or one staged e4m3 row group per warp
+  // (see score_groups)
+  constexpr int kStageBytes = (kScoreThreads / 32) * (16 * kHeadDim + 64);
+  static_assert(kStageBytes >= 2 * 16 * kHeadDim * 4, "the staging area also holds the fp32 query group");
+  __shared__ __align__(128) float q_s[kStageBytes / 4];
   __shared__ int prefix[kScoreMaxUnits + 1];
   const int units = a.batch * a.retrieval_heads;
   const int warp = threadIdx.x >> 5;
@@ -82,7 +85,7 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_kernel(const ckv_layer
     if (first_group >= last_group) {
       continue;
     }
-    score_groups<kScoreThreads>(a, flat, first_group, last_group, q_s);
+    score_groups<kScoreThreads, kStageBytes>(a, flat, first_group, last_group, q_s);
   }
 }
 

@@ -2,6 +2,8 @@
 // the stand-alone kernels and the fused per-layer cluster kernel (sm_100a).
 #pragma once
 
+#include <cstddef>
+
 #include "ckv_device.cuh"
 
 namespace ckv {
@@ -73,12 +75,20 @@ __device__ __forceinline__ void score_groups_impl(const ckv_layer_args& a, int f
   // per group
   constexpr int kStride = kThreads / 32;
   uint4 raw_even[4], raw_odd[4];
+  int size_even = 0, size_odd = 0;  // size of this lane's row, fetched with the group's rows
+  const int32_t* sizes = a.community_sizes + static_cast<int64_t>(flat) * capacity;
+  auto load_size = [&](int group_index) {
+    const int row = group_index * 16 + my_row_in_group;
+    return ((slice & 1) == 0 && row < limit) ? __ldg(sizes + row) : 0;
+  };
   int current = first_group + warp;
   if (current < last_group) {
     load_group(table, current * 16, quad, slice, capacity, raw_even);
+    size_even = load_size(current);
   }
   if (current + kStride < last_group) {
     load_group(table, (current + kStride) * 16, quad, slice, capacity, raw_odd);
+    size_odd = load_size(current + kStride);
   }
   const __nv_bfloat16* query =
       reinterpret_cast<const __nv_bfloat16*>(a.query) + static_cast<int64_t>(flat) * group * kHeadDim;
@@ -111,10 +121,9 @@ __device__ __forceinline__ void score_groups_impl(const ckv_layer_args& a, int f
   __syncthreads();
 
   const int count = a.community_counts[flat];
-  const int32_t* sizes = a.community_sizes + static_cast<int64_t>(flat) * capacity;
   __half* out = reinterpret_cast<__half*>(a.scores) + static_cast<int64_t>(flat) * capacity;
 
-  auto score_one = [&](uint4 (&raw)[4], int current) {
+  auto score_one = [&](uint4 (&raw)[4], int& held_size, int current) {
     // The narrow path widens e4m3 to bf16 with integer operations and feeds
     // mixed-precision FMAs (bf16 x bf16 + fp32, one rounding: the same value as
     // the fp32 FMA of the widened operands); the wide path widens to fp32.
@@ -135,14 +144,12 @@ __device__ __forceinline__ void score_groups_impl(const ckv_layer_args& a, int f
       }
     }
     const int next = current + 2 * kStride;  // this buffer's next group
+    const int size = held_size;
     if (next < last_group) {
       load_group(table, next * 16, quad, slice, capacity, raw);
+      held_size = load_size(next);
     }
     const int row = current * 16 + my_row_in_group;
-    int size = 0;
-    if ((slice & 1) == 0 && row < limit) {
-      size = __ldg(sizes + row);
-    }
 
     float best;
     if constexpr (kNarrow) {
@@ -234,17 +241,161 @@ __device__ __forceinline__ void score_groups_impl(const ckv_layer_args& a, int f
     }
   };
   for (; current < last_group; current += 2 * kStride) {
-    score_one(raw_even, current);
+    score_one(raw_even, size_even, current);
     if (current + kStride < last_group) {
-      score_one(raw_odd, current + kStride);
+      score_one(raw_odd, size_odd, current + kStride);
     }
   }
 }
 
-template <int kThreads>
+// Tensor-core variant of score_groups (CKV_FLAG_TENSOR_SCORES, group size <= 8).
+//
+// A 16-row group is one mma.m16n8k16 tile: the 16 communities on M, the (padded)
+// query group on N = 8, eight k-blocks of 16 dimensions accumulated in ascending
+// order in fp32.  The e4m3 rows travel global -> shared memory with 16-byte cp.async
+// (no register staging; `stage` holds two groups per warp for four warps) and are
+// read back with ldmatrix, which hands thread (g, t) the four bytes 4t..4t+3 of row
+// g's 16-byte chunk: after the integer widening to bf16 those are exactly one
+// A-fragment pair, so no shuffle is needed.  (The order of the 16 products inside one
+// k-block does not change the result of the instruction, so the query fragments use
+// the same 4t..4t+3 assignment.)  The sum is the hardware's, not the fixed CUDA-core
+// order: a score may differ from the fixed-order one in the last fp16 bit.
+template <int kThreads, int kStageBytes>
+__device__ __forceinline__ void score_groups_mma(const ckv_layer_args& a, int flat, int first_group,
+                                                 int last_group, float* stage_f,
+                                                 const ScoreSlice* slice_out) {
+  constexpr int kWarps = kThreads / 32;
+  constexpr int kGroupBytes = 16 * kHeadDim;                 // one staged group of e4m3 rows
+  constexpr int kSlotBytes = kGroupBytes + 64;               // ... followed by the rows' sizes
+  constexpr int kRing = kStageBytes / (kWarps * kSlotBytes);   // groups in flight per warp
+  static_assert(kRing >= 1 && kRing <= 4, "staging area: one to four groups per warp");
+  const int group = a.group_size;
+  const int capacity = a.community_capacity;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const int limit = score_limit(a, flat);
+  const uint8_t* table = reinterpret_cast<const uint8_t*>(a.centroids) +
+                         static_cast<int64_t>(flat) * capacity * kHeadDim;
+  const uint32_t stage = smem_u32(stage_f) + warp * (kRing * kSlotBytes);
+  const int32_t* sizes = a.community_sizes + static_cast<int64_t>(flat) * capacity;
+  __syncthreads();  // the staging area is free (a previous unit's rows have been consumed)
+
+  auto issue = [&](int group_index, int slot) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int piece = lane + 32 * i;
+      const int row = piece >> 3;
+      const int chunk = piece & 7;
+      const int source_row = min(group_index * 16 + row, capacity - 1);
+      cp_async16(stage + slot * kSlotBytes + row * kHeadDim + ((chunk ^ (row & 7)) << 4),
+                 table + static_cast<int64_t>(source_row) * kHeadDim + chunk * 16, 16u);
+    }
+    if (lane < 16) {
+      cp_async4(stage + slot * kSlotBytes + kGroupBytes + lane * 4,
+                sizes + min(group_index * 16 + lane, capacity - 1));
+    }
+  };
+  constexpr int kStride = kWarps;
+  int current = first_group + warp;
+#pragma unroll
+  for (int r = 0; r < kRing; ++r) {
+    if (current + r * kStride < last_group) {
+      issue(current + r * kStride, r);
+    }
+    cp_async_commit();
+  }
+
+  // B fragments: head g of the group (zero beyond it), dimensions 16j + 4t .. + 3
+  uint32_t qb[8][2];
+  {
+    const __nv_bfloat16* query = reinterpret_cast<const __nv_bfloat16*>(a.query) +
+                                 static_cast<int64_t>(flat) * group * kHeadDim;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint2 pair = make_uint2(0u, 0u);
+      if (g < group) {
+        pair = *reinterpret_cast<const uint2*>(query + g * kHeadDim + 16 * j + 4 * t);
+      }
+      qb[j][0] = pair.x;
+      qb[j][1] = pair.y;
+    }
+  }
+  const int count = a.community_counts[flat];
+  __half* out = reinterpret_cast<__half*>(a.scores) + static_cast<int64_t>(flat) * capacity;
+  // ldmatrix.x4 row address of this lane: matrix m = lane >> 3 covers rows 8 (m & 1) ..,
+  // chunk j + (m >> 1)
+  const int lm_row = (lane & 7) + 8 * ((lane >> 3) & 1);
+  const int lm_chunk = lane >> 4;
+
+  int slot = 0;
+  for (; current < last_group; current += kStride) {
+    // lanes t == 0 report row g, lanes t == 1 row g + 8
+    const int row = current * 16 + g + 8 * (t & 1);
+    cp_async_wait<kRing - 1>();
+    __syncwarp();
+    int size;
+    asm volatile("ld.shared.s32 %0, [%1];"
+                 : "=r"(size)
+                 : "r"(stage + slot * kSlotBytes + kGroupBytes + (g + 8 * (t & 1)) * 4));
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint32_t base = stage + slot * kSlotBytes + lm_row * kHeadDim;
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      uint32_t r0, r1, r2, r3;
+      ldmatrix_x4(base + (((j + lm_chunk) ^ (lm_row & 7)) << 4), r0, r1, r2, r3);
+      uint32_t a0, a1, a2, a3;
+      e4m3x4_to_bf16x2(r0, a0, a2);
+      e4m3x4_to_bf16x2(r1, a1, a3);
+      mma_bf16_16816(d, a0, a1, a2, a3, qb[j][0], qb[j][1]);
+      e4m3x4_to_bf16x2(r2, a0, a2);
+      e4m3x4_to_bf16x2(r3, a1, a3);
+      mma_bf16_16816(d, a0, a1, a2, a3, qb[j + 1][0], qb[j + 1][1]);
+    }
+    __syncwarp();  // every lane has read the slot
+    if (current + kRing * kStride < last_group) {
+      issue(current + kRing * kStride, slot);
+    }
+    cp_async_commit();
+    slot = (slot + 1) % kRing;
+    // d0/d1: row g, heads 2t, 2t+1; d2/d3: row g + 8
+    const bool head0 = 2 * t < group;
+    const bool head1 = 2 * t + 1 < group;
+    float low = fmaxf(head0 ? d[0] : -INFINITY, head1 ? d[1] : -INFINITY);
+    float high = fmaxf(head0 ? d[2] : -INFINITY, head1 ? d[3] : -INFINITY);
+    low = fmaxf(low, __shfl_xor_sync(0xffffffffu, low, 1));
+    high = fmaxf(high, __shfl_xor_sync(0xffffffffu, high, 1));
+    low = fmaxf(low, __shfl_xor_sync(0xffffffffu, low, 2));
+    high = fmaxf(high, __shfl_xor_sync(0xffffffffu, high, 2));
+    if (t < 2 && row < limit) {
+      const float best = t == 0 ? low : high;
+      const bool live = row < count && size > 0;
+      const __half rounded = __float2half_rn(live ? best : -INFINITY);
+      out[row] = rounded;
+      if (slice_out != nullptr) {
+        const int key = live ? ordered_key16(__half_as_ushort(rounded)) : 0;
+        slice_out->key[row - slice_out->row0] = static_cast<uint16_t>(key);
+        slice_out->size[row - slice_out->row0] = live ? size : 0;
+        if (live) {
+          atomicAdd(&slice_out->hist_mass[key >> 8], size);
+          atomicAdd(&slice_out->hist_count[key >> 8], 1);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+}
+
+// `q_s`: staging area of kStageBytes (>= 16 KB, 128-byte aligned) in shared memory.
+template <int kThreads, int kStageBytes = 2 * 16 * kHeadDim * 4>
 __device__ __forceinline__ void score_groups(const ckv_layer_args& a, int flat, int first_group,
                                              int last_group, float* q_s,
                                              const ScoreSlice* slice_out = nullptr) {
+  if ((a.flags & CKV_FLAG_TENSOR_SCORES) && a.group_size <= 8) {
+    score_groups_mma<kThreads, kStageBytes>(a, flat, first_group, last_group, q_s, slice_out);
+    return;
+  }
   if (a.group_size <= 4) {
     score_groups_impl<kThreads, true>(a, flat, first_group, last_group, q_s, slice_out);
   } else {
@@ -693,8 +844,15 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+constexpr int kClusterStageBytes = 2 * 16 * kHeadDim * 4 + 2 * kDescStash * 4;  // 32 KB
+
 struct ClusterSelectSmem {
-  alignas(16) float query[2 * 16 * kHeadDim];  // staged query group, every value twice
+  // Staging area of the scoring phase (query group as fp32 pairs, or a ring of e4m3
+  // row groups); the descriptor list, which is only written after every CTA of the
+  // cluster has finished scoring, is part of it.
+  alignas(128) float query[2 * 16 * kHeadDim];
+  int32_t desc_comm[kDescStash];  // the complete list, filled by every slice's owner
+  int32_t desc_end[kDescStash];
   uint16_t key[kStash];   // this CTA's slice
   int size[kStash];
   int hist_mass[256];     // slice histograms, read by the other CTAs
@@ -707,9 +865,8 @@ struct ClusterSelectSmem {
   Quad scan_total;
   int stored_equal;       // stored at-threshold communities of all slices (every owner adds here)
   int bin, mass, count, descriptors;
-  int32_t desc_comm[kDescStash];  // the complete list, filled by every slice's owner
-  int32_t desc_end[kDescStash];
 };
+static_assert(offsetof(ClusterSelectSmem, key) == kClusterStageBytes, "staging area must be contiguous");
 
 // Zeroes what scoring accumulates into; call before score_groups, followed by a
 // block barrier (score_groups starts with one).

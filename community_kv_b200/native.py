@@ -161,6 +161,7 @@ FLAG_ATTENTION_ONLY = 2
 FLAG_UPDATE_ONLY = 4
 # ckv_decode_layer: four stand-alone kernels instead of the single cluster launch
 FLAG_UNFUSED = 8
+FLAG_TENSOR_SCORES = 32  # centroid scoring with mma.sync instead of the fixed CUDA-core order
 FLAG_REFERENCE_DIVISION = 16  # centroid mean with the reference kernel's approximate division
 DEV_WAIT_TIMEOUT = 1
 PARTIAL_STRIDE = 132
@@ -251,6 +252,7 @@ __all__ = [
     "FLAG_ATTENTION_ONLY",
     "FLAG_SKIP_UPDATE",
     "FLAG_REFERENCE_DIVISION",
+    "FLAG_TENSOR_SCORES",
     "FLAG_UNFUSED",
     "FLAG_UPDATE_ONLY",
     "LayerArgs",

@@ -232,6 +232,7 @@ def score_centroids(
         graphs=workspace.kv_heads,
         retrieval_to_graph=native.pointer(mapping),
         retrieval_to_kv=native.pointer(mapping),
+        flags=_layout_flags(),
     )
     native.call("ckv_score_centroids", args, native.current_stream(device))
     return workspace.scores
@@ -495,11 +496,15 @@ def _layout_flags() -> int:
     the reference's compiled Triton kernel (approximate ``div.full.f32``) instead of
     like its CPU test helper (IEEE division): the stored e4m3 centroid then matches the
     reference kernel bit for bit also when the exact quotient is a rounding tie.
+    ``CKV_TENSOR_SCORES=1`` scores the centroids on the tensor cores (a score may then
+    differ from the fixed-order one in its last fp16 bit).
     """
 
     flags = native.FLAG_UNFUSED if os.environ.get("CKV_UNFUSED") == "1" else 0
     if os.environ.get("CKV_REFERENCE_DIVISION") == "1":
         flags |= native.FLAG_REFERENCE_DIVISION
+    if os.environ.get("CKV_TENSOR_SCORES") == "1":
+        flags |= native.FLAG_TENSOR_SCORES
     return flags
 
 

@@ -72,6 +72,9 @@ typedef enum ckv_status {
                                      position resolution, no merge); for kernel timing */
 #define CKV_FLAG_UNFUSED 8        /* ckv_decode_layer: run the four stand-alone kernels even when
                                      the single cluster launch is available (same results) */
+#define CKV_FLAG_TENSOR_SCORES 32  /* centroid scoring on the tensor cores (group size <= 8): the 128-long
+                                     dot products are accumulated by mma.m16n8k16 in fp32 instead of in
+                                     the fixed CUDA-core order; a score may differ in its last fp16 bit */
 #define CKV_FLAG_REFERENCE_DIVISION 16 /* running centroid mean (old*n + key)/(n+1): divide with the
                                      GPU's approximate full-range division (div.full.f32, at most 2 ulp
                                      off), which is what the reference's Triton kernel compiles `/` to

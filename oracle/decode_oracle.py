@@ -677,8 +677,16 @@ def decode_layer(
     max_communities: int = 0,
     update: bool = True,
     exact: bool = True,
+    given_scores: torch.Tensor | None = None,
 ) -> LayerResult:
-    """Score, select, attend, assign: the whole per-layer decode transition on CPU."""
+    """Score, select, attend, assign: the whole per-layer decode transition on CPU.
+
+    With ``given_scores`` (fp16 ``[heads, capacity]``) the scoring step is skipped and the
+    selection starts from those scores: that is how a device path whose scores come out
+    of the tensor cores (hardware summation order, last fp16 bit not reproducible here)
+    is checked - its scores against ``score_centroids`` to one unit in the last place,
+    everything downstream bit for bit given its scores.
+    """
 
     heads, capacity, _ = state.centroids.shape
     group = query.shape[0] // heads
@@ -696,15 +704,18 @@ def decode_layer(
     if tile_descriptors is None:
         tile_descriptors = torch.zeros((heads, tile_count), dtype=torch.int32)
 
-    score_centroids(
-        query=query,
-        centroids=state.centroids,
-        community_sizes=state.community_sizes,
-        community_counts=state.community_counts,
-        scores=scores,
-        cover=cover,
-        exact=exact,
-    )
+    if given_scores is not None:
+        scores.copy_(given_scores)
+    else:
+        score_centroids(
+            query=query,
+            centroids=state.centroids,
+            community_sizes=state.community_sizes,
+            community_counts=state.community_counts,
+            scores=scores,
+            cover=cover,
+            exact=exact,
+        )
     select_into_workspace(
         scores=scores,
         community_sizes=state.community_sizes,

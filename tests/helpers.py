@@ -77,6 +77,16 @@ def assert_step_equal(*, selection, attention, update, result: oracle.LayerResul
         assert torch.equal(update.overflow.cpu(), result.overflow), f"{where} overflow"
 
 
+def fp16_ulp_distance(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Distance between fp16 tensors in units in the last place (0 where both are -inf)."""
+
+    def ordered(x):
+        bits = x.view(torch.int16).to(torch.int32) & 0xFFFF
+        return torch.where(bits >= 0x8000, 0xFFFF - bits, bits + 0x8000)
+
+    return (ordered(a) - ordered(b)).abs()
+
+
 class OracleLayer:
     """Persistent CPU twin of one sequence's layer state, stepped by the oracle."""
 
@@ -95,8 +105,19 @@ class OracleLayer:
         self.tiles = torch.zeros((heads, token_budget // 64), dtype=torch.int32)
         self.sinks = torch.arange(num_sink, dtype=torch.int32)
 
-    def step(self, *, query, key, value, softmax_scale, lam, update=True) -> oracle.LayerResult:
+    def exact_scores(self, query) -> torch.Tensor:
+        """Fixed-order fp16 scores of the current state (what the default device path reproduces)."""
+
+        scores = torch.zeros_like(self.scores)
+        oracle.score_centroids(
+            query=query, centroids=self.state.centroids, community_sizes=self.state.community_sizes,
+            community_counts=self.state.community_counts, scores=scores, cover=self.cover,
+        )
+        return scores
+
+    def step(self, *, query, key, value, softmax_scale, lam, update=True, given_scores=None) -> oracle.LayerResult:
         return oracle.decode_layer(
+            given_scores=given_scores,
             query=query,
             key=key,
             value=value,

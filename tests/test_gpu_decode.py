@@ -12,7 +12,7 @@ from community_kv_b200.config import CommunityKVConfig, GraphAggregation
 from community_kv_b200.runtime import DecodeRuntime, convert_prefill_tensors
 from community_kv_b200.state import DecodeLayerWorkspace
 from community_kv_b200.synthetic import make_layer, make_query
-from tests.helpers import OracleLayer, assert_state_equal, assert_step_equal
+from tests.helpers import OracleLayer, assert_state_equal, assert_step_equal, fp16_ulp_distance
 
 pytestmark = pytest.mark.gpu
 SCALE = 128 ** -0.5
@@ -23,7 +23,10 @@ def _cover(converted):
     return [min(capacity, c + converted.decode_capacity) for c in converted.initial_community_counts]
 
 
-def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None):
+def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, tensor_scores=False):
+    """``tensor_scores``: the device scores come from the tensor cores; they are checked against the
+    fixed-order scores to one fp16 unit in the last place and everything after them bit for bit."""
+
     device = torch.device("cuda", 0)
     runtime = DecodeRuntime(config, splits=splits)
     state = runtime.prepare_layer(0, **layer.to(device).prepare_kwargs())
@@ -47,8 +50,17 @@ def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None):
             softmax_scale=SCALE,
         )
         assert out.shape == (1, 1, layer.query_heads, 128)
-        want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=config.lam)
         where = f"step {step}"
+        given = None
+        if tensor_scores:
+            given = state.workspace.selection.scores.detach().cpu().clone()
+            exact = twin.exact_scores(query)
+            covered = torch.arange(given.shape[1])[None, :] < torch.tensor(twin.cover)[:, None]
+            distance = fp16_ulp_distance(given, exact)[covered]
+            assert int(distance.max()) <= 1, f"{where}: tensor-core score {int(distance.max())} ulp off"
+            assert float((distance > 0).float().mean()) < 5e-3, where
+        want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=config.lam,
+                         given_scores=given)
         assert_step_equal(
             selection=state.workspace.selection,
             attention=state.workspace.attention,
@@ -80,6 +92,22 @@ def test_unfused_kernels_give_the_same_result(monkeypatch):
     layer = make_layer(seed=0, seq_len=8192, communities=64, max_decode_tokens=8, aggregation="query_group")
     config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation="query_group")
     _run_sequence(layer, config, steps=4, seed=100)
+
+
+@pytest.mark.parametrize("unfused", [False, True])
+def test_tensor_core_scores(monkeypatch, unfused):
+    """Scoring on the tensor cores (single cluster launch and the stand-alone kernels): scores within one
+    fp16 unit in the last place of the fixed-order ones, the rest of the step exact given those scores."""
+
+    monkeypatch.setenv("CKV_TENSOR_SCORES", "1")
+    if unfused:
+        monkeypatch.setenv("CKV_UNFUSED", "1")
+    layer = make_layer(seed=11, seq_len=16384, communities=700, max_decode_tokens=8, zipf_exponent=1.1)
+    config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation="query_group")
+    _run_sequence(layer, config, steps=6, seed=1100, tensor_scores=True)
+    layer = make_layer(seed=12, kv_heads=2, group_size=8, seq_len=4096, communities=100, max_decode_tokens=4)
+    config = CommunityKVConfig(token_budget=512, num_sink=4, lam=0.5, aggregation="query_group")
+    _run_sequence(layer, config, steps=3, seed=1200, tensor_scores=True, splits=3)
 
 
 def test_many_small_communities_and_delta_chains():
