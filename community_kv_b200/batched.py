@@ -54,6 +54,7 @@ class BatchedLayerState:
     token_budget: int
     args: native.LayerArgs | None = None
     cache_key: tuple | None = None
+    update_done: object = None  # deferred update: event of the layer's last online assignment
 
     def sequence_view(self, index: int) -> tuple[PrefillCSR, MutableGraphState, torch.Tensor]:
         """Reference-shaped views (no copy) of one sequence slot."""
@@ -174,10 +175,17 @@ def stack_sequences(
 class BatchedDecodeRuntime:
     """Per-layer batched states; ``decode`` is one CUDA-library call per layer and step."""
 
-    def __init__(self, config: CommunityKVConfig, *, splits: int | None = None) -> None:
+    def __init__(self, config: CommunityKVConfig, *, splits: int | None = None,
+                 defer_update: bool = False) -> None:
         self.config = config
         self.splits = splits
+        self.defer_update = defer_update  # see ops.DeferredUpdate
+        self._deferred: ops.DeferredUpdate | None = None
         self.layers: dict[int, BatchedLayerState] = {}
+
+    def synchronize_updates(self) -> None:
+        if self._deferred is not None:
+            self._deferred.synchronize()
 
     def install(self, layer_idx: int, state: BatchedLayerState) -> BatchedLayerState:
         if layer_idx in self.layers:
@@ -249,10 +257,17 @@ class BatchedDecodeRuntime:
         if not query.is_contiguous():
             query = query.contiguous()
         args = self.pack(layer_idx, query=query, key=key, value=value, softmax_scale=softmax_scale)
-        native.call("ckv_decode_layer", args, native.current_stream(query.device))
+        if self.defer_update:
+            if self._deferred is None:
+                self._deferred = ops.DeferredUpdate(query.device)
+            layer = self.layers[layer_idx]
+            layer.update_done = self._deferred.launch(args, pending=layer.update_done)
+        else:
+            native.call("ckv_decode_layer", args, native.current_stream(query.device))
         return self.layers[layer_idx].workspace.attention.output
 
     def assert_no_overflow(self) -> None:
+        self.synchronize_updates()
         failures = {}
         for layer_idx, layer in self.layers.items():
             if int(torch.count_nonzero(layer.workspace.update.overflow)):

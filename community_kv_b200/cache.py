@@ -2,7 +2,9 @@
 
 Same behaviour as the reference's ``community_kv/attention/cache.py:9-121``:
 prefill appends with a host cursor; after ``enable_device_updates`` the cursor
-lives on the device so that decode steps have no host round trip.
+lives on the device so that decode steps have no host round trip.  A decode step's
+single new row goes in through one ``ckv_append_kv`` launch that reads the device
+cursor itself (the reference runs ``arange`` + two ``index_copy_``, ``cache.py:39-47``).
 """
 
 from __future__ import annotations
@@ -29,6 +31,13 @@ class StaticCacheLayer(StaticLayer):
             self.lazy_initialization(key_states, value_states)
         count = key_states.shape[-2]
         if self.device_updates:
+            if count == 1 and key_states.is_cuda and self.keys.is_contiguous() and self.values.is_contiguous():
+                from community_kv_b200 import ops
+
+                ops.append_kv(self.keys, self.values, key_states[..., 0, :], value_states[..., 0, :],
+                              self.cumulative_length)
+                self.cumulative_length.add_(1)
+                return self.keys, self.values
             rows = torch.arange(count, device=self.device) + self.cumulative_length
             self.cumulative_length.add_(count)
             self.keys.index_copy_(2, rows, key_states)

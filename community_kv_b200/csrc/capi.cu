@@ -9,8 +9,8 @@ cudaError_t launch_resolve(const ckv_layer_args& a, cudaStream_t stream);
 cudaError_t launch_attention(const ckv_layer_args& a, cudaStream_t stream);
 cudaError_t launch_merge_update(const ckv_layer_args& a, cudaStream_t stream);
 cudaError_t launch_append_kv(void* key_cache, void* value_cache, const void* new_key, const void* new_value,
-                             int64_t units, int64_t unit_stride, const int32_t* row_index, int64_t row,
-                             cudaStream_t stream);
+                             int64_t units, int64_t unit_stride, const int32_t* row_index,
+                             int64_t row_index_stride, int64_t row, cudaStream_t stream);
 cudaError_t launch_wait_peers(uint32_t* flag, uint32_t expected, uint32_t* status, cudaStream_t stream);
 bool fused_layer_supported(const ckv_layer_args& a);
 cudaError_t launch_fused_layer(const ckv_layer_args& a, cudaStream_t stream);
@@ -183,16 +183,18 @@ int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream) {
 }
 
 int ckv_append_kv(void* key_cache, void* value_cache, const void* new_key, const void* new_value,
-                  int64_t units, int64_t unit_stride, const int32_t* row_index, int64_t row,
-                  void* cuda_stream) {
+                  int64_t units, int64_t unit_stride, const int32_t* row_index,
+                  int64_t row_index_stride, int64_t row, void* cuda_stream) {
   if (!key_cache || !value_cache || !new_key || !new_value) return CKV_ERR_NULL;
   if (units <= 0 || unit_stride <= 0 || (row_index == nullptr && row < 0)) return CKV_ERR_SHAPE;
+  if (row_index != nullptr && row_index_stride != 0 && row_index_stride != 1) return CKV_ERR_SHAPE;
   if (unit_stride % 8 || ((reinterpret_cast<uintptr_t>(key_cache) | reinterpret_cast<uintptr_t>(value_cache) |
                            reinterpret_cast<uintptr_t>(new_key) | reinterpret_cast<uintptr_t>(new_value)) & 15u)) {
     return CKV_ERR_ALIGN;
   }
   return ckv::launched(ckv::launch_append_kv(key_cache, value_cache, new_key, new_value, units, unit_stride,
-                                             row_index, row, static_cast<cudaStream_t>(cuda_stream)));
+                                             row_index, row_index_stride, row,
+                                             static_cast<cudaStream_t>(cuda_stream)));
 }
 
 int ckv_wait_peers(uint32_t* flag, uint32_t expected, uint32_t* status, void* cuda_stream) {

@@ -68,13 +68,14 @@ __global__ void __launch_bounds__(kMergeThreads) sync_shared_kernel(const ckv_la
 __global__ void __launch_bounds__(128) append_kv_kernel(uint4* key_cache, uint4* value_cache,
                                                         const uint4* new_key, const uint4* new_value,
                                                         int64_t units, int64_t unit_stride_vec,
-                                                        const int32_t* row_index, int64_t row) {
+                                                        const int32_t* row_index, int64_t row_index_stride,
+                                                        int64_t row) {
   const int64_t unit = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   if (unit >= units) {
     return;
   }
   const int lane = threadIdx.x & 31;
-  const int64_t target = row_index != nullptr ? row_index[unit] : row;
+  const int64_t target = row_index != nullptr ? row_index[unit * row_index_stride] : row;
   if (target < 0) {
     return;
   }
@@ -85,11 +86,11 @@ __global__ void __launch_bounds__(128) append_kv_kernel(uint4* key_cache, uint4*
 }
 
 cudaError_t launch_append_kv(void* key_cache, void* value_cache, const void* new_key, const void* new_value,
-                             int64_t units, int64_t unit_stride, const int32_t* row_index, int64_t row,
-                             cudaStream_t stream) {
+                             int64_t units, int64_t unit_stride, const int32_t* row_index,
+                             int64_t row_index_stride, int64_t row, cudaStream_t stream) {
   append_kv_kernel<<<static_cast<unsigned>((units + 3) / 4), 128, 0, stream>>>(
       static_cast<uint4*>(key_cache), static_cast<uint4*>(value_cache), static_cast<const uint4*>(new_key),
-      static_cast<const uint4*>(new_value), units, unit_stride / 8, row_index, row);
+      static_cast<const uint4*>(new_value), units, unit_stride / 8, row_index, row_index_stride, row);
   return cudaGetLastError();
 }
 

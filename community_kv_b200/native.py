@@ -215,7 +215,7 @@ def library() -> ctypes.CDLL:
     lib.ckv_decode_layer_kernels.argtypes = [ctypes.POINTER(LayerArgs)]
     lib.ckv_append_kv.restype = ctypes.c_int
     lib.ckv_append_kv.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p,
-                                  ctypes.c_int64, ctypes.c_void_p]
+                                  ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]
     lib.ckv_wait_peers.restype = ctypes.c_int
     lib.ckv_wait_peers.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p]
     lib.ckv_prefill_topk.restype = ctypes.c_int

@@ -590,6 +590,52 @@ def decode_layer(
     )
 
 
+class DeferredUpdate:
+    """Runs the online graph update of a layer beside whatever follows its attention.
+
+    Nothing downstream of a layer's attention output depends on that layer's online
+    assignment (labels, sizes, centroid, delta chains): only the SAME layer's next decode
+    step does.  ``launch`` therefore enqueues the layer's attention
+    (``ckv_decode_layer`` with ``CKV_FLAG_SKIP_UPDATE``: scores, selection, attention,
+    merged outputs, log-sum-exp and the eight neighbour candidates) on the caller's
+    stream and the assignment (``ckv_online_update``) on a second stream, ordered after
+    the attention by an event; the returned event marks the update as done and must be
+    handed back as ``pending`` for the layer's next step.  Results are identical to the
+    single call.  The split also works under CUDA-graph stream capture, where it becomes
+    a side branch of the graph.
+    """
+
+    def __init__(self, device: torch.device) -> None:
+        self.stream = torch.cuda.Stream(device)
+
+    def launch(
+        self,
+        args: native.LayerArgs,
+        *,
+        pending: "torch.cuda.Event | None" = None,
+    ) -> "torch.cuda.Event":
+        device = self.stream.device
+        main = torch.cuda.current_stream(device)
+        if pending is not None:
+            main.wait_event(pending)
+        attend = native.LayerArgs.from_buffer_copy(args)
+        attend.flags |= native.FLAG_SKIP_UPDATE
+        native.call("ckv_decode_layer", attend, main.cuda_stream)
+        attended = torch.cuda.Event()
+        attended.record(main)
+        self.stream.wait_event(attended)
+        update = native.LayerArgs.from_buffer_copy(args)
+        update.peer_count = 0          # the head outputs were already stored by the attention call
+        update.peer_wait_flag = None
+        native.call("ckv_online_update", update, self.stream.cuda_stream)
+        done = torch.cuda.Event()
+        done.record(self.stream)
+        return done
+
+    def synchronize(self) -> None:
+        self.stream.synchronize()
+
+
 def append_kv(
     key_cache: torch.Tensor,
     value_cache: torch.Tensor,
@@ -600,8 +646,9 @@ def append_kv(
     """``cache[..., row, :] = new[..., :]`` for both caches in one small launch.
 
     The caches are bf16 ``[..., rows, 128]`` (contiguous), the new rows bf16 ``[..., 128]``
-    with the same leading shape; ``row`` is one index for all of them or an int32 tensor
-    with one index per leading entry (negative: skip).
+    with the same leading shape; ``row`` is one index for all of them, an int32 tensor
+    with one element (a device-side cursor shared by all of them, read by the kernel: no
+    host round trip), or an int32 tensor with one index per leading entry (negative: skip).
     """
 
     if key_cache.shape != value_cache.shape or new_key.shape != new_value.shape:
@@ -615,16 +662,18 @@ def append_kv(
     device = _require_cuda(key_cache, value_cache, new_key, new_value)
     units = new_key.numel() // HEAD_DIM
     index = None
+    stride = 0
     if isinstance(row, torch.Tensor):
-        if row.dtype != torch.int32 or row.numel() != units:
-            raise ValueError("row must be int32 with one entry per cache row to write")
+        if row.dtype != torch.int32 or row.numel() not in (1, units) or row.device != device:
+            raise ValueError("row must be an int32 device tensor with one entry, or one per cache row to write")
         index = row.contiguous()
+        stride = 0 if row.numel() == 1 else 1
     elif not 0 <= int(row) < key_cache.shape[-2]:
         raise ValueError("row is outside the cache")
     keep = (new_key.contiguous(), new_value.contiguous())
     status = native.library().ckv_append_kv(
         key_cache.data_ptr(), value_cache.data_ptr(), keep[0].data_ptr(), keep[1].data_ptr(), units,
-        key_cache.shape[-2] * HEAD_DIM, native.pointer(index), 0 if index is not None else int(row),
+        key_cache.shape[-2] * HEAD_DIM, native.pointer(index), stride, 0 if index is not None else int(row),
         native.current_stream(device),
     )
     if status:
@@ -632,6 +681,7 @@ def append_kv(
 
 
 __all__ = [
+    "DeferredUpdate",
     "append_kv",
     "build_layer_args",
     "decode_layer",

@@ -67,6 +67,7 @@ class DecodeLayerState:
     sink_positions: torch.Tensor
     args: native.LayerArgs | None = None
     cache_key: tuple[int, ...] | None = None
+    update_done: Any = None  # deferred update: event of the layer's last online assignment
 
 
 def _pad_member_offsets(member_offsets: torch.Tensor, *, community_capacity: int) -> torch.Tensor:
@@ -213,13 +214,26 @@ def convert_prefill_tensors(
 class DecodeRuntime:
     """Fixed-address per-layer decode states; one CUDA-library call per layer and token."""
 
-    def __init__(self, config: CommunityKVConfig, *, splits: int | None = None) -> None:
+    def __init__(self, config: CommunityKVConfig, *, splits: int | None = None,
+                 defer_update: bool = False) -> None:
+        """``defer_update``: run each layer's online assignment on a second stream beside the
+        work that follows the layer's attention (see ``ops.DeferredUpdate``); same results."""
+
         self.config = config
         self.splits = splits
+        self.defer_update = defer_update
+        self._deferred: ops.DeferredUpdate | None = None
         self.layers: dict[int, DecodeLayerState] = {}
 
     def reset(self) -> None:
+        self.synchronize_updates()
         self.layers.clear()
+
+    def synchronize_updates(self) -> None:
+        """Wait for deferred online assignments (before the graph state is read on the host)."""
+
+        if self._deferred is not None:
+            self._deferred.synchronize()
 
     def prepare_partitioned_layer(self, state: Any) -> DecodeLayerState:
         """Install a partitioned layer (any object with the reference's ``PartitionedLayer`` fields)."""
@@ -321,10 +335,16 @@ class DecodeRuntime:
             )
             layer.cache_key = cache_key
         layer.args.query = flat_query.data_ptr()
-        native.call("ckv_decode_layer", layer.args, native.current_stream(query.device))
+        if self.defer_update:
+            if self._deferred is None:
+                self._deferred = ops.DeferredUpdate(query.device)
+            layer.update_done = self._deferred.launch(layer.args, pending=layer.update_done)
+        else:
+            native.call("ckv_decode_layer", layer.args, native.current_stream(query.device))
         return layer.workspace.attention.output.view(1, 1, heads, HEAD_DIM)
 
     def assert_no_overflow(self) -> None:
+        self.synchronize_updates()
         failures = {}
         for layer_idx, layer in self.layers.items():
             flags = layer.workspace.update.overflow
@@ -490,7 +510,9 @@ class CommunityKVRuntime:
         )
 
         def option(name: str, default: Any) -> Any:
-            return kwargs[name] if name in kwargs else getattr(generation_config, name, default)
+            # an unset generation option reads as None in recent transformers releases
+            value = kwargs[name] if name in kwargs else getattr(generation_config, name, default)
+            return default if value is None else value
 
         if option("num_beams", 1) != 1:
             raise ValueError("CommunityKV generate does not support beam search")

@@ -179,6 +179,89 @@ def make_layer(
     )
 
 
+@dataclass(slots=True)
+class SyntheticPartitionedLayer:
+    """What ``DecodeRuntime.prepare_partitioned_layer`` reads (the reference's ``PartitionedLayer``
+    fields, community_kv/graph/partition.py:30-68)."""
+
+    layer_idx: int
+    member_offsets: torch.Tensor
+    member_positions: torch.Tensor
+    community_counts: torch.Tensor
+    centroids: torch.Tensor
+    community_sizes: torch.Tensor
+    community_weight: torch.Tensor
+    total_weight: torch.Tensor
+    token_communities: torch.Tensor
+    retrieval_to_graph: torch.Tensor
+    retrieval_to_kv: torch.Tensor
+    prefill_seq_len: int
+    query_heads: int
+    kv_heads: int
+    aggregation: GraphAggregation
+
+
+class SyntheticPartitioner:
+    """Stand-in for the host-side Leiden partitioner: random labels with Zipf-sized communities.
+
+    Callable with the keyword arguments ``CommunityKVRuntime.submit_prefill_layer`` passes
+    to its ``partitioner``.  The neighbour edges are accepted and ignored: the labels are
+    drawn per (layer, graph) from a seeded generator, ``communities`` per graph with sizes
+    proportional to ``rank ** -zipf_exponent`` (or equal sizes of contiguous position blocks
+    with ``zipf_exponent=None``), and the decode state is assembled from them with the same
+    layout rules as a real partition (``community_kv_b200.assembly``).  For benchmarks and
+    tests that need a whole model running through the plug-in without a graph partitioner.
+    """
+
+    def __init__(self, *, communities: int, zipf_exponent: float | None = 1.1, seed: int = 0) -> None:
+        if communities <= 0:
+            raise ValueError("communities must be positive")
+        self.communities = communities
+        self.zipf_exponent = zipf_exponent
+        self.seed = seed
+        self.edges_seen: dict[int, tuple[int, ...]] = {}
+
+    def __call__(self, *, layer_idx: int, topk_indices: torch.Tensor, topk_scores: torch.Tensor,
+                 keys: torch.Tensor, num_sink: int, max_decode_tokens: int,
+                 aggregation: GraphAggregation | str, **_: object) -> SyntheticPartitionedLayer:
+        aggregation = GraphAggregation(aggregation)
+        kv_heads, length, _dim = keys.shape
+        query_heads = int(topk_indices.shape[0])
+        self.edges_seen[layer_idx] = tuple(topk_indices.shape)
+        graphs = aggregation.graph_count(query_heads=query_heads, kv_heads=kv_heads)
+        count = min(self.communities, max(1, length - num_sink))
+        labels = torch.empty((graphs, length), dtype=torch.int64)
+        for graph in range(graphs):
+            generator = torch.Generator().manual_seed((self.seed * 1000003 + layer_idx) * 4099 + graph)
+            if self.zipf_exponent is None:
+                ids = (torch.arange(length) * count) // length
+            else:
+                sizes = zipf_sizes(length, count, self.zipf_exponent, generator)
+                ids = torch.repeat_interleave(torch.arange(count), sizes)[torch.randperm(length, generator=generator)]
+            labels[graph] = ids
+        assembled = assemble_layer(
+            labels.to(torch.int32).to(keys.device), keys, aggregation=aggregation, query_heads=query_heads,
+            num_sink=num_sink, max_decode_tokens=max_decode_tokens,
+        )
+        return SyntheticPartitionedLayer(
+            layer_idx=layer_idx,
+            member_offsets=assembled.member_offsets,
+            member_positions=assembled.member_positions,
+            community_counts=assembled.num_communities,
+            centroids=assembled.centroids,
+            community_sizes=assembled.community_sizes,
+            community_weight=assembled.community_weight,
+            total_weight=assembled.total_weight,
+            token_communities=assembled.token_communities,
+            retrieval_to_graph=assembled.retrieval_to_graph,
+            retrieval_to_kv=assembled.retrieval_to_kv,
+            prefill_seq_len=length,
+            query_heads=query_heads,
+            kv_heads=kv_heads,
+            aggregation=aggregation,
+        )
+
+
 def make_query(*, seed: int, query_heads: int, integer_valued: bool = False) -> torch.Tensor:
     generator = torch.Generator().manual_seed(seed)
     if integer_valued:
@@ -186,4 +269,5 @@ def make_query(*, seed: int, query_heads: int, integer_valued: bool = False) -> 
     return torch.randn((query_heads, HEAD_DIM), generator=generator).to(torch.bfloat16)
 
 
-__all__ = ["SyntheticLayer", "make_layer", "make_query", "zipf_sizes"]
+__all__ = ["SyntheticLayer", "SyntheticPartitionedLayer", "SyntheticPartitioner", "make_layer", "make_query",
+           "zipf_sizes"]

@@ -257,12 +257,14 @@ int ckv_decode_layer(const ckv_layer_args* args, void* cuda_stream);
 /* Writes the decoded token's K and V rows into the caches: cache[u, row, :] = new[u, :]
  * for u < units, where the caches are bf16 [units, rows, 128] with `unit_stride`
  * elements between units and the new rows are contiguous bf16 [units, 128].  The row
- * is `row_index[u]` when row_index is given (int32, device) and `row` otherwise.  One
- * small launch instead of a strided tensor copy per cache (the reference goes through
- * the Hugging Face cache's index_copy_, community_kv/cache.py). */
+ * is `row_index[u * row_index_stride]` when row_index is given (int32, device;
+ * stride 0: one device-side cursor shared by all units, stride 1: one row per unit;
+ * a negative row skips the unit) and `row` otherwise.  One small launch instead of the
+ * arange + two index_copy_ calls of the reference's cache layer
+ * (community_kv/attention/cache.py:39-47). */
 int ckv_append_kv(void* key_cache, void* value_cache, const void* new_key, const void* new_value,
-                  int64_t units, int64_t unit_stride, const int32_t* row_index, int64_t row,
-                  void* cuda_stream);
+                  int64_t units, int64_t unit_stride, const int32_t* row_index,
+                  int64_t row_index_stride, int64_t row, void* cuda_stream);
 
 /* Waits (on the stream, in a one-thread kernel with a bounded number of polls)
  * until *flag >= expected, then subtracts `expected` from it.  `flag` is this GPU's

@@ -23,12 +23,13 @@ def _cover(converted):
     return [min(capacity, c + converted.decode_capacity) for c in converted.initial_community_counts]
 
 
-def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, tensor_scores=False):
+def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, tensor_scores=False,
+                  defer_update=False):
     """``tensor_scores``: the device scores come from the tensor cores; they are checked against the
     fixed-order scores to one fp16 unit in the last place and everything after them bit for bit."""
 
     device = torch.device("cuda", 0)
-    runtime = DecodeRuntime(config, splits=splits)
+    runtime = DecodeRuntime(config, splits=splits, defer_update=defer_update)
     state = runtime.prepare_layer(0, **layer.to(device).prepare_kwargs())
     twin = OracleLayer(
         state.converted.csr,
@@ -50,6 +51,7 @@ def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, ten
             softmax_scale=SCALE,
         )
         assert out.shape == (1, 1, layer.query_heads, 128)
+        runtime.synchronize_updates()
         where = f"step {step}"
         given = None
         if tensor_scores:
@@ -108,6 +110,16 @@ def test_tensor_core_scores(monkeypatch, unfused):
     layer = make_layer(seed=12, kv_heads=2, group_size=8, seq_len=4096, communities=100, max_decode_tokens=4)
     config = CommunityKVConfig(token_budget=512, num_sink=4, lam=0.5, aggregation="query_group")
     _run_sequence(layer, config, steps=3, seed=1200, tensor_scores=True, splits=3)
+
+
+@pytest.mark.parametrize("aggregation", [GraphAggregation.QUERY_GROUP, GraphAggregation.LAYER_WISE])
+def test_deferred_update_gives_the_same_result(aggregation):
+    """Attention on the caller's stream, online assignment on a second stream: same step, same state."""
+
+    layer = make_layer(seed=21, seq_len=8192, communities=200, max_decode_tokens=10, aggregation=aggregation,
+                       zipf_exponent=1.1)
+    config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation=aggregation)
+    _run_sequence(layer, config, steps=8, seed=2100, defer_update=True)
 
 
 def test_many_small_communities_and_delta_chains():
