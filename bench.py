@@ -73,9 +73,16 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--update", choices=["inline", "deferred"], default="inline",
                         help="online graph update inside the layer launch (inline), or as its own launch on a "
                              "second stream that runs beside the next layer's launch (deferred)")
+    parser.add_argument("--scaling", choices=["weak", "strong"], default="weak",
+                        help="weak: --batch-per-gpu sequences per GPU (8N in all); strong: 16 sequences in all, "
+                             "the stated batch of the long-context configuration, whatever N (needs N >= 2)")
     parser.add_argument("--sweep-context", type=int, default=1_048_576)
-    parser.add_argument("--workload", choices=["decode", "prefill", "sweep"], default="decode",
-                        help="prefill: the score-graph emission kernel at S=16384 (a second, separate line)")
+    parser.add_argument("--workload", choices=["decode", "prefill", "sweep", "model"], default="decode",
+                        help="prefill: the score-graph emission kernel at S=16384 (a second, separate line); "
+                             "model: a random-init Qwen3-8B-shaped decoder driven through the Hugging Face plug-in")
+    parser.add_argument("--prompt-length", type=int, default=32768)
+    parser.add_argument("--new-tokens", type=int, default=128)
+    parser.add_argument("--model-layers", type=int, default=36)
     parser.add_argument("--prefill-length", type=int, default=16384)
     return parser.parse_args()
 
@@ -186,12 +193,12 @@ def run_reference(args: argparse.Namespace) -> None:
         "warmup": args.warmup,
         "ms_per_step": 1000.0 / value,
         "higher_is_better": True,
-        "scaling": "weak",
+        "scaling": args.scaling,
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic",
         "config": workload_config(
-            args, batch=(args.batch_per_gpu or 8) * args.gpus, world=args.gpus,
+            args, batch=16 if args.scaling == "strong" else (args.batch_per_gpu or 8) * args.gpus, world=args.gpus,
             exchange_mode=default_exchange_mode(args, args.gpus),
         ),
         "cpu_baseline": {**last, "value": value},
@@ -346,8 +353,13 @@ def run_b200(args: argparse.Namespace) -> None:
         dist.init_process_group("nccl", device_id=device)
     heads_local = KV_HEADS // world
     query_local = heads_local * (QUERY_HEADS // KV_HEADS)
-    per_gpu = pick_batch(args.batch_per_gpu, args, KV_HEADS, torch)
-    batch = per_gpu * world
+    if args.scaling == "strong":
+        if world < 2:
+            raise SystemExit("--scaling strong keeps 16 sequences in all: that needs at least two GPUs")
+        batch = 16
+    else:
+        per_gpu = pick_batch(args.batch_per_gpu, args, KV_HEADS, torch)
+        batch = per_gpu * world
     total_steps = args.warmup + args.steps
     e2e_steps = max(3, min(args.steps, 10))
     extra_steps = 4 + e2e_steps + 3 + 4  # e2e steps, three event-timed passes, one phase-stamped pass
@@ -586,10 +598,11 @@ def run_b200(args: argparse.Namespace) -> None:
     # ---- end to end: host queries and new K/V rows in, head outputs out, every step ----
     pinned_q = torch.randn((e2e_steps, launches, slots, query_local, HEAD_DIM)).to(torch.bfloat16).pin_memory()
     pinned_kv = (torch.randn((e2e_steps, 2, launches, slots, heads_local, HEAD_DIM)) * SCALE).to(torch.bfloat16).pin_memory()
-    pinned_out = torch.empty((launches, world, slots, query_local, HEAD_DIM), dtype=torch.bfloat16).pin_memory()
+    # every rank reads back the head outputs it computed (together the ranks read the whole result once)
+    pinned_out = torch.empty((launches, slots, query_local, HEAD_DIM), dtype=torch.bfloat16).pin_memory()
     new_kv = torch.empty((2, launches, slots, heads_local, HEAD_DIM), dtype=torch.bfloat16, device=device)
     cursor = int(work.state(0).current_position.max())
-    result = out_full if world > 1 else out_local
+    result = exchange.gathered[:, rank] if exchange is not None else out_local
     barrier()
     e2e_begin, e2e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
@@ -599,7 +612,7 @@ def run_b200(args: argparse.Namespace) -> None:
             new_kv.copy_(pinned_kv[step], non_blocking=True)
             ops.append_kv(work.key, work.value, new_kv[0], new_kv[1], cursor + step)
             run_step()
-            pinned_out.view(result.shape).copy_(result, non_blocking=True)
+            pinned_out.copy_(result, non_blocking=True)
             stream.synchronize()  # the caller reads the step's output before the next token
         e2e_end.record()
     barrier()
@@ -641,7 +654,7 @@ def run_b200(args: argparse.Namespace) -> None:
         "ms_per_step": ms_per_step,
         "us_per_step": ms_per_step * 1e3,
         "higher_is_better": True,
-        "scaling": "weak",
+        "scaling": args.scaling,
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic",
@@ -934,8 +947,126 @@ def run_sweep(args: argparse.Namespace) -> None:
     finish(world, dist)
 
 
+def run_model(args: argparse.Namespace) -> None:
+    """Whole-model decode behind the Hugging Face plug-in: a random-init Qwen3-8B-shaped decoder
+    (36 layers, hidden 4096, 32/8 heads, head_dim 128, FFN 12288, vocab 151936, bf16), batch 1, a prompt of
+    uniform-random token ids, greedy generation.  512 communities per (layer, KV head) with Zipf(1.1) sizes from
+    the synthetic partitioner, budget 2048.  Reports whole-step tokens/s (Hugging Face eager loop: projections,
+    MLP, norms, sampling and Python included) and, separately, the attention path (CUDA events around every
+    decode-layer call)."""
+
+    import torch
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+
+    from community_kv_b200 import CommunityKVAttention, CommunityKVConfig, CommunityKVRuntime, PartitionConfig
+    from community_kv_b200.synthetic import SyntheticPartitioner
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    layers = args.model_layers
+    config = Qwen3Config(
+        hidden_size=4096, intermediate_size=12288, num_hidden_layers=layers, num_attention_heads=QUERY_HEADS,
+        num_key_value_heads=KV_HEADS, head_dim=HEAD_DIM, vocab_size=151936,
+        max_position_embeddings=args.prompt_length + args.new_tokens + 8, tie_word_embeddings=False,
+    )
+    torch.manual_seed(args.seed)
+    build_begin = time.perf_counter()
+    with torch.device(device):
+        previous = torch.get_default_dtype()
+        torch.set_default_dtype(torch.bfloat16)
+        try:
+            model = Qwen3ForCausalLM(config).eval()
+        finally:
+            torch.set_default_dtype(previous)
+    build_seconds = time.perf_counter() - build_begin
+    generator = torch.Generator().manual_seed(args.seed)
+    prompt = torch.randint(0, config.vocab_size, (1, args.prompt_length), generator=generator).to(device)
+    ckv = CommunityKVConfig(token_budget=BUDGET, num_sink=NUM_SINK, lam=0.5, aggregation="query_group")
+    partitioner = SyntheticPartitioner(communities=512, zipf_exponent=ZIPF, seed=args.seed)
+    sampler = ClockSampler(device.index or 0)
+    with CommunityKVRuntime(config=ckv, partition=PartitionConfig(), num_layers=layers,
+                            max_decode_tokens=args.new_tokens, partitioner=partitioner) as runtime:
+        model.config._attn_implementation = CommunityKVAttention(runtime).register()
+        decode = runtime.decode_runtime.decode
+        spans: list[tuple] = []
+
+        def timed_decode(**kwargs):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            out = decode(**kwargs)
+            end.record()
+            spans.append((begin, end))
+            return out
+
+        runtime.decode_runtime.decode = timed_decode
+        first_decode = {}
+        ensure_ready = runtime.ensure_ready
+
+        def mark_ready():
+            if "t" not in first_decode:
+                torch.cuda.synchronize()
+                first_decode["t"] = time.perf_counter()
+            ensure_ready()
+
+        runtime.ensure_ready = mark_ready
+        sampler.start()
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        with torch.no_grad():
+            output = runtime.generate(model, prompt, max_new_tokens=args.new_tokens)
+        torch.cuda.synchronize()
+        end = time.perf_counter()
+        clocks = sampler.stop()
+    decode_tokens = args.new_tokens - 1
+    decode_seconds = end - first_decode["t"]
+    attention_ms = sum(a.elapsed_time(b) for a, b in spans)
+    per_token_attention_ms = attention_ms / max(decode_tokens, 1)
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_path.read_text())["hbm_gbs"]) if peaks_path.exists() else 6650.0
+    bytes_per_token = layers * KV_HEADS * (512 * HEAD_DIM + 2 * BUDGET * HEAD_DIM * 2)
+    line = {
+        "metric": "whole-model sparse decode tokens/s behind the Hugging Face plug-in (batch 1)",
+        "value": decode_tokens / decode_seconds,
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": decode_tokens,
+        "warmup": 0,
+        "ms_per_step": 1e3 * decode_seconds / max(decode_tokens, 1),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {
+            "workload": f"random-init Qwen3-8B-shaped decoder ({layers} layers, hidden 4096, 32/8 heads, FFN 12288, "
+                        f"vocab 151936), batch 1, prompt {args.prompt_length} random ids, {args.new_tokens} new tokens, "
+                        f"512 Zipf({ZIPF}) communities per (layer, KV head), budget {BUDGET}",
+            "loop": "Hugging Face generate, eager (no CUDA graph): projections, MLP, norms and sampling included",
+        },
+        "prefill_seconds": first_decode["t"] - begin,
+        "attention_path": {
+            "ms_per_token": per_token_attention_ms,
+            "us_per_layer_call": 1e3 * attention_ms / max(len(spans), 1),
+            "calls": len(spans),
+            "algorithmic_bytes_per_token": bytes_per_token,
+            "achieved_gbs": bytes_per_token / (per_token_attention_ms * 1e-3) / 1e9,
+            "frac_of_hbm_peak": bytes_per_token / (per_token_attention_ms * 1e-3) / 1e9 / peak,
+            "note": "CUDA events around every decode-layer call (one launch each); one sequence gives a launch "
+                    "only 8 units, so this is the latency of the phase chain, not a bandwidth figure",
+        },
+        "generated": int(output.shape[-1] - args.prompt_length),
+        "gpu_launches": len(spans),
+        "clocks": clocks,
+        "build_seconds": build_seconds,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     args = parse_args()
+    if args.workload == "model" and args.impl != "reference":
+        run_model(args)
+        return
     if args.workload == "prefill" and args.impl != "reference":
         run_prefill(args)
         return

@@ -263,24 +263,25 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
   }
   __syncthreads();
   if (a.peer_count > 0 && threadIdx.x == 0 && !update_only) {
-    // all output rows of this unit were stored before the barrier: publish them
-    __threadfence_system();
+    // All output rows of this unit were stored before the barrier.  With a local counter
+    // (peer_done) a unit only has to order its stores before its count at GPU scope; the
+    // last unit of the call, which has observed every other unit's count, then issues ONE
+    // system-scope fence (fences are cumulative: it covers the other units' stores too)
+    // and signals every peer with relaxed remote adds, which it does not wait for.
     bool signal = true;
     if (a.peer_done != nullptr) {
-      // units count themselves locally; the last one of the call speaks for all
-      // (every unit fenced its stores before counting, the last one fences again
-      // before it signals: the fences are cumulative)
+      __threadfence();
       const uint32_t units = static_cast<uint32_t>(a.batch * a.retrieval_heads);
       const uint32_t before = atomicAdd(a.peer_done, 1u);
       signal = before == units - 1;
       if (signal) {
         atomicExch(a.peer_done, 0u);
-        __threadfence_system();
       }
     }
     if (signal) {
+      __threadfence_system();
       for (int p = 0; p < a.peer_count; ++p) {
-        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.peer_flag[p]) : "memory");
+        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(a.peer_flag[p]) : "memory");
       }
     }
   }

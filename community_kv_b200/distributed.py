@@ -155,6 +155,17 @@ class PeerOutputExchange:
     ``ckv_layer_args`` at the peers' slots and counters; ``wait`` enqueues the
     bounded wait for the peers' rows of that launch.  No NVLink multicast object is
     created (plain peer mappings only).
+
+    There is no acknowledgement back to the writer: a peer may store the rows of step
+    t + 1 into ``gathered[launch]`` as soon as it has received this rank's rows of step
+    t for that launch.  With two or more launches per step, stream order on every rank
+    keeps a launch's rows intact until the rank's own next launch has been enqueued
+    behind its consumer; a step made of a single launch has no such slack, so the
+    constructor refuses ``launches < 2`` (use the collective, ``gather_head_outputs``,
+    there).  A consumer that reads ``gathered`` outside the stream (a host copy, another
+    stream) must finish before it enqueues the next step.  After a wait has timed out
+    (``check`` raises) the counters are out of step with the peers for good: the
+    exchange must be rebuilt, not reused.
     """
 
     def __init__(self, *, launches: int, slots: int, heads: int, head_dim: int, units: int,
@@ -167,6 +178,8 @@ class PeerOutputExchange:
         self.rank = dist.get_rank(group)
         if self.world - 1 > native.MAX_PEERS:
             raise ValueError("at most %d peers" % native.MAX_PEERS)
+        if launches < 2:
+            raise ValueError("the peer exchange needs at least two launches per step (no back-pressure)")
         self.units = units
         self.gathered = symm_mem.empty(
             (launches, self.world, slots, heads, head_dim), dtype=torch.bfloat16, device=device
