@@ -70,7 +70,7 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--peer-wait", choices=["node", "launch"], default="node",
                         help="peer exchange: wait for the peers' rows in a one-thread kernel after each layer "
                              "(node) or inside the layer launch itself (launch)")
-    parser.add_argument("--update", choices=["inline", "deferred"], default="inline",
+    parser.add_argument("--update", choices=["inline", "deferred"], default="deferred",
                         help="online graph update inside the layer launch (inline), or as its own launch on a "
                              "second stream that runs beside the next layer's launch (deferred)")
     parser.add_argument("--scaling", choices=["weak", "strong"], default="weak",
@@ -524,7 +524,8 @@ def run_b200(args: argparse.Namespace) -> None:
     layer_ms = []
     solo = []  # the same launches without the cross-GPU stores: these passes are not synchronised
     for launch in range(launches):
-        clone = native.LayerArgs.from_buffer_copy(packed[launch])
+        # the launch the timed step uses: without the online update when that runs as its own launch
+        clone = native.LayerArgs.from_buffer_copy(attend_args[launch] if deferred else packed[launch])
         clone.peer_count = 0
         clone.peer_wait_flag = None
         solo.append(clone)
@@ -662,7 +663,7 @@ def run_b200(args: argparse.Namespace) -> None:
         "roofline": {
             "kernel": (
                 "decode_cluster_kernel (one launch per layer: centroid scoring, selection, KV gather + "
-                "segmented flash-decode, split merge, online update)"
+                "segmented flash-decode, split merge" + ("" if deferred else ", online update") + ")"
                 if kernels_per_layer == 1 else
                 "score_kernel + select_kernel + attention_kernel + merge_update_kernel (one layer)"
             ),
@@ -814,7 +815,7 @@ def run_sweep(args: argparse.Namespace) -> None:
 
     from community_kv_b200 import distributed as ckv_dist
     from community_kv_b200.config import CommunityKVConfig
-    from community_kv_b200.sequence_shard import SequenceShardedLayer, decode_emulated
+    from community_kv_b200.sequence_shard import SequenceShardedLayer
     from community_kv_b200.workload import build_planted_layer
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -834,7 +835,7 @@ def run_sweep(args: argparse.Namespace) -> None:
     config = CommunityKVConfig(token_budget=budget, num_sink=sinks, lam=0.5, aggregation="query_group")
     layer = SequenceShardedLayer(
         converted=converted, key_shard=key[:, begin:end].contiguous(), value_shard=value[:, begin:end].contiguous(),
-        row_begin=begin, total_rows=total_rows, config=config, splits=args.splits or None,
+        row_begin=begin, total_rows=total_rows, config=config, splits=args.splits or 8,
     )
     del key, value
     torch.cuda.empty_cache()
@@ -847,9 +848,7 @@ def run_sweep(args: argparse.Namespace) -> None:
     stream = torch.cuda.Stream(device)
 
     def enqueue() -> "torch.Tensor":
-        if world > 1:
-            return layer.decode(q_cur, k_cur, SCALE)
-        return decode_emulated([layer], q_cur, k_cur, SCALE)
+        return layer.decode(q_cur, k_cur, SCALE)
 
     graph = None
 
@@ -926,11 +925,13 @@ def run_sweep(args: argparse.Namespace) -> None:
         "config": {
             "workload": f"sequence-sharded single-layer decode: batch 1, 32 Q / 8 KV heads, ctx {args.sweep_context}, "
                         f"{clusters} planted clusters per head, budget {budget}, rows split x{world}",
-            "exchange": "NCCL all-gather of (max, sum, acc) triples and top-8 candidates" if world > 1 else "none",
+            "exchange": "one NCCL all-gather of the ranks' merged (acc, max, sum) rows and top-8 candidates, "
+                        "merged in place by ckv_merge_partials" if world > 1 else "none",
             "l2": "inputs larger than L2 (each step gathers rows scattered over the whole KV cache)",
         },
         "roofline": {
-            "kernel": "score_kernel + select_kernel + attention_kernel + merge_update_kernel (one sharded layer step)",
+            "kernel": "score_kernel + select_kernel + attention_kernel + merge_update_kernel"
+                      + (" + all-gather + merge_update_kernel over the ranks' rows" if world > 1 else ""),
             "bound": "hbm",
             "achieved": bytes_per_gpu / (ms_per_step * 1e-3) / 1e9,
             "peak": peak,
@@ -939,7 +940,7 @@ def run_sweep(args: argparse.Namespace) -> None:
             "traffic": None,
             "algorithmic_bytes_per_launch": bytes_per_gpu,
         },
-        "gpu_launches": args.steps * 6,
+        "gpu_launches": args.steps * (4 if world == 1 else 5),
         "cuda_graph": use_graph,
         "clocks": clocks,
     }

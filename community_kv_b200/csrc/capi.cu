@@ -235,6 +235,44 @@ int ckv_online_update(const ckv_layer_args* args, void* cuda_stream) {
   return ckv::launched(ckv::launch_merge_update(local, static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int ckv_merge_partials(const ckv_layer_args* args, void* cuda_stream) {
+  const int common = ckv::check_common(args);
+  if (common != CKV_OK) return common;
+  const ckv_layer_args& a = *args;
+  if (!a.partials || !a.partial_topk || !a.output || !a.lse || !a.topk_scores || !a.topk_positions) {
+    return CKV_ERR_NULL;
+  }
+  if (a.splits <= 0 || a.splits > 32) return CKV_ERR_SHAPE;
+  if (a.partial_unit_stride < 0 || a.partial_split_stride < 0 || a.topk_unit_stride < 0 ||
+      a.topk_split_stride < 0 || (a.partial_unit_stride % 4) || (a.partial_split_stride % 4)) {
+    return CKV_ERR_SHAPE;  // rows are read 16 bytes at a time
+  }
+  if (reinterpret_cast<uintptr_t>(a.partials) % 16 || reinterpret_cast<uintptr_t>(a.partial_topk) % 8) {
+    return CKV_ERR_ALIGN;
+  }
+  if (!(a.flags & CKV_FLAG_SKIP_UPDATE)) {
+    if (!a.centroids || !a.community_sizes || !a.community_counts || !a.community_weight ||
+        !a.total_weight || !a.token_communities || !a.current_position || !a.delta_positions ||
+        !a.chunk_start || !a.chunk_capacity || !a.chunk_size || !a.chunk_next || !a.chunk_previous ||
+        !a.community_head || !a.community_tail || !a.delta_sizes || !a.next_free_chunk ||
+        !a.next_free_position || !a.assigned || !a.overflow) {
+      return CKV_ERR_NULL;
+    }
+    if (!a.current_key && !a.key) return CKV_ERR_NULL;
+    if (a.sequence_capacity <= 0 || a.token_capacity <= 0 || a.chunks_per_graph <= 0 ||
+        a.delta_position_capacity <= 0) {
+      return CKV_ERR_SHAPE;
+    }
+  }
+  const int status = ckv::select_device(args);
+  if (status != CKV_OK) return status;
+  ckv_layer_args local = a;
+  local.flags = a.flags & ~(CKV_FLAG_UPDATE_ONLY | CKV_FLAG_ATTENTION_ONLY);
+  local.merged = nullptr;  // the rows being merged may be the caller's `merged` records themselves
+  local.merged_topk = nullptr;
+  return ckv::launched(ckv::launch_merge_update(local, static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int ckv_prefill_topk(const ckv_prefill_args* args, void* cuda_stream) {
   if (args == nullptr) return CKV_ERR_NULL;
   const ckv_prefill_args& a = *args;

@@ -20,7 +20,7 @@
 // device functions run in the same order on the same data.  The path needs one
 // graph per retrieval head (a graph shared by several heads is updated by its
 // leader while followers may still be reading it, which only a kernel boundary
-// orders) and descriptors that fit the selection's shared-memory stash.
+// orders) and per-CTA community slices that fit the selection's shared-memory stash.
 
 #include "merge_update.cuh"
 #include "score_select.cuh"
@@ -112,10 +112,10 @@ __global__ void __launch_bounds__(kFusedThreads, 3) decode_cluster_kernel(const 
 }
 
 bool fused_layer_supported(const ckv_layer_args& a) {
-  const int budget = a.token_budget - a.num_sink - 1;
-  const int descriptors = a.descriptor_capacity < budget ? a.descriptor_capacity : budget;
-  return a.graphs == a.retrieval_heads && a.splits >= 1 && a.splits <= 8 &&
-         descriptors <= kDescStash && a.community_capacity <= kStash &&
+  // every CTA stages the rows it scores: a 1/splits share of the 16-row groups
+  const int groups = (a.community_capacity + 15) / 16;
+  const int rows_per_cta = 16 * ((groups + a.splits - 1) / (a.splits > 0 ? a.splits : 1));
+  return a.graphs == a.retrieval_heads && a.splits >= 1 && a.splits <= 8 && rows_per_cta <= kStash &&
          !(a.flags & (CKV_FLAG_ATTENTION_ONLY | CKV_FLAG_UPDATE_ONLY | CKV_FLAG_UNFUSED));
 }
 

@@ -59,7 +59,11 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
   const int capacity = a.community_capacity;
   const bool leader = u.head == u.graph && !(a.flags & CKV_FLAG_SKIP_UPDATE);
   const int64_t graph_slot = static_cast<int64_t>(u.batch) * a.graphs + u.graph;
-  const float* partial = a.partials + static_cast<int64_t>(flat) * splits * group * kPartialStride;
+  // partial rows: dense [unit][split][head][132] unless the caller gives strides
+  const int64_t split_stride =
+      a.partial_split_stride > 0 ? a.partial_split_stride : static_cast<int64_t>(group) * kPartialStride;
+  const int64_t unit_stride = a.partial_unit_stride > 0 ? a.partial_unit_stride : splits * split_stride;
+  const float* partial = a.partials + static_cast<int64_t>(flat) * unit_stride;
 
   // state of the update warp that crosses the barrier
   float my_score = 0.f;
@@ -115,14 +119,14 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
       for (int s = 0; s < kMaxSplitsInFlight; ++s) {
         if (s < splits) {
           rows[s] = __ldcg(reinterpret_cast<const float4*>(
-              partial + (s * group + g) * kPartialStride + 4 * lane));
+              partial + s * split_stride + g * kPartialStride + 4 * lane));
         }
       }
       float my_max = -INFINITY;
       float my_sum = 0.f;
       if (lane < splits) {
         const float2 pair = __ldcg(reinterpret_cast<const float2*>(
-            partial + (lane * group + g) * kPartialStride + kHeadDim));
+            partial + lane * split_stride + g * kPartialStride + kHeadDim));
         my_max = pair.x;
         my_sum = pair.y;
       }
@@ -152,7 +156,7 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
       for (int s = kMaxSplitsInFlight; s < splits; ++s) {
         const float w = __shfl_sync(0xffffffffu, weight, s);
         const float4 v = __ldcg(reinterpret_cast<const float4*>(
-            partial + (s * group + g) * kPartialStride + 4 * lane));
+            partial + s * split_stride + g * kPartialStride + 4 * lane));
         numerator.x += v.x * w;
         numerator.y += v.y * w;
         numerator.z += v.z * w;
@@ -191,13 +195,17 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
   } else if (warp == merge_warps) {
     // ---- update warp, before the barrier: global top-8 of the per-split
     // candidates (every head reports it) and the loads that depend only on it ----
-    const uint64_t* candidates = a.partial_topk + static_cast<int64_t>(flat) * splits * kKappa;
+    const int64_t topk_split = a.topk_split_stride > 0 ? a.topk_split_stride : kKappa;
+    const int64_t topk_unit = a.topk_unit_stride > 0 ? a.topk_unit_stride : splits * topk_split;
+    const uint64_t* candidates = a.partial_topk + static_cast<int64_t>(flat) * topk_unit;
     const int total = splits * kKappa;
     uint64_t mine[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int index = lane + 32 * i;
-      mine[i] = (index < total && !update_only) ? __ldcg(candidates + index) : 0ull;
+      mine[i] = (index < total && !update_only)
+                    ? __ldcg(candidates + (index / kKappa) * topk_split + (index % kKappa))
+                    : 0ull;
     }
     if (leader) {
       active = a.community_counts[flat];
@@ -222,6 +230,9 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
       if (lane == k) {
         my_score = key32_to_float(static_cast<uint32_t>(best >> 32));
         my_position = static_cast<int>(0xffffffffu - static_cast<uint32_t>(best));
+        if (a.merged_topk != nullptr) {
+          a.merged_topk[static_cast<int64_t>(flat) * kKappa + k] = best;
+        }
       }
     }
     if (update_only) {

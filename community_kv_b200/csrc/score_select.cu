@@ -89,8 +89,23 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_kernel(const ckv_layer
   }
 }
 
-__global__ void __launch_bounds__(kSelectThreads, 1) select_kernel(const ckv_layer_args a) {
+// Dynamic shared memory: one 256-bin (mass, count) histogram per warp, then the key/size
+// stash of `stash_capacity` entries (sizes first).
+constexpr int kSelectWarpHistBytes = (kSelectThreads / 32) * 256 * 2 * static_cast<int>(sizeof(int));
+
+__global__ void __launch_bounds__(kSelectThreads, 1) select_kernel(const ckv_layer_args a,
+                                                                    int stash_capacity) {
   __shared__ SelectSmem sm;
+  extern __shared__ __align__(16) uint8_t dynamic[];
+  if (threadIdx.x == 0) {
+    sm.warp_mass = reinterpret_cast<int*>(dynamic);
+    sm.warp_count = sm.warp_mass + (kSelectThreads / 32) * 256;
+    uint8_t* stash = dynamic + kSelectWarpHistBytes;
+    sm.stash_size = reinterpret_cast<int*>(stash);
+    sm.stash_key = reinterpret_cast<uint16_t*>(stash + static_cast<size_t>(stash_capacity) * sizeof(int));
+    sm.stash_capacity = stash_capacity;
+  }
+  __syncthreads();
   pdl_release_dependents();
   pdl_wait_for_predecessor();  // the fp16 scores come from the scoring kernel
   select_unit<kSelectThreads>(a, blockIdx.x, sm, true, 0, a.token_budget);
@@ -123,8 +138,32 @@ cudaError_t launch_score(const ckv_layer_args& a, cudaStream_t stream) {
 }
 
 cudaError_t launch_select(const ckv_layer_args& a, cudaStream_t stream) {
-  return launch_dependent(select_kernel, dim3(a.batch * a.retrieval_heads), dim3(kSelectThreads), 0,
-                          stream, a);
+  // Stage every community's key and size in shared memory when they fit (6 bytes each;
+  // one CTA per SM, so up to kSelectStashMax communities); beyond that the kernel re-reads
+  // them from global memory in every pass.
+  constexpr int kSelectStashMax = 20480;
+  constexpr int kSelectStashBytes = kSelectStashMax * 6 + kSelectWarpHistBytes;
+  static bool configured[64] = {};
+  const int device = a.device >= 0 && a.device < 64 ? a.device : 0;
+  if (!configured[device]) {
+    const cudaError_t err =
+        cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSelectStashBytes);
+    if (err != cudaSuccess) return err;
+    configured[device] = true;
+  }
+  int capacity = ((a.community_capacity + 7) / 8) * 8;
+  if (capacity > kSelectStashMax) capacity = kStash;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(a.batch * a.retrieval_heads);
+  config.blockDim = dim3(kSelectThreads);
+  config.dynamicSmemBytes = static_cast<size_t>(capacity) * 6 + kSelectWarpHistBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, select_kernel, a, capacity);
 }
 
 cudaError_t launch_resolve(const ckv_layer_args& a, cudaStream_t stream) {

@@ -624,8 +624,13 @@ __device__ __forceinline__ void resolve_tokens(const ckv_layer_args& a, int flat
 
 // Shared memory of one selection.
 struct SelectSmem {
-  uint16_t stash_key[kStash];
-  int stash_size[kStash];
+  // keys and sizes of the unit's communities, staged by the caller in (dynamic) shared
+  // memory: `stash_capacity` entries each
+  uint16_t* stash_key;
+  int* stash_size;
+  int stash_capacity;
+  int* warp_mass;   // optional: one 256-bin histogram per warp (see select_unit), else null
+  int* warp_count;
   int hist_mass[256];
   int hist_count[256];
   Quad scan_scratch[32];
@@ -652,7 +657,7 @@ __device__ __forceinline__ void select_unit(const ckv_layer_args& a, int flat, S
   const uint16_t* score_bits =
       reinterpret_cast<const uint16_t*>(a.scores) + static_cast<int64_t>(flat) * capacity;
   const int32_t* sizes = a.community_sizes + static_cast<int64_t>(flat) * capacity;
-  const bool stashed = active <= kStash;
+  const bool stashed = active <= sm.stash_capacity;
 
   for (int bin = tid; bin < 256; bin += kThreads) {
     sm.hist_mass[bin] = 0;
@@ -683,16 +688,49 @@ __device__ __forceinline__ void select_unit(const ckv_layer_args& a, int flat, S
     }
   };
 
-  // Pass 1: histogram of the high key byte, weighted by community size.
-  for (int c = tid; c < active; c += kThreads) {
-    int size, key;
-    item(c, size, key);
-    if (size > 0) {
-      atomicAdd(&sm.hist_mass[key >> 8], size);
-      atomicAdd(&sm.hist_count[key >> 8], 1);
+  // A histogram pass.  Scores crowd into a few bins, so atomics on one shared pair of
+  // histograms would queue up behind each other across all warps: every warp counts
+  // into a histogram of its own (sm.warp_mass / sm.warp_count, when the caller provides
+  // them) and the copies are summed afterwards.
+  constexpr int kWarps = kThreads / 32;
+  const bool privatized = sm.warp_mass != nullptr;
+  auto histogram = [&](auto&& bin_of) {
+    if (privatized) {
+      for (int i = tid; i < kWarps * 256; i += kThreads) {
+        sm.warp_mass[i] = 0;
+        sm.warp_count[i] = 0;
+      }
+      __syncthreads();
     }
-  }
-  __syncthreads();
+    int* mass = privatized ? sm.warp_mass + (tid >> 5) * 256 : sm.hist_mass;
+    int* count = privatized ? sm.warp_count + (tid >> 5) * 256 : sm.hist_count;
+    for (int c = tid; c < active; c += kThreads) {
+      int size, key;
+      item(c, size, key);
+      const int bin = bin_of(key);
+      if (size > 0 && bin >= 0) {
+        atomicAdd(&mass[bin], size);
+        atomicAdd(&count[bin], 1);
+      }
+    }
+    __syncthreads();
+    if (privatized) {
+      for (int bin = tid; bin < 256; bin += kThreads) {
+        int total_mass = 0, total_count = 0;
+#pragma unroll 8
+        for (int w = 0; w < kWarps; ++w) {
+          total_mass += sm.warp_mass[w * 256 + bin];
+          total_count += sm.warp_count[w * 256 + bin];
+        }
+        sm.hist_mass[bin] = total_mass;
+        sm.hist_count[bin] = total_count;
+      }
+      __syncthreads();
+    }
+  };
+
+  // Pass 1: histogram of the high key byte, weighted by community size.
+  histogram([](int key) { return key >> 8; });
   if (tid < 32) {
     find_threshold_bin(sm.hist_mass, sm.hist_count, budget, limit, 0, 0, &sm.bin, &sm.mass, &sm.count);
   }
@@ -707,15 +745,7 @@ __device__ __forceinline__ void select_unit(const ckv_layer_args& a, int flat, S
   }
   __syncthreads();
   // Pass 2: histogram of the low byte inside the chosen high bin.
-  for (int c = tid; c < active; c += kThreads) {
-    int size, key;
-    item(c, size, key);
-    if (size > 0 && (key >> 8) == high_bin) {
-      atomicAdd(&sm.hist_mass[key & 0xff], size);
-      atomicAdd(&sm.hist_count[key & 0xff], 1);
-    }
-  }
-  __syncthreads();
+  histogram([high_bin](int key) { return (key >> 8) == high_bin ? (key & 0xff) : -1; });
   if (tid < 32) {
     find_threshold_bin(sm.hist_mass, sm.hist_count, budget, limit, mass_above, count_above, &sm.bin,
                        &sm.mass, &sm.count);
@@ -897,12 +927,21 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
   const int active = max(0, min(capacity, a.community_counts[flat]));
   const int budget = a.token_budget - a.num_sink - 1;
   const int limit = a.max_communities;
-  // the last slice also takes any active rows beyond the scored cover
+  // The last slice also takes any active rows beyond the scored cover (there are none when
+  // the cover is the initial count plus the decode headroom).  They must fit its stash:
+  // what does not is left out and reported in the status word.
   if (rank == ranks - 1 && active > row0 + rows) {
     const uint16_t* score_bits =
         reinterpret_cast<const uint16_t*>(a.scores) + static_cast<int64_t>(flat) * capacity;
     const int32_t* sizes = a.community_sizes + static_cast<int64_t>(flat) * capacity;
-    for (int c = row0 + rows + tid; c < active; c += kThreads) {
+    int active_here = active;
+    if (active - row0 > kStash) {
+      active_here = row0 + kStash;
+      if (tid == 0 && a.status != nullptr) {
+        atomicOr(a.status, CKV_DEV_STASH_OVERFLOW);
+      }
+    }
+    for (int c = row0 + rows + tid; c < active_here; c += kThreads) {
       const int size = __ldg(sizes + c);
       const int key = size > 0 ? ordered_key16(__ldcg(score_bits + c)) : 0;
       sm.size[c - row0] = size > 0 ? size : 0;
@@ -912,7 +951,7 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
         atomicAdd(&sm.hist_count[key >> 8], 1);
       }
     }
-    rows = active - row0;
+    rows = active_here - row0;
   }
   rows = max(0, min(rows, active - row0));
   cluster_sync_all();  // every slice's first-pass histogram is complete
@@ -1109,8 +1148,12 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
   __syncthreads();
   const int descriptors = sm.descriptors;
   phase_stamp(a, flat, rank, 5);
-  const int32_t* search_ends = sm.desc_end;
-  const int32_t* search_comm = sm.desc_comm;
+  // The shared-memory list holds the first kDescStash descriptors; a longer list (a large
+  // budget spent on very small communities) is searched in the workspace, where every
+  // slice's owner stored it before the barrier above.
+  const bool in_smem = descriptors <= kDescStash;
+  const int32_t* search_ends = in_smem ? sm.desc_end : out_ends;
+  const int32_t* search_comm = in_smem ? sm.desc_comm : out_comm;
 
   resolve_tokens<kThreads>(a, flat, u, search_ends, search_comm, descriptors, rank == 0, token_begin,
                            token_end);

@@ -107,6 +107,11 @@ class LayerArgs(ctypes.Structure):
         ("peer_done", _ptr),
         ("peer_wait_flag", _ptr),
         ("phase_times", _ptr),
+        ("partial_unit_stride", _i64),
+        ("partial_split_stride", _i64),
+        ("topk_unit_stride", _i64),
+        ("topk_split_stride", _i64),
+        ("merged_topk", _ptr),
     ]
 
 
@@ -180,6 +185,7 @@ ENTRY_POINTS = (
     "ckv_online_update",
     "ckv_wait_peers",
     "ckv_append_kv",
+    "ckv_merge_partials",
 )
 
 

@@ -487,23 +487,31 @@ def segmented_attention_static(
     return workspace.output, workspace.lse, workspace.topk_scores, workspace.topk_positions
 
 
+def tensor_scores_enabled() -> bool:
+    """Centroid scoring on the tensor cores (the default); ``CKV_TENSOR_SCORES=0`` selects the
+    fixed-order CUDA-core sum, which a CPU can reproduce bit for bit."""
+
+    return os.environ.get("CKV_TENSOR_SCORES", "1") != "0"
+
+
 def _layout_flags() -> int:
     """Process-wide switches read from the environment.
 
+    ``CKV_TENSOR_SCORES=0``: score the centroids on the CUDA cores in one fixed summation
+    order instead of on the tensor cores (``mma.m16n8k16``, which is also what the
+    reference's ``tl.dot`` compiles to; the two may differ in a score's last fp16 bit).
     ``CKV_UNFUSED=1`` selects the four stand-alone kernels for ``ckv_decode_layer``
     instead of the single cluster launch (same results; a debugging and A/B-timing
     switch).  ``CKV_REFERENCE_DIVISION=1`` makes the running centroid mean divide like
     the reference's compiled Triton kernel (approximate ``div.full.f32``) instead of
     like its CPU test helper (IEEE division): the stored e4m3 centroid then matches the
     reference kernel bit for bit also when the exact quotient is a rounding tie.
-    ``CKV_TENSOR_SCORES=1`` scores the centroids on the tensor cores (a score may then
-    differ from the fixed-order one in its last fp16 bit).
     """
 
     flags = native.FLAG_UNFUSED if os.environ.get("CKV_UNFUSED") == "1" else 0
     if os.environ.get("CKV_REFERENCE_DIVISION") == "1":
         flags |= native.FLAG_REFERENCE_DIVISION
-    if os.environ.get("CKV_TENSOR_SCORES") == "1":
+    if tensor_scores_enabled():
         flags |= native.FLAG_TENSOR_SCORES
     return flags
 
@@ -692,5 +700,6 @@ __all__ = [
     "select_weighted_descriptors_auto",
     "select_weighted_descriptors_cluster",
     "select_weighted_descriptors_native",
+    "tensor_scores_enabled",
     "triton_segmented_attention",
 ]

@@ -49,7 +49,14 @@ def unpack_candidates(packed: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]
 
 
 class SequenceShardedLayer:
-    """This rank's share of one layer: replicated state, rows ``[row_begin, row_begin + rows)`` of K/V."""
+    """This rank's share of one layer: replicated state, rows ``[row_begin, row_begin + rows)`` of K/V.
+
+    A step is ``local`` (scoring, selection, attention over the rows held here, merged into
+    one un-normalised ``(acc, max, sum)`` row per head plus this shard's eight best neighbour
+    candidates, written straight into ``record``), ONE all-gather of the ranks' records, and
+    ``finish`` (``ckv_merge_partials`` with one "split" per rank, reading the gathered records
+    in place: log-sum-exp merge, global top-8, online update of this rank's replica).
+    """
 
     def __init__(
         self,
@@ -94,103 +101,82 @@ class SequenceShardedLayer:
         )
         self.sinks = torch.arange(config.num_sink, dtype=torch.int32, device=device)
         heads = mutable.retrieval_head_count
-        self.merged = torch.zeros(
-            (heads, converted.group_size, PARTIAL_STRIDE), dtype=torch.float32, device=device
-        )
+        # what one rank contributes to the exchange: [R, G, 132] floats, then [R, 8] packed candidates
+        self.merged_floats = heads * converted.group_size * PARTIAL_STRIDE
+        self.record_bytes = self.merged_floats * 4 + heads * KAPPA * 8
+        self.record = torch.zeros((self.record_bytes,), dtype=torch.uint8, device=device)
+        self.merged = self.record[: self.merged_floats * 4].view(torch.float32).view(
+            heads, converted.group_size, PARTIAL_STRIDE)
+        self.merged_topk = self.record[self.merged_floats * 4 :].view(torch.int64).view(heads, KAPPA)
+        self._gathered: torch.Tensor | None = None
+        kv_map = mutable.retrieval_to_kv.cpu()
+        self._identity_kv = bool(torch.equal(kv_map, torch.arange(heads, dtype=kv_map.dtype)))
+        self._kv_index = mutable.retrieval_to_kv.long()
+        self._keep: torch.Tensor | None = None
 
-    # -- step 1: replicated scoring + selection, local attention partials ---------------------
-    def partial(self, query: torch.Tensor, softmax_scale: float):
-        """Returns ``(maxima [Hq], sums [Hq], accumulators [Hq, 128], packed candidates [R, 8])``."""
-
+    def _layer_args(self, query: torch.Tensor, softmax_scale: float, *, update: bool) -> native.LayerArgs:
         conv, ws = self.converted, self.workspace
-        state = conv.mutable
-        segments = ops.score_and_select(
-            query=query,
-            centroids=state.centroids,
-            community_sizes=state.community_sizes,
-            community_counts=state.community_counts,
-            workspace=ws.selection,
-            csr=conv.csr,
-            state=state,
-            sink_positions=self.sinks,
-            current_position=conv.current_position,
+        args = ops.build_layer_args(
+            query=query, key=self.key, value=self.value, csr=conv.csr, state=conv.mutable,
+            sink_positions=self.sinks, current_position=conv.current_position,
+            softmax_scale=softmax_scale, lam=self.config.lam, workspace=ws,
         )
-        args = native.LayerArgs()
-        ops._graph_args(
-            args, csr=conv.csr, state=state, sink_positions=self.sinks,
-            current_position=conv.current_position,
-        )
-        ops._attention_args(
-            args, query=query, key=self.key, value=self.value, softmax_scale=softmax_scale,
-            lam=self.config.lam, workspace=ws.attention, update=None, token_budget=segments.token_budget,
-        )
+        native.fill(args, sequence_capacity=self.total_rows)
+        if not update:
+            args.flags |= native.FLAG_SKIP_UPDATE
+        return args
+
+    def _key_rows(self, current_key: torch.Tensor) -> torch.Tensor:
+        """The new token's key per retrieval head ``[R, 128]`` (bf16, contiguous)."""
+
+        rows = current_key if self._identity_kv else current_key[self._kv_index]
+        rows = rows.contiguous()
+        self._keep = rows  # the kernel reads it asynchronously
+        return rows
+
+    # -- step 1: replicated scoring + selection, attention over the local rows ----------------
+    def local(self, query: torch.Tensor, softmax_scale: float) -> torch.Tensor:
+        """Fills and returns ``record`` (uint8 ``[record_bytes]``): this shard's merged rows and candidates."""
+
+        args = self._layer_args(query, softmax_scale, update=False)
         native.fill(
             args,
-            device=query.device.index or 0,
-            batch=1,
-            num_sink=segments.num_sink,
-            descriptor_capacity=segments.communities.shape[-1],
-            communities=native.pointer(segments.communities),
-            cumulative_ends=native.pointer(segments.cumulative_ends),
-            descriptor_counts=native.pointer(segments.descriptor_counts),
-            tile_descriptors=native.pointer(segments.tile_descriptors),
-            positions=native.pointer(ws.selection.positions),
             kv_row_begin=self.row_begin,
             kv_row_count=self.key.shape[1],
             merged=native.pointer(self.merged),
+            merged_topk=native.pointer(self.merged_topk),
         )
-        native.call("ckv_segmented_attention", args, native.current_stream(query.device))
-        flat = self.merged.view(-1, PARTIAL_STRIDE)
-        packed = pack_candidates(ws.attention.topk_scores, ws.attention.topk_positions)
-        return flat[:, HEAD_DIM], flat[:, HEAD_DIM + 1], flat[:, :HEAD_DIM], packed
+        native.call("ckv_decode_layer", args, native.current_stream(query.device))
+        return self.record
 
     # -- step 2: every rank applies the same combined result to its replica --------------------
     def finish(
         self,
-        output: torch.Tensor,
-        lse: torch.Tensor,
-        packed_topk: torch.Tensor,
+        query: torch.Tensor,
+        gathered: torch.Tensor,
         current_key: torch.Tensor,
         softmax_scale: float,
     ) -> torch.Tensor:
-        conv, ws = self.converted, self.workspace
-        state = conv.mutable
-        attention = ws.attention
-        attention.output.copy_(output.to(torch.bfloat16))
-        attention.lse.copy_(lse)
-        scores, positions = unpack_candidates(packed_topk)
-        attention.topk_scores.copy_(scores)
-        attention.topk_positions.copy_(positions)
-        key_rows = current_key[state.retrieval_to_kv.long()].contiguous()  # [R, 128]
-        args = native.LayerArgs()
-        ops._graph_args(
-            args, csr=conv.csr, state=state, sink_positions=self.sinks,
-            current_position=conv.current_position,
-        )
+        """``gathered`` uint8 ``[ranks, record_bytes]``: every rank's record, merged in place."""
+
+        ranks = gathered.shape[0]
+        if gathered.dtype != torch.uint8 or gathered.shape[1] != self.record_bytes or not gathered.is_contiguous():
+            raise ValueError("gathered must be contiguous uint8 [ranks, record_bytes]")
+        args = self._layer_args(query, softmax_scale, update=True)
+        group = self.converted.group_size
         native.fill(
             args,
-            device=output.device.index or 0,
-            batch=1,
-            group_size=conv.group_size,
-            token_budget=ws.selection.token_budget,
-            num_sink=ws.selection.num_sink,
-            sequence_capacity=self.total_rows,
-            lam=float(self.config.lam),
-            softmax_scale=float(softmax_scale),
-            splits=1,
-            lse=native.pointer(attention.lse),
-            topk_scores=native.pointer(attention.topk_scores),
-            topk_positions=native.pointer(attention.topk_positions),
-            output=native.pointer(attention.output),
-            partials=native.pointer(attention.partials),
-            partial_topk=native.pointer(attention.partial_topk_packed),
-            assigned=native.pointer(ws.update.assigned_communities),
-            overflow=native.pointer(ws.update.overflow),
-            current_key=native.pointer(key_rows),
+            splits=ranks,
+            partials=gathered.data_ptr(),
+            partial_unit_stride=group * PARTIAL_STRIDE,
+            partial_split_stride=self.record_bytes // 4,
+            partial_topk=gathered.data_ptr() + self.merged_floats * 4,
+            topk_unit_stride=KAPPA,
+            topk_split_stride=self.record_bytes // 8,
+            current_key=native.pointer(self._key_rows(current_key)),
         )
-        native.call("ckv_online_update", args, native.current_stream(output.device))
-        self._keep = key_rows  # the kernel reads it asynchronously
-        return attention.output
+        native.call("ckv_merge_partials", args, native.current_stream(query.device))
+        return self.workspace.attention.output
 
     def decode(
         self,
@@ -201,12 +187,22 @@ class SequenceShardedLayer:
     ) -> torch.Tensor:
         """One decode step across the ranks of ``group``; returns bf16 ``[Hq, 128]`` on every rank."""
 
-        maxima, sums, accumulators, packed = self.partial(query, softmax_scale)
-        output, lse = ckv_dist.combine_partials(maxima, sums, accumulators, group=group)
-        world = dist.get_world_size(group)
-        gathered = torch.empty((world,) + packed.shape, dtype=packed.dtype, device=packed.device)
-        dist.all_gather_into_tensor(gathered.view(world * packed.shape[0], KAPPA), packed.contiguous(), group=group)
-        return self.finish(output, lse, ckv_dist.merge_topk(gathered), current_key, softmax_scale)
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if world == 1 and self.row_begin == 0 and self.key.shape[1] == self.total_rows:
+            return self.decode_whole(query, current_key, softmax_scale)
+        record = self.local(query, softmax_scale)
+        if self._gathered is None or self._gathered.shape[0] != world:
+            self._gathered = torch.empty((world, self.record_bytes), dtype=torch.uint8, device=record.device)
+        dist.all_gather_into_tensor(self._gathered.view(-1), record, group=group)
+        return self.finish(query, self._gathered, current_key, softmax_scale)
+
+    def decode_whole(self, query: torch.Tensor, current_key: torch.Tensor, softmax_scale: float) -> torch.Tensor:
+        """The whole cache is local: one ``ckv_decode_layer`` call, nothing to exchange."""
+
+        args = self._layer_args(query, softmax_scale, update=True)
+        native.fill(args, current_key=native.pointer(self._key_rows(current_key)))
+        native.call("ckv_decode_layer", args, native.current_stream(query.device))
+        return self.workspace.attention.output
 
 
 def decode_emulated(
@@ -217,15 +213,10 @@ def decode_emulated(
 ) -> torch.Tensor:
     """All shards in one process, one after the other (no collectives): for tests on one GPU."""
 
-    pieces = [shard.partial(query, softmax_scale) for shard in shards]
-    output, lse = ckv_dist.merge_partials(
-        torch.stack([p[0] for p in pieces]), torch.stack([p[1] for p in pieces]),
-        torch.stack([p[2] for p in pieces]),
-    )
-    top = ckv_dist.merge_topk(torch.stack([p[3] for p in pieces]))
+    gathered = torch.stack([shard.local(query, softmax_scale) for shard in shards])
     result = None
     for shard in shards:
-        result = shard.finish(output, lse, top, current_key, softmax_scale)
+        result = shard.finish(query, gathered, current_key, softmax_scale)
     return result
 
 

@@ -29,7 +29,7 @@
  *                            (third_party/flash_attention/community-kv.patch)
  *   ckv_append_kv            the cache layer's index_copy_ of the decoded token
  *                            community_kv/attention/cache.py:29-36
- * Without a counterpart in the (single-GPU) reference: ckv_online_update,
+ * Without a counterpart in the (single-GPU) reference: ckv_online_update, ckv_merge_partials,
  * ckv_wait_peers and the peer_* fields (KV heads or sequence rows sharded over GPUs),
  * ckv_segmented_attention_static, ckv_decode_layer_kernels.
  */
@@ -59,7 +59,8 @@ typedef enum ckv_status {
 } ckv_status;
 
 /* bits OR-ed into *status by the kernels */
-#define CKV_DEV_WAIT_TIMEOUT 1u /* a bounded mbarrier wait gave up */
+#define CKV_DEV_WAIT_TIMEOUT 1u /* a bounded wait gave up */
+#define CKV_DEV_STASH_OVERFLOW 2u /* more active communities beyond score_cover than a CTA can stage */
 
 #define CKV_MAX_PEERS 7
 
@@ -191,6 +192,16 @@ typedef struct ckv_layer_args {
                                   2..4 after the selection's three cluster exchanges, 5 descriptors
                                   known, 6 cache rows resolved, 7 attended, 8 partials of the whole
                                   cluster visible (rank 0), 9 merged and updated (rank 0) */
+  /* ---- partial rows in a foreign layout (all zero / null: the dense local layout) ----
+   * ckv_merge_partials can merge rows that were not produced by this GPU's attention
+   * kernel, e.g. one merged row set per GPU after an all-gather of sequence shards. */
+  int64_t partial_unit_stride;  /* floats between units in `partials`; 0: splits * G * 132 */
+  int64_t partial_split_stride; /* floats between the splits of a unit; 0: G * 132 */
+  int64_t topk_unit_stride;     /* uint64 elements between units in `partial_topk`; 0: splits * 8 */
+  int64_t topk_split_stride;    /* uint64 elements between the splits of a unit; 0: 8 */
+  uint64_t* merged_topk;        /* optional [batch, R, 8]: with `merged`, the packed eight best
+                                   neighbour candidates of every unit (ordered fp32 score << 32 |
+                                   0xffffffff - position; 0: none), for a cross-GPU combine */
 } ckv_layer_args;
 
 /* Arguments of the prefill score-graph kernel.  Q, K, V, O are bf16 with a
@@ -282,6 +293,14 @@ int ckv_decode_layer_kernels(const ckv_layer_args* args);
  * `lse`, `topk_scores` and `topk_positions` already in the workspace (for
  * sequence-sharded decoding, where those are combined across GPUs first). */
 int ckv_online_update(const ckv_layer_args* args, void* cuda_stream);
+
+/* A4+A5 alone.  Merges the `splits` partial (acc, max, sum) rows per head and the
+ * `splits` candidate lists per unit that are already in `partials` / `partial_topk`
+ * (addressed with the partial_*_stride / topk_*_stride fields), writes output, lse and the
+ * top-8 neighbours, and (unless CKV_FLAG_SKIP_UPDATE) applies the online update.  With
+ * sequence-sharded decoding every GPU all-gathers the GPUs' `merged` / `merged_topk`
+ * records and calls this with splits = number of GPUs; no reference counterpart. */
+int ckv_merge_partials(const ckv_layer_args* args, void* cuda_stream);
 
 /* P1.  Causal attention (output + lse) that also emits each row's strongest
  * Q.K neighbours: the reference's top-8 rule (mode 1) or exact top-m per KV head

@@ -7,6 +7,7 @@ from dataclasses import fields
 import numpy as np
 import torch
 
+from community_kv_b200 import ops
 from community_kv_b200.state import DecodeDeltaChunks, MutableGraphState, PrefillCSR
 from oracle import decode_oracle as oracle
 
@@ -115,7 +116,23 @@ class OracleLayer:
         )
         return scores
 
-    def step(self, *, query, key, value, softmax_scale, lam, update=True, given_scores=None) -> oracle.LayerResult:
+    def step(self, *, query, key, value, softmax_scale, lam, update=True, given_scores=None,
+             device_scores=None) -> oracle.LayerResult:
+        """``device_scores``: the fp16 scores the device produced for this step.  When the library
+        scores on the tensor cores (its default) they are checked against the fixed-order scores to
+        one unit in the last place and the rest of the step is computed from them, so that everything
+        downstream is compared bit for bit; with ``CKV_TENSOR_SCORES=0`` they are ignored and the
+        comparison of the scores themselves is exact."""
+
+        if device_scores is not None and given_scores is None and ops.tensor_scores_enabled():
+            given_scores = device_scores.detach().cpu().clone()
+            exact = self.exact_scores(query)
+            covered = torch.ones_like(exact, dtype=torch.bool)
+            if self.cover is not None:
+                covered = torch.arange(exact.shape[1])[None, :] < torch.as_tensor(self.cover)[:, None]
+            distance = fp16_ulp_distance(given_scores, exact)[covered]
+            assert int(distance.max()) <= 1, f"tensor-core score {int(distance.max())} ulp from the fixed-order score"
+            assert float((distance > 0).float().mean()) < 5e-3
         return oracle.decode_layer(
             given_scores=given_scores,
             query=query,

@@ -23,10 +23,7 @@ def _cover(converted):
     return [min(capacity, c + converted.decode_capacity) for c in converted.initial_community_counts]
 
 
-def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, tensor_scores=False,
-                  defer_update=False):
-    """``tensor_scores``: the device scores come from the tensor cores; they are checked against the
-    fixed-order scores to one fp16 unit in the last place and everything after them bit for bit."""
+def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, defer_update=False):
 
     device = torch.device("cuda", 0)
     runtime = DecodeRuntime(config, splits=splits, defer_update=defer_update)
@@ -53,16 +50,8 @@ def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, ten
         assert out.shape == (1, 1, layer.query_heads, 128)
         runtime.synchronize_updates()
         where = f"step {step}"
-        given = None
-        if tensor_scores:
-            given = state.workspace.selection.scores.detach().cpu().clone()
-            exact = twin.exact_scores(query)
-            covered = torch.arange(given.shape[1])[None, :] < torch.tensor(twin.cover)[:, None]
-            distance = fp16_ulp_distance(given, exact)[covered]
-            assert int(distance.max()) <= 1, f"{where}: tensor-core score {int(distance.max())} ulp off"
-            assert float((distance > 0).float().mean()) < 5e-3, where
         want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=config.lam,
-                         given_scores=given)
+                         device_scores=state.workspace.selection.scores)
         assert_step_equal(
             selection=state.workspace.selection,
             attention=state.workspace.attention,
@@ -97,19 +86,37 @@ def test_unfused_kernels_give_the_same_result(monkeypatch):
 
 
 @pytest.mark.parametrize("unfused", [False, True])
+def test_fixed_order_scores_are_bit_exact(monkeypatch, unfused):
+    """``CKV_TENSOR_SCORES=0``: the CUDA-core scoring path sums in the fixed order the CPU restatement
+    reproduces, so the fp16 scores themselves (and with them everything else) match bit for bit."""
+
+    monkeypatch.setenv("CKV_TENSOR_SCORES", "0")
+    assert not ops.tensor_scores_enabled()
+    if unfused:
+        monkeypatch.setenv("CKV_UNFUSED", "1")
+    layer = make_layer(seed=13, seq_len=16384, communities=700, max_decode_tokens=8, zipf_exponent=1.1)
+    config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation="query_group")
+    _run_sequence(layer, config, steps=6, seed=1300)
+    layer = make_layer(seed=0, seq_len=8192, communities=64, max_decode_tokens=8, aggregation="per_query_head")
+    config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation="per_query_head")
+    _run_sequence(layer, config, steps=3, seed=100)
+
+
+@pytest.mark.parametrize("unfused", [False, True])
 def test_tensor_core_scores(monkeypatch, unfused):
     """Scoring on the tensor cores (single cluster launch and the stand-alone kernels): scores within one
     fp16 unit in the last place of the fixed-order ones, the rest of the step exact given those scores."""
 
     monkeypatch.setenv("CKV_TENSOR_SCORES", "1")
+    assert ops.tensor_scores_enabled()
     if unfused:
         monkeypatch.setenv("CKV_UNFUSED", "1")
     layer = make_layer(seed=11, seq_len=16384, communities=700, max_decode_tokens=8, zipf_exponent=1.1)
     config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation="query_group")
-    _run_sequence(layer, config, steps=6, seed=1100, tensor_scores=True)
+    _run_sequence(layer, config, steps=6, seed=1100)
     layer = make_layer(seed=12, kv_heads=2, group_size=8, seq_len=4096, communities=100, max_decode_tokens=4)
     config = CommunityKVConfig(token_budget=512, num_sink=4, lam=0.5, aggregation="query_group")
-    _run_sequence(layer, config, steps=3, seed=1200, tensor_scores=True, splits=3)
+    _run_sequence(layer, config, steps=3, seed=1200, splits=3)
 
 
 @pytest.mark.parametrize("aggregation", [GraphAggregation.QUERY_GROUP, GraphAggregation.LAYER_WISE])
@@ -190,7 +197,8 @@ def test_batched_sequences_match_per_sequence_oracle():
         assert out.shape == (3, 16, 128)
         for b in range(3):
             want = twins[b].step(query=queries[b], key=layers[b].key, value=layers[b].value,
-                                 softmax_scale=SCALE, lam=config.lam)
+                                 softmax_scale=SCALE, lam=config.lam,
+                                 device_scores=state.workspace.selection.scores[b])
             ws = state.workspace
             view = lambda obj, names: type("V", (), {n: getattr(obj, n)[b] for n in names})
             assert_step_equal(
@@ -236,7 +244,8 @@ def test_standalone_entry_points_and_skip_update():
         deltas=mutable.deltas, segments=segments, sink_positions=sinks,
         current_position=converted.current_position, softmax_scale=SCALE, workspace=ws.attention,
         update_state=mutable, update_workspace=None, update_lam=0.5, positions=ws.selection.positions)
-    want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=0.5, update=False)
+    want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=0.5, update=False,
+                     device_scores=ws.selection.scores)
     assert_step_equal(selection=ws.selection, attention=ws.attention, update=ws.update, result=want,
                       check_update=False)
     assert_state_equal(mutable, twin.state, "skip-update leaves the state untouched")
@@ -260,7 +269,8 @@ def test_topk_communities_mode_and_underfill():
     for step in range(3):
         query = make_query(seed=700 + step, query_heads=16)
         runtime.decode(layer_idx=0, query=query.to(device)[None], key=key, value=value, softmax_scale=SCALE)
-        want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=0.5)
+        want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=0.5,
+                         device_scores=state.workspace.selection.scores[0])
         ws = state.workspace
         view = lambda obj, names: type("V", (), {n: getattr(obj, n)[0] for n in names})
         assert int(ws.selection.descriptor_counts.max()) <= 5
@@ -289,7 +299,8 @@ def test_overflow_flags_stop_the_cursor():
         query = make_query(seed=800 + step, query_heads=4)
         runtime.decode(layer_idx=0, query=query.to(device)[None, :, None, :], key=key, value=value,
                        softmax_scale=SCALE)
-        want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=0.5)
+        want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=0.5,
+                         device_scores=state.workspace.selection.scores)
         assert torch.equal(state.workspace.update.overflow.cpu(), want.overflow), step
         assert_state_equal(state.converted.mutable, twin.state, f"step {step}")
         assert torch.equal(state.converted.current_position.cpu(), twin.current)

@@ -49,7 +49,8 @@ def test_four_shards_match_the_unsharded_layer(aggregation):
         query = make_query(seed=1000 + step, query_heads=8)
         current = int(twin.current[0])
         out = decode_emulated(shards, query.to(device), layer.key[:, current].to(device), SCALE)
-        want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=0.5)
+        want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=0.5,
+                         device_scores=shards[0].workspace.selection.scores)
         diff = (out.float().cpu() - want.output.float()).abs()
         assert float(diff.max()) <= OUTPUT_MAX_ABS and float(diff.mean()) <= OUTPUT_MEAN_ABS, step
         for rank, shard in enumerate(shards):
