@@ -1,12 +1,15 @@
-"""Host/torch assembly of the decode state from community labels.
+"""Assembly of the decode state from community labels.
 
 Produces the layout the decode kernels consume - per-community member lists in
-recency-descending order, e4m3 mean-key centroids with decode headroom, and the
-retrieval-head -> (graph, KV head) maps - with the semantics of the reference's
-``build_member_csr``, ``compute_centroids`` and ``aggregation_mappings``
-(``community_kv/graph/partition.py:71-94, 382-492``).  Plain torch ops that run
-on CPU or GPU tensors; the Leiden partition that produces the labels stays on
-the host and is not part of this package.
+recency-descending order, e4m3 mean-key centroids with decode headroom, the
+modularity bookkeeping and the retrieval-head -> (graph, KV head) maps - with the
+semantics of the reference's ``build_member_csr``, ``compute_centroids``,
+``init_modularity_state`` and ``aggregation_mappings``
+(``community_kv/graph/partition.py:71-94, 382-535``).  CUDA tensors go through the
+assembly kernels of the CUDA library (``ckv_assemble_*``; bf16 keys); CPU tensors
+take a plain torch path that exists for building fixtures and synthetic workloads
+on the host.  The Leiden partition that produces the labels stays on the host and
+is not part of this package.
 """
 
 from __future__ import annotations
@@ -49,6 +52,8 @@ def build_member_csr(
 
     graphs, length = community_ids.shape
     widest = int(community_counts.max())
+    if community_ids.is_cuda:
+        return _member_csr_cuda(community_ids, widest, num_sink)
     labels = community_ids[:, num_sink:].long()
     where = torch.arange(num_sink, length, device=community_ids.device).expand(graphs, -1)
     order = (labels * length + (length - 1 - where)).argsort(dim=1)
@@ -84,6 +89,8 @@ def compute_centroids(
     live = int(community_counts.max())
     capacity = live + max_decode_tokens
     dim = keys.shape[-1]
+    if community_ids.is_cuda and keys.dtype == torch.bfloat16 and dim == 128:
+        return _centroids_cuda(community_ids, keys, retrieval_to_graph, retrieval_to_kv, live, capacity, num_sink)
     labels = community_ids[retrieval_to_graph.long(), num_sink:].long()
     rows = keys[retrieval_to_kv.long(), num_sink:].float()
     sums = torch.zeros((heads, capacity, dim), dtype=torch.float32, device=keys.device)
@@ -92,6 +99,92 @@ def compute_centroids(
     sizes.scatter_add_(1, labels, torch.ones_like(labels, dtype=torch.int32))
     sums[:, :live] /= sizes[:, :live].float().clamp_min(1).unsqueeze(-1)
     return sums.clamp_(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), sizes
+
+
+def _native():
+    from community_kv_b200 import native
+
+    return native
+
+
+def _check(status: int) -> None:
+    if status:
+        native = _native()
+        raise native.NativeError(native.library().ckv_status_string(status).decode())
+
+
+def _member_csr_cuda(community_ids: torch.Tensor, widest: int, num_sink: int) -> tuple[torch.Tensor, torch.Tensor]:
+    native = _native()
+    graphs, length = community_ids.shape
+    labels = community_ids.to(torch.int32).contiguous()
+    device = labels.device
+    counts = torch.empty((graphs, widest), dtype=torch.int32, device=device)
+    offsets = torch.empty((graphs, widest + 1), dtype=torch.int32, device=device)
+    positions = torch.empty((graphs, length - num_sink), dtype=torch.int32, device=device)
+    with torch.cuda.device(device):
+        _check(native.library().ckv_assemble_member_csr(
+            labels.data_ptr(), graphs, length, num_sink, widest, counts.data_ptr(), offsets.data_ptr(),
+            positions.data_ptr(), length - num_sink, native.current_stream(device)))
+    return offsets, positions
+
+
+def _centroids_cuda(community_ids, keys, retrieval_to_graph, retrieval_to_kv, live, capacity, num_sink):
+    native = _native()
+    device = keys.device
+    counts = torch.full((community_ids.shape[0],), live, dtype=torch.int32, device=device)
+    offsets, positions = build_member_csr(community_ids, counts, num_sink=num_sink)
+    heads = retrieval_to_graph.numel()
+    if keys.stride(-1) != 1:
+        keys = keys.contiguous()
+    centroids = torch.empty((heads, capacity, 128), dtype=torch.float8_e4m3fn, device=device)
+    sizes = torch.empty((heads, capacity), dtype=torch.int32, device=device)
+    to_graph = retrieval_to_graph.to(torch.int32).contiguous()
+    to_kv = retrieval_to_kv.to(torch.int32).contiguous()
+    with torch.cuda.device(device):
+        _check(native.library().ckv_assemble_centroids(
+            offsets.data_ptr(), positions.data_ptr(), live, positions.shape[1], keys.data_ptr(),
+            keys.stride(0), keys.stride(1), to_graph.data_ptr(), to_kv.data_ptr(), heads, live, capacity,
+            centroids.data_ptr(), sizes.data_ptr(), native.current_stream(device)))
+    return centroids, sizes
+
+
+def init_modularity_state(
+    community_ids: torch.Tensor,
+    edge_src: torch.Tensor,
+    edge_dst: torch.Tensor,
+    edge_weight: torch.Tensor,
+    *,
+    community_capacity: int,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Community weights ``[graphs, capacity]`` and total weight ``[graphs]`` of an edge list whose
+    vertices are flat ``graph * length + position`` indices (the reference's
+    ``init_modularity_state``, ``community_kv/graph/partition.py:495-535``)."""
+
+    graphs, length = community_ids.shape
+    device = community_ids.device
+    weight = torch.zeros((graphs, community_capacity), dtype=torch.float32, device=device)
+    total = torch.zeros((graphs,), dtype=torch.float32, device=device)
+    if not edge_src.numel():
+        return weight, total
+    if community_ids.is_cuda:
+        native = _native()
+        labels = community_ids.to(torch.int32).contiguous()
+        source, destination = edge_src.long().contiguous(), edge_dst.long().contiguous()
+        values = edge_weight.float().contiguous()
+        with torch.cuda.device(device):
+            _check(native.library().ckv_assemble_modularity(
+                labels.data_ptr(), graphs, length, source.data_ptr(), destination.data_ptr(), values.data_ptr(),
+                source.numel(), community_capacity, weight.data_ptr(), total.data_ptr(),
+                native.current_stream(device)))
+        return weight, total
+    source, destination = edge_src.long(), edge_dst.long()
+    graph = source // length
+    flat = weight.view(-1)
+    values = edge_weight.float()
+    flat.scatter_add_(0, graph * community_capacity + community_ids[graph, source % length].long(), values)
+    flat.scatter_add_(0, graph * community_capacity + community_ids[graph, destination % length].long(), values)
+    total.scatter_add_(0, graph, 2.0 * values)
+    return weight, total
 
 
 @dataclass(slots=True)
@@ -176,4 +269,5 @@ __all__ = [
     "assemble_layer",
     "build_member_csr",
     "compute_centroids",
+    "init_modularity_state",
 ]

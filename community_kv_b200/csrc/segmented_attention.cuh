@@ -82,8 +82,11 @@ __device__ __forceinline__ void attention_split(const ckv_layer_args& a, int fla
   const int32_t* positions = a.positions + static_cast<int64_t>(flat) * a.token_budget;
   // With a sequence-sharded cache only rows [begin, begin+count) are local: other
   // selected rows become masked slots here and are attended to by their owner.
+  // A row at or beyond the cache's capacity (the cursor of a full cache, a corrupt member
+  // list) is a masked slot too: it is never read.
   const int row_begin = a.kv_row_count > 0 ? a.kv_row_begin : 0;
-  const int row_end = a.kv_row_count > 0 ? a.kv_row_begin + a.kv_row_count : 0x7fffffff;
+  const int row_end = a.kv_row_count > 0 ? min(a.kv_row_begin + a.kv_row_count, a.sequence_capacity)
+                                         : a.sequence_capacity;
   auto local_row = [&](int pos) { return (pos >= row_begin && pos < row_end) ? pos - row_begin : -1; };
   const __nv_bfloat16* key_head = reinterpret_cast<const __nv_bfloat16*>(a.key) +
                                   u.batch * a.key_batch_stride + u.kv * a.key_head_stride;

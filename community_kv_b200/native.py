@@ -186,6 +186,9 @@ ENTRY_POINTS = (
     "ckv_wait_peers",
     "ckv_append_kv",
     "ckv_merge_partials",
+    "ckv_assemble_member_csr",
+    "ckv_assemble_centroids",
+    "ckv_assemble_modularity",
 )
 
 
@@ -222,6 +225,13 @@ def library() -> ctypes.CDLL:
     lib.ckv_append_kv.restype = ctypes.c_int
     lib.ckv_append_kv.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p,
                                   ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]
+    _p, _i, _l = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
+    lib.ckv_assemble_member_csr.restype = ctypes.c_int
+    lib.ckv_assemble_member_csr.argtypes = [_p, _i, _i, _i, _i, _p, _p, _p, _i, _p]
+    lib.ckv_assemble_centroids.restype = ctypes.c_int
+    lib.ckv_assemble_centroids.argtypes = [_p, _p, _i, _i, _p, _l, _l, _p, _p, _i, _i, _i, _p, _p, _p]
+    lib.ckv_assemble_modularity.restype = ctypes.c_int
+    lib.ckv_assemble_modularity.argtypes = [_p, _i, _i, _p, _p, _p, _l, _i, _p, _p, _p]
     lib.ckv_wait_peers.restype = ctypes.c_int
     lib.ckv_wait_peers.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p]
     lib.ckv_prefill_topk.restype = ctypes.c_int

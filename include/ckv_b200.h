@@ -29,6 +29,9 @@
  *                            (third_party/flash_attention/community-kv.patch)
  *   ckv_append_kv            the cache layer's index_copy_ of the decoded token
  *                            community_kv/attention/cache.py:29-36
+ *   ckv_assemble_member_csr, ckv_assemble_centroids, ckv_assemble_modularity
+ *                            build_member_csr, compute_centroids, init_modularity_state
+ *                            community_kv/graph/partition.py:382-535
  * Without a counterpart in the (single-GPU) reference: ckv_online_update, ckv_merge_partials,
  * ckv_wait_peers and the peer_* fields (KV heads or sequence rows sharded over GPUs),
  * ckv_segmented_attention_static, ckv_decode_layer_kernels.
@@ -301,6 +304,39 @@ int ckv_online_update(const ckv_layer_args* args, void* cuda_stream);
  * sequence-sharded decoding every GPU all-gathers the GPUs' `merged` / `merged_topk`
  * records and calls this with splits = number of GPUs; no reference counterpart. */
 int ckv_merge_partials(const ckv_layer_args* args, void* cuda_stream);
+
+/* ---- decode-state assembly from community labels (the step between a finished partition
+ * and the first decode step; the reference runs it as torch sort / scatter operations) ---- */
+
+/* Member lists.  labels int32 [graphs, length] (community id of every position; sinks are the
+ * first num_sink positions and are left out).  Writes offsets int32 [graphs, communities + 1]
+ * and member_positions int32 [graphs, member_capacity >= length - num_sink]: the positions of
+ * community c are member_positions[g, offsets[g, c] .. offsets[g, c + 1]), newest first.
+ * `counts` is int32 scratch [graphs, communities].  Replaces build_member_csr
+ * (community_kv/graph/partition.py:457-492). */
+int ckv_assemble_member_csr(const int32_t* labels, int32_t graphs, int32_t length, int32_t num_sink,
+                            int32_t communities, int32_t* counts, int32_t* offsets,
+                            int32_t* member_positions, int32_t member_capacity, void* cuda_stream);
+
+/* Centroids.  For every retrieval head h and community c < capacity: sizes[h, c] = members of c
+ * in graph retrieval_to_graph[h], centroids[h, c, :] = e4m3(clamp(mean of the members' key rows
+ * of KV head retrieval_to_kv[h])) (zero rows beyond `live`; the sum runs over the members oldest
+ * first in fp32).  keys bf16 [KV heads, rows, 128] with element strides.  Replaces
+ * compute_centroids (community_kv/graph/partition.py:382-455). */
+int ckv_assemble_centroids(const int32_t* offsets, const int32_t* member_positions, int32_t communities,
+                           int32_t member_capacity, const void* keys, int64_t key_head_stride,
+                           int64_t key_row_stride, const int32_t* retrieval_to_graph,
+                           const int32_t* retrieval_to_kv, int32_t heads, int32_t live, int32_t capacity,
+                           void* centroids, int32_t* sizes, void* cuda_stream);
+
+/* Modularity bookkeeping.  Edge e joins flat vertices edge_src[e], edge_dst[e] (graph * length +
+ * position, int64) with weight edge_weight[e]: community_weight[g, label] += w for both end
+ * points, total_weight[g] += 2 w (both outputs are cleared first).  Replaces
+ * init_modularity_state (community_kv/graph/partition.py:495-535). */
+int ckv_assemble_modularity(const int32_t* labels, int32_t graphs, int32_t length, const int64_t* edge_src,
+                            const int64_t* edge_dst, const float* edge_weight, int64_t edges,
+                            int32_t capacity, float* community_weight, float* total_weight,
+                            void* cuda_stream);
 
 /* P1.  Causal attention (output + lse) that also emits each row's strongest
  * Q.K neighbours: the reference's top-8 rule (mode 1) or exact top-m per KV head

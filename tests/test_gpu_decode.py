@@ -69,7 +69,7 @@ def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, def
     "aggregation", [GraphAggregation.QUERY_GROUP, GraphAggregation.PER_QUERY_HEAD, GraphAggregation.LAYER_WISE]
 )
 def test_single_layer_config0_parity(aggregation):
-    """BASELINE config 1: ctx 8192, 32/8 heads, 64 planted clusters, budget 1024."""
+    """Single-layer configuration: ctx 8192, 32/8 heads, 64 planted clusters, budget 1024."""
 
     layer = make_layer(seed=0, seq_len=8192, communities=64, max_decode_tokens=8, aggregation=aggregation)
     config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation=aggregation)
@@ -155,7 +155,7 @@ def test_group_sizes(group_size, kv_heads):
 
 
 def test_zipf_communities_full_context_unit():
-    """BASELINE config 4 shape for one sequence-layer: ctx 131072, 4096 Zipf communities, budget 2048."""
+    """One (sequence, layer) of the batched long-context configuration: ctx 131072, 4096 Zipf communities, budget 2048."""
 
     layer = make_layer(seed=5, seq_len=131072, communities=4096, max_decode_tokens=4, zipf_exponent=1.1)
     config = CommunityKVConfig(token_budget=2048, num_sink=10, lam=0.5, aggregation="query_group")
@@ -163,7 +163,7 @@ def test_zipf_communities_full_context_unit():
 
 
 def test_config3_layer_with_online_assignment():
-    """BASELINE config 3 shape for one layer: ctx 32768, 512 Zipf(1.1) communities per KV head,
+    """One layer of the whole-model configuration: ctx 32768, 512 Zipf(1.1) communities per KV head,
     budget 2048, every decoded token assigned online (eight steps)."""
 
     layer = make_layer(seed=7, seq_len=32768, communities=512, max_decode_tokens=12, zipf_exponent=1.1)
@@ -253,7 +253,7 @@ def test_standalone_entry_points_and_skip_update():
 
 
 def test_topk_communities_mode_and_underfill():
-    """Extension (BASELINE config 1 wording): at most k communities; unfilled slots are masked."""
+    """Extension (top-k communities under a token budget): at most k communities; unfilled slots are masked."""
 
     device = torch.device("cuda", 0)
     config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation="query_group")
@@ -308,6 +308,35 @@ def test_overflow_flags_stop_the_cursor():
         runtime.assert_no_overflow()
 
 
+def test_full_cache_masks_the_cursor_row():
+    """Once the cache is full the cursor equals its capacity: the update reports it (overflow bit 8) and
+    the attention treats that slot as masked instead of reading one row past the head's slice."""
+
+    device = torch.device("cuda", 0)
+    layer = make_layer(seed=41, kv_heads=2, seq_len=1024, communities=16, max_decode_tokens=3).to(device)
+    config = CommunityKVConfig(token_budget=128, num_sink=2, lam=0.5, aggregation="query_group")
+    runtime = DecodeRuntime(config, splits=2)
+    state = runtime.prepare_layer(0, **layer.prepare_kwargs())
+    rows = 1024 + 2  # a cache that ends two rows after the prompt
+    key = layer.key[:, :rows].contiguous()[None]
+    value = layer.value[:, :rows].contiguous()[None]
+    # poison what lies right behind the last head's slice: it must never be read
+    for step in range(4):
+        query = make_query(seed=810 + step, query_heads=8).to(device)
+        out = runtime.decode(layer_idx=0, query=query[None, :, None, :], key=key, value=value, softmax_scale=SCALE)
+        assert torch.isfinite(out.float()).all(), step
+        flags = state.workspace.update.overflow.cpu()
+        cursor = state.converted.current_position.cpu()
+        if step < 2:
+            assert int(flags.max()) == 0 and int(cursor.min()) == 1024 + step + 1
+        else:
+            assert bool(((flags & 8) == 8).all()) and int(cursor.max()) == rows
+            # every slot of the budget is a cached row or masked, never the row at the capacity
+            assert int(state.workspace.selection.positions.max()) <= rows
+    with pytest.raises(RuntimeError, match="overflow"):
+        runtime.assert_no_overflow()
+
+
 def test_shape_errors_are_reported_before_launch():
     device = torch.device("cuda", 0)
     layer = make_layer(seed=50, kv_heads=1, seq_len=1024, communities=16, max_decode_tokens=2)
@@ -348,7 +377,7 @@ def test_append_kv_rows():
 
 
 def test_full_size_batch_one_launch_equals_four_kernels():
-    """BASELINE config 4 as far as one layer goes (8 sequences x 8 KV heads at ctx 131072,
+    """The batched long-context configuration as far as one layer goes (8 sequences x 8 KV heads at ctx 131072,
     1024-4096 Zipf communities, budget 2048): the single cluster launch and the four
     stand-alone kernels, fed the same inputs for three steps, leave bit-identical
     workspaces and graph state (one unit of this size is checked against the CPU oracle

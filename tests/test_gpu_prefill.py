@@ -127,7 +127,7 @@ def test_batch_and_validation():
 
 
 def test_full_size_properties():
-    """BASELINE config 2 at full size (S = 16384, 32 / 8 heads, 256 planted clusters): sampled rows
+    """The prefill configuration at full size (S = 16384, 32 / 8 heads, 256 planted clusters): sampled rows
     against fp32 torch arithmetic - attention within tolerance; every edge's score is the group
     maximum of that key, edges are sorted, and nothing outside the list beats the last edge."""
 

@@ -66,7 +66,7 @@ def test_four_shards_match_the_unsharded_layer(aggregation):
 
 
 def test_large_context_shards_agree_with_one_gpu():
-    """BASELINE config 5 shape (scaled to 262144 tokens so that two replicas fit comfortably):
+    """The sequence-sharded stress configuration (scaled to 262144 tokens so that two replicas fit comfortably):
     16384 planted clusters per head, budget 8192.  Two row shards against the whole cache in one
     piece: same selection, same neighbours and labels bit for bit, outputs within 2e-2."""
 
