@@ -187,6 +187,84 @@ def init_modularity_state(
     return weight, total
 
 
+def reshape_by_aggregation(
+    topk_indices: torch.Tensor,
+    topk_scores: torch.Tensor,
+    *,
+    aggregation: GraphAggregation | str,
+    num_kv_heads: int,
+    num_sink: int,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Per-query-head prefill edges ``[Hq, rows, kappa]`` -> per-graph rows and their positions.
+
+    Row ``i`` of the prefill kernel's output belongs to position ``kappa - 1 + num_sink + i``;
+    a graph that several query heads share gets those heads' rows one after the other (the
+    reference's ``_reshape_by_aggregation``, ``community_kv/graph/partition.py:96-147``).
+    """
+
+    aggregation = GraphAggregation(aggregation)
+    heads, rows, kappa = topk_indices.shape
+    group = heads // num_kv_heads
+    first = kappa - 1 + num_sink
+    positions = torch.arange(first, first + rows, dtype=torch.int64, device=topk_indices.device)
+    if aggregation is GraphAggregation.PER_QUERY_HEAD:
+        return topk_indices, topk_scores, positions.unsqueeze(0).expand(heads, -1)
+    if aggregation is GraphAggregation.QUERY_GROUP:
+        return (
+            topk_indices.reshape(num_kv_heads, group * rows, kappa),
+            topk_scores.reshape(num_kv_heads, group * rows, kappa),
+            positions.repeat(group).unsqueeze(0).expand(num_kv_heads, -1),
+        )
+    return (
+        topk_indices.reshape(1, heads * rows, kappa),
+        topk_scores.reshape(1, heads * rows, kappa),
+        positions.repeat(heads).unsqueeze(0),
+    )
+
+
+def build_adjacency(
+    topk_indices: torch.Tensor,
+    topk_scores: torch.Tensor,
+    query_positions: torch.Tensor,
+    *,
+    seq_len: int,
+    lam: float,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Coalesced undirected edge list ``(src int32, dst int32, weight fp32)`` of the batched graph.
+
+    CUDA tensors only (``ckv_build_adjacency``): this is the consumer of the prefill kernel's
+    edges, there is no host variant.  Same result as the reference's ``build_adjacency``
+    (``community_kv/graph/partition.py:168-249``), with the duplicate weights added in the
+    reference's enumeration order.
+    """
+
+    if not topk_indices.is_cuda:
+        raise ValueError("build_adjacency runs on CUDA tensors")
+    if topk_indices.ndim != 3 or topk_scores.shape != topk_indices.shape:
+        raise ValueError("top-k tensors must have shape [graphs, rows, kappa]")
+    native = _native()
+    graphs, rows, kappa = topk_indices.shape
+    device = topk_indices.device
+    indices = topk_indices.to(torch.int32).contiguous()
+    scores = topk_scores.float().contiguous()
+    positions = query_positions.to(torch.int64).expand(graphs, rows).contiguous()
+    lib = native.library()
+    raw = int(lib.ckv_adjacency_raw_edges(graphs, rows, kappa, float(lam)))
+    scratch = torch.empty((int(lib.ckv_adjacency_scratch_bytes(graphs, rows, kappa, float(lam))),),
+                          dtype=torch.uint8, device=device)
+    source = torch.empty((raw,), dtype=torch.int32, device=device)
+    destination = torch.empty((raw,), dtype=torch.int32, device=device)
+    weight = torch.empty((raw,), dtype=torch.float32, device=device)
+    count = torch.zeros((1,), dtype=torch.int64, device=device)
+    with torch.cuda.device(device):
+        _check(lib.ckv_build_adjacency(
+            indices.data_ptr(), scores.data_ptr(), positions.data_ptr(), graphs, rows, kappa, int(seq_len),
+            float(lam), source.data_ptr(), destination.data_ptr(), weight.data_ptr(), raw, count.data_ptr(),
+            scratch.data_ptr(), scratch.numel(), native.current_stream(device)))
+    edges = int(count.item())
+    return source[:edges], destination[:edges], weight[:edges]
+
+
 @dataclass(slots=True)
 class AssembledLayer:
     """Everything ``DecodeRuntime.prepare_layer`` takes, built from labels and keys."""
@@ -267,7 +345,9 @@ __all__ = [
     "AssembledLayer",
     "aggregation_mappings",
     "assemble_layer",
+    "build_adjacency",
     "build_member_csr",
     "compute_centroids",
     "init_modularity_state",
+    "reshape_by_aggregation",
 ]

@@ -189,6 +189,9 @@ ENTRY_POINTS = (
     "ckv_assemble_member_csr",
     "ckv_assemble_centroids",
     "ckv_assemble_modularity",
+    "ckv_adjacency_raw_edges",
+    "ckv_adjacency_scratch_bytes",
+    "ckv_build_adjacency",
 )
 
 
@@ -232,6 +235,11 @@ def library() -> ctypes.CDLL:
     lib.ckv_assemble_centroids.argtypes = [_p, _p, _i, _i, _p, _l, _l, _p, _p, _i, _i, _i, _p, _p, _p]
     lib.ckv_assemble_modularity.restype = ctypes.c_int
     lib.ckv_assemble_modularity.argtypes = [_p, _i, _i, _p, _p, _p, _l, _i, _p, _p, _p]
+    for name in ("ckv_adjacency_raw_edges", "ckv_adjacency_scratch_bytes"):
+        getattr(lib, name).restype = ctypes.c_int64
+        getattr(lib, name).argtypes = [_l, _l, _i, ctypes.c_double]
+    lib.ckv_build_adjacency.restype = ctypes.c_int
+    lib.ckv_build_adjacency.argtypes = [_p, _p, _p, _i, _l, _i, _i, ctypes.c_double, _p, _p, _p, _l, _p, _p, _l, _p]
     lib.ckv_wait_peers.restype = ctypes.c_int
     lib.ckv_wait_peers.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p]
     lib.ckv_prefill_topk.restype = ctypes.c_int

@@ -32,6 +32,7 @@
  *   ckv_assemble_member_csr, ckv_assemble_centroids, ckv_assemble_modularity
  *                            build_member_csr, compute_centroids, init_modularity_state
  *                            community_kv/graph/partition.py:382-535
+ *   ckv_build_adjacency      build_adjacency  community_kv/graph/partition.py:168-249
  * Without a counterpart in the (single-GPU) reference: ckv_online_update, ckv_merge_partials,
  * ckv_wait_peers and the peer_* fields (KV heads or sequence rows sharded over GPUs),
  * ckv_segmented_attention_static, ckv_decode_layer_kernels.
@@ -337,6 +338,24 @@ int ckv_assemble_modularity(const int32_t* labels, int32_t graphs, int32_t lengt
                             const int64_t* edge_dst, const float* edge_weight, int64_t edges,
                             int32_t capacity, float* community_weight, float* total_weight,
                             void* cuda_stream);
+
+/* Edge list -> coalesced adjacency: what the host partitioner consumes.  topk_indices int32 and
+ * topk_scores fp32 are [graphs, rows, kappa] (neighbour position per row, -1 or >= seq_len:
+ * none), query_positions int64 [graphs, rows] the position a row belongs to.  A row contributes
+ * kappa direct edges (weight score * lam / 2) and, for lam < 1, kappa (kappa + 1) / 2
+ * co-attention edges between its neighbours (weight score_a * score_b * (1 - lam)); edges are
+ * stored as (min, max) over vertices graph * seq_len + position, duplicates merged by adding
+ * their weights in enumeration order (the scale factors are lam / 2 and 1 - lam rounded to fp32
+ * once, as a Python float times an fp32 tensor gives), output sorted by (min, max): edge_src / edge_dst int32,
+ * edge_weight fp32, *edge_count the number of distinct edges (device int64; edges beyond
+ * edge_capacity are counted but not stored).  scratch: ckv_adjacency_scratch_bytes() bytes,
+ * 256-byte aligned.  Replaces build_adjacency (community_kv/graph/partition.py:168-249). */
+int64_t ckv_adjacency_raw_edges(int64_t graphs, int64_t rows, int32_t kappa, double lam);
+int64_t ckv_adjacency_scratch_bytes(int64_t graphs, int64_t rows, int32_t kappa, double lam);
+int ckv_build_adjacency(const int32_t* topk_indices, const float* topk_scores, const int64_t* query_positions,
+                        int32_t graphs, int64_t rows, int32_t kappa, int32_t seq_len, double lam,
+                        int32_t* edge_src, int32_t* edge_dst, float* edge_weight, int64_t edge_capacity,
+                        int64_t* edge_count, void* scratch, int64_t scratch_bytes, void* cuda_stream);
 
 /* P1.  Causal attention (output + lse) that also emits each row's strongest
  * Q.K neighbours: the reference's top-8 rule (mode 1) or exact top-m per KV head

@@ -2,7 +2,7 @@
 
 Run from anywhere, in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference [group ...]
 
 It imports the reference package (``community_kv``) and the semantic helpers
 that live in the reference's own unit tests, feeds them seeded random inputs and
@@ -27,7 +27,9 @@ REFERENCE = Path(sys.argv[1])
 sys.path.insert(0, str(REFERENCE))
 
 from community_kv.graph.partition import (  # noqa: E402
+    _reshape_by_aggregation,
     aggregation_mappings,
+    build_adjacency,
     build_member_csr,
     compute_centroids,
 )
@@ -291,6 +293,47 @@ def online_update_cases(rng: np.random.Generator) -> dict[str, np.ndarray]:
     return out
 
 
+def adjacency_cases(rng: np.random.Generator) -> dict[str, np.ndarray]:
+    """Prefill edges -> coalesced adjacency (build_adjacency) and the per-graph reshaping of the edges."""
+
+    out: dict[str, np.ndarray] = {}
+    shapes = [(1, 2, 2, 4, 1.0), (1, 2, 2, 4, 0.5), (3, 40, 8, 64, 0.5), (2, 75, 8, 90, 0.0),
+              (4, 60, 5, 33, 0.25), (8, 128, 8, 200, 0.7), (2, 300, 8, 310, 1.0)]
+    for case, (graphs, rows, kappa, length, lam) in enumerate(shapes):
+        indices = rng.integers(-2, length + 3, size=(graphs, rows, kappa)).astype(np.int32)
+        if case % 2:
+            indices[:, :, 1] = indices[:, :, 0]  # duplicated neighbours inside a row
+        scores = rng.uniform(0.0, 1.0, size=(graphs, rows, kappa)).astype(np.float32)
+        positions = rng.integers(0, length, size=(graphs, rows)).astype(np.int64)
+        source, destination, weight = build_adjacency(
+            torch.from_numpy(indices), torch.from_numpy(scores), torch.from_numpy(positions),
+            seq_len=length, lam=lam,
+        )
+        out[f"indices_{case}"] = indices
+        out[f"scores_{case}"] = scores
+        out[f"positions_{case}"] = positions
+        out[f"scalars_{case}"] = np.array([length, lam], dtype=np.float64)
+        out[f"source_{case}"] = source.numpy()
+        out[f"destination_{case}"] = destination.numpy()
+        out[f"weight_{case}"] = weight.numpy()
+    out["cases"] = np.arange(len(shapes))
+    heads, kv_heads, rows, kappa, sink = 8, 2, 21, 8, 3
+    indices = torch.from_numpy(rng.integers(0, 40, size=(heads, rows, kappa)).astype(np.int32))
+    scores = torch.from_numpy(rng.uniform(size=(heads, rows, kappa)).astype(np.float32))
+    for index, mode in enumerate(("per_query_head", "query_group", "layer_wise")):
+        shaped = _reshape_by_aggregation(
+            indices, scores, aggregation=__import__("community_kv").GraphAggregation(mode),
+            num_kv_heads=kv_heads, num_sink=sink,
+        )
+        out[f"reshape_indices_{index}"] = shaped[0].numpy()
+        out[f"reshape_scores_{index}"] = shaped[1].numpy()
+        out[f"reshape_positions_{index}"] = shaped[2].numpy()
+    out["reshape_inputs_indices"] = indices.numpy()
+    out["reshape_inputs_scores"] = scores.numpy()
+    out["reshape_meta"] = np.array([heads, kv_heads, rows, kappa, sink], dtype=np.int64)
+    return out
+
+
 def main() -> None:
     groups = {
         "selection": selection_cases,
@@ -298,8 +341,12 @@ def main() -> None:
         "positions": position_cases,
         "assembly": assembly_cases,
         "online_update": online_update_cases,
+        "adjacency": adjacency_cases,
     }
+    wanted = set(sys.argv[2:])
     for seed, (name, builder) in enumerate(groups.items()):
+        if wanted and name not in wanted:
+            continue
         arrays = builder(np.random.default_rng(1000 + seed))
         np.savez_compressed(HERE / f"{name}.npz", **arrays)
         print(name, len(arrays), "arrays")

@@ -129,3 +129,49 @@ def test_assembled_layer_on_the_device_equals_the_host_one():
             torch.testing.assert_close(b, a, rtol=1e-6, atol=0, msg=name)
         else:
             assert torch.equal(a, b), name
+
+
+# ---- edge list -> adjacency -----------------------------------------------------------------------
+def _adjacency_equal(got, want, where):
+    source, destination, weight = (t.cpu().numpy() for t in got)
+    assert np.array_equal(source, want[0]), where
+    assert np.array_equal(destination, want[1]), where
+    assert np.array_equal(weight.view(np.int32), want[2].view(np.int32)), where  # fp32 sums bit for bit
+
+
+def test_adjacency_fixture_from_the_reference(golden_dir):
+    from community_kv_b200.assembly import build_adjacency
+
+    device = torch.device("cuda", 0)
+    data = np.load(golden_dir / "adjacency.npz")
+    for case in data["cases"].tolist():
+        length, lam = int(data[f"scalars_{case}"][0]), float(data[f"scalars_{case}"][1])
+        got = build_adjacency(torch.from_numpy(data[f"indices_{case}"]).to(device),
+                              torch.from_numpy(data[f"scores_{case}"]).to(device),
+                              torch.from_numpy(data[f"positions_{case}"]).to(device), seq_len=length, lam=lam)
+        _adjacency_equal(got, (data[f"source_{case}"], data[f"destination_{case}"], data[f"weight_{case}"]),
+                         f"case {case}")
+
+
+@pytest.mark.parametrize("graphs,rows,length,lam", [(8, 4 * 4000, 4096, 0.5), (2, 30000, 32768, 0.5),
+                                                    (1, 50000, 131072, 1.0)])
+def test_adjacency_against_the_cpu_restatement(graphs, rows, length, lam):
+    """Sizes of a real prefill (causal neighbours, hub keys, several heads sharing a graph): every
+    distinct edge, in order, with its weight summed in the reference's order."""
+
+    from community_kv_b200.assembly import build_adjacency
+    from oracle.adjacency_oracle import build_adjacency as oracle_adjacency
+
+    device = torch.device("cuda", 0)
+    rng = np.random.default_rng(rows)
+    positions = rng.integers(20, length, size=(graphs, rows)).astype(np.int64)
+    # neighbours are earlier positions, a few of them shared hubs; some slots are empty
+    indices = (positions[..., None] * rng.uniform(0, 1, size=(graphs, rows, 8))).astype(np.int32)
+    hubs = rng.integers(0, 64, size=(graphs, rows, 8)).astype(np.int32)
+    indices = np.where(rng.uniform(size=indices.shape) < 0.2, hubs, indices)
+    indices = np.where(rng.uniform(size=indices.shape) < 0.05, -1, indices).astype(np.int32)
+    scores = rng.uniform(0, 1, size=indices.shape).astype(np.float32)
+    want = oracle_adjacency(indices, scores, positions, seq_len=length, lam=lam)
+    got = build_adjacency(torch.from_numpy(indices).to(device), torch.from_numpy(scores).to(device),
+                          torch.from_numpy(positions).to(device), seq_len=length, lam=lam)
+    _adjacency_equal(got, want, f"{graphs}x{rows}")

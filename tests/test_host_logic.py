@@ -253,7 +253,7 @@ def test_batched_stack_pads_and_views():
 # ---- the C ABI surface ---------------------------------------------------------------------
 def test_library_exports_every_declared_symbol():
     header = (ROOT / "include" / "ckv_b200.h").read_text()
-    declared = set(re.findall(r"^(?:int|const char\*)\s+(ckv_\w+)\s*\(", header, flags=re.M))
+    declared = set(re.findall(r"^(?:int|int64_t|const char\*)\s+(ckv_\w+)\s*\(", header, flags=re.M))
     assert declared == set(native.ENTRY_POINTS)
     lib = native.library()
     for name in declared:

@@ -364,3 +364,43 @@ def test_attention_unit_matches_dense_softmax():
     order = np.argsort(-np.where(valid & (np.arange(tokens) >= 5), scores[0], -np.inf), kind="stable")[:8]
     assert top_positions.tolist() == (order * 3).tolist()
     assert np.array_equal(top_scores, scores[0][order])
+
+
+# ---- edge list -> adjacency ---------------------------------------------------------------------
+def test_adjacency_oracle_known_answers_of_the_reference_tests():
+    """tests/community_kv/graph/test_partition.py:212-248 of the reference."""
+
+    from oracle.adjacency_oracle import build_adjacency
+
+    indices = np.array([[[1, 2], [2, 1]]], dtype=np.int32)
+    source, destination, weight = build_adjacency(indices, np.ones_like(indices, dtype=np.float32),
+                                                  np.array([[2, 3]]), seq_len=4, lam=1.0)
+    assert {(int(a), int(b)): float(w) for a, b, w in zip(source, destination, weight)} == {
+        (1, 2): 0.5, (2, 2): 0.5, (1, 3): 0.5, (2, 3): 0.5}
+    indices = np.array([[[1, 4], [-1, 5]]], dtype=np.int32)
+    source, destination, weight = build_adjacency(indices, np.ones_like(indices, dtype=np.float32),
+                                                  np.array([[2, 3]]), seq_len=4, lam=0.5)
+    assert {(int(a), int(b)): float(w) for a, b, w in zip(source, destination, weight)} == {
+        (1, 1): 0.5, (1, 2): 0.25}
+
+
+def test_adjacency_oracle_matches_reference_fixture(golden_dir):
+    from community_kv_b200.assembly import reshape_by_aggregation
+    from oracle.adjacency_oracle import build_adjacency
+
+    data = np.load(golden_dir / "adjacency.npz")
+    for case in data["cases"].tolist():
+        length, lam = int(data[f"scalars_{case}"][0]), float(data[f"scalars_{case}"][1])
+        source, destination, weight = build_adjacency(data[f"indices_{case}"], data[f"scores_{case}"],
+                                                      data[f"positions_{case}"], seq_len=length, lam=lam)
+        assert np.array_equal(source, data[f"source_{case}"]), case
+        assert np.array_equal(destination, data[f"destination_{case}"]), case
+        assert np.array_equal(weight.view(np.int32), data[f"weight_{case}"].view(np.int32)), case
+    heads, kv_heads, rows, kappa, sink = data["reshape_meta"].tolist()
+    indices = torch.from_numpy(data["reshape_inputs_indices"])
+    scores = torch.from_numpy(data["reshape_inputs_scores"])
+    for index, mode in enumerate(("per_query_head", "query_group", "layer_wise")):
+        shaped = reshape_by_aggregation(indices, scores, aggregation=mode, num_kv_heads=kv_heads, num_sink=sink)
+        assert np.array_equal(shaped[0].numpy(), data[f"reshape_indices_{index}"]), mode
+        assert np.array_equal(shaped[1].numpy(), data[f"reshape_scores_{index}"]), mode
+        assert np.array_equal(shaped[2].numpy(), data[f"reshape_positions_{index}"]), mode
