@@ -13,7 +13,14 @@ from dataclasses import dataclass
 
 import torch
 
-from community_kv_b200.assembly import AssembledLayer, aggregation_mappings, assemble_layer
+from community_kv_b200.assembly import (
+    AssembledLayer,
+    aggregation_mappings,
+    assemble_layer,
+    build_adjacency,
+    init_modularity_state,
+    reshape_by_aggregation,
+)
 from community_kv_b200.config import GraphAggregation
 
 HEAD_DIM = 128
@@ -205,12 +212,15 @@ class SyntheticPartitioner:
     """Stand-in for the host-side Leiden partitioner: random labels with Zipf-sized communities.
 
     Callable with the keyword arguments ``CommunityKVRuntime.submit_prefill_layer`` passes
-    to its ``partitioner``.  The neighbour edges are accepted and ignored: the labels are
-    drawn per (layer, graph) from a seeded generator, ``communities`` per graph with sizes
-    proportional to ``rank ** -zipf_exponent`` (or equal sizes of contiguous position blocks
-    with ``zipf_exponent=None``), and the decode state is assembled from them with the same
-    layout rules as a real partition (``community_kv_b200.assembly``).  For benchmarks and
-    tests that need a whole model running through the plug-in without a graph partitioner.
+    to its ``partitioner``.  Everything around the partition itself is the real pipeline: on
+    CUDA tensors the prefill edges are regrouped per graph and coalesced into the adjacency a
+    partitioner would be handed (``assembly.build_adjacency``), the modularity weights of the
+    labels are taken from that adjacency (``assembly.init_modularity_state``), and the decode
+    state is assembled by the assembly kernels.  Only the labels are synthetic: drawn per
+    (layer, graph) from a seeded generator, ``communities`` per graph with sizes proportional
+    to ``rank ** -zipf_exponent`` (or equal sizes of contiguous position blocks with
+    ``zipf_exponent=None``).  For benchmarks and tests that need a whole model running through
+    the plug-in without a graph partitioner.
     """
 
     def __init__(self, *, communities: int, zipf_exponent: float | None = 1.1, seed: int = 0) -> None:
@@ -220,10 +230,12 @@ class SyntheticPartitioner:
         self.zipf_exponent = zipf_exponent
         self.seed = seed
         self.edges_seen: dict[int, tuple[int, ...]] = {}
+        self.adjacency_edges: dict[int, int] = {}
 
     def __call__(self, *, layer_idx: int, topk_indices: torch.Tensor, topk_scores: torch.Tensor,
                  keys: torch.Tensor, num_sink: int, max_decode_tokens: int,
-                 aggregation: GraphAggregation | str, **_: object) -> SyntheticPartitionedLayer:
+                 aggregation: GraphAggregation | str, lam: float = 0.5,
+                 **_: object) -> SyntheticPartitionedLayer:
         aggregation = GraphAggregation(aggregation)
         kv_heads, length, _dim = keys.shape
         query_heads = int(topk_indices.shape[0])
@@ -239,9 +251,20 @@ class SyntheticPartitioner:
                 sizes = zipf_sizes(length, count, self.zipf_exponent, generator)
                 ids = torch.repeat_interleave(torch.arange(count), sizes)[torch.randperm(length, generator=generator)]
             labels[graph] = ids
+        labels = labels.to(torch.int32).to(keys.device)
+        weights: dict[str, torch.Tensor] = {}
+        if keys.is_cuda:
+            shaped = reshape_by_aggregation(topk_indices, topk_scores, aggregation=aggregation,
+                                            num_kv_heads=kv_heads, num_sink=num_sink)
+            source, destination, weight = build_adjacency(*shaped, seq_len=length, lam=lam)
+            self.adjacency_edges[layer_idx] = int(source.numel())
+            capacity = int(labels.max()) + 1 + max_decode_tokens
+            community_weight, total_weight = init_modularity_state(
+                labels, source.long(), destination.long(), weight, community_capacity=capacity)
+            weights = dict(community_weight=community_weight, total_weight=total_weight)
         assembled = assemble_layer(
-            labels.to(torch.int32).to(keys.device), keys, aggregation=aggregation, query_heads=query_heads,
-            num_sink=num_sink, max_decode_tokens=max_decode_tokens,
+            labels, keys, aggregation=aggregation, query_heads=query_heads,
+            num_sink=num_sink, max_decode_tokens=max_decode_tokens, **weights,
         )
         return SyntheticPartitionedLayer(
             layer_idx=layer_idx,

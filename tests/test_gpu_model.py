@@ -61,6 +61,8 @@ def test_generate_through_the_plugin_matches_dense_attention(aggregation):
         # both layers went through the prefill kernel and handed their edges to the partitioner
         assert set(partitioner.edges_seen) == {0, 1}
         assert partitioner.edges_seen[0] == (8, prompt_length - (4 + 7), 8)
+        # ... which coalesced them into a graph (direct and co-attention edges of 244 rows per head)
+        assert all(edges > 244 * 8 for edges in partitioner.adjacency_edges.values())
         for layer in runtime.decode_runtime.layers.values():
             assert layer.workspace.selection.token_budget == 256
             steps = new_tokens - 1  # the first new token comes out of the prefill
