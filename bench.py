@@ -564,7 +564,8 @@ def run_b200(args: argparse.Namespace) -> None:
             "score": stat(span(0, 1)),
             "select_wait_for_cluster": stat(span(1, 2)),
             "select_exchanges": stat(span(2, 5)),
-            "select_detail": {"2_3": stat(span(2, 3)), "3_4": stat(span(3, 4)), "4_5": stat(span(4, 5))},
+            "select_detail": {"histograms": stat(span(2, 3)), "threshold_scan_publish": stat(span(3, 4)),
+                              "count": stat(span(4, 5))},
             "resolve_positions": stat(span(5, 6)),
             "gather_attention": stat(span(6, 7)),
             "wait_for_cluster": stat(span(7, 8, slice(0, 1))),

@@ -63,7 +63,6 @@ __global__ void __launch_bounds__(kFusedThreads, 3) decode_cluster_kernel(const 
     }
   }
   pdl_wait_for_predecessor();  // the query and last step's state come from upstream
-
   // ---- 1. centroid scores: this CTA's share of the unit's 16-row groups; the keys
   // stay in shared memory and are counted into the slice's histogram on the way ----
   ClusterSelectSmem& sm = *reinterpret_cast<ClusterSelectSmem*>(smem);
@@ -72,8 +71,15 @@ __global__ void __launch_bounds__(kFusedThreads, 3) decode_cluster_kernel(const 
   const int last_group = static_cast<int>(static_cast<int64_t>(split + 1) * groups / a.splits);
   phase_stamp(a, flat, split, 0);
   cluster_select_begin<kFusedThreads>(sm);
+  // last step's threshold of this unit (-1 before the first step): its high byte is the guess
+  int guess_bin = -1;
+  if (a.threshold_state != nullptr) {
+    const int previous = a.threshold_state[static_cast<int64_t>(flat) * 4];
+    guess_bin = previous >= 0 ? (previous >> 8) & 0xff : -1;
+  }
   {
-    const ScoreSlice slice = {sm.key, sm.size, sm.hist_mass, sm.hist_count, first_group * 16};
+    const ScoreSlice slice = {sm.key,       sm.size,      sm.hist_mass, sm.hist_count, first_group * 16,
+                              sm.low_mass,  sm.low_count, guess_bin};
     score_groups<kFusedThreads, kClusterStageBytes>(a, flat, first_group, last_group, sm.query, &slice);
   }
   __syncthreads();
@@ -87,7 +93,7 @@ __global__ void __launch_bounds__(kFusedThreads, 3) decode_cluster_kernel(const 
     const int row0 = first_group * 16;
     const int rows = min(score_limit(a, flat), last_group * 16) - row0;
     select_cluster<kFusedThreads>(a, flat, sm, split, a.splits, row0, rows,
-                                  step_begin * kStepTokens, step_end * kStepTokens);
+                                  step_begin * kStepTokens, step_end * kStepTokens, guess_bin);
   }
   __syncthreads();  // positions written above are read by other threads of this CTA
   phase_stamp(a, flat, split, 6);

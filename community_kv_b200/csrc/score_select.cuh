@@ -53,6 +53,12 @@ struct ScoreSlice {
   int* hist_mass;    // 256 bins over the high key byte, weighted by size
   int* hist_count;
   int row0;
+  // Speculation: last step's threshold usually falls into the same high-byte bin again.
+  // Rows whose key lies in `guess_bin` (-1: none) are also counted by their low byte, so
+  // that the second histogram pass of the selection is already done if the guess holds.
+  int* low_mass;
+  int* low_count;
+  int guess_bin;
 };
 
 template <int kThreads, bool kNarrow>
@@ -236,6 +242,10 @@ __device__ __forceinline__ void score_groups_impl(const ckv_layer_args& a, int f
         if (live) {
           atomicAdd(&slice_out->hist_mass[key >> 8], size);
           atomicAdd(&slice_out->hist_count[key >> 8], 1);
+          if ((key >> 8) == slice_out->guess_bin) {
+            atomicAdd(&slice_out->low_mass[key & 0xff], size);
+            atomicAdd(&slice_out->low_count[key & 0xff], 1);
+          }
         }
       }
     }
@@ -380,6 +390,10 @@ __device__ __forceinline__ void score_groups_mma(const ckv_layer_args& a, int fl
         if (live) {
           atomicAdd(&slice_out->hist_mass[key >> 8], size);
           atomicAdd(&slice_out->hist_count[key >> 8], 1);
+          if ((key >> 8) == slice_out->guess_bin) {
+            atomicAdd(&slice_out->low_mass[key & 0xff], size);
+            atomicAdd(&slice_out->low_count[key & 0xff], 1);
+          }
         }
       }
     }
@@ -891,10 +905,12 @@ struct ClusterSelectSmem {
   int low_count[256];
   int sum_mass[256];      // cluster-wide sums (private)
   int sum_count[256];
+  int before_mass[256];   // sums over the slices in front of this one (private)
+  int before_count[256];
   Quad scan_scratch[32];
   Quad scan_total;
   int stored_equal;       // stored at-threshold communities of all slices (every owner adds here)
-  int bin, mass, count, descriptors;
+  int bin, mass, count, front_mass, front_count, descriptors;
 };
 static_assert(offsetof(ClusterSelectSmem, key) == kClusterStageBytes, "staging area must be contiguous");
 
@@ -917,10 +933,11 @@ __device__ __forceinline__ void cluster_select_begin(ClusterSelectSmem& sm) {
 // histogram are already filled by score_groups).  Every CTA of the cluster calls
 // this; on return sm.desc_* hold all descriptors and the logical tokens
 // [token_begin, token_end) are resolved to cache rows.
+// `guess_bin`: the high-byte bin score_groups counted the low bytes of (-1: none).
 template <int kThreads>
 __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat, ClusterSelectSmem& sm,
                                                int rank, int ranks, int row0, int rows,
-                                               int token_begin, int token_end) {
+                                               int token_begin, int token_end, int guess_bin) {
   const Unit u = make_unit(a, flat);
   const int tid = threadIdx.x;
   const int capacity = a.community_capacity;
@@ -949,6 +966,10 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
       if (size > 0) {
         atomicAdd(&sm.hist_mass[key >> 8], size);
         atomicAdd(&sm.hist_count[key >> 8], 1);
+        if ((key >> 8) == guess_bin) {
+          atomicAdd(&sm.low_mass[key & 0xff], size);
+          atomicAdd(&sm.low_count[key & 0xff], 1);
+        }
       }
     }
     rows = active_here - row0;
@@ -963,10 +984,13 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
   // for the slices before this one, without another exchange.
   constexpr int kBins = 256 / kThreads;
   static_assert(kBins * kThreads == 256, "thread count must divide 256");
+  // Sum a pair of 256-bin histograms over the cluster.  Each thread owns 256 / kThreads
+  // bins and reads every slice's values (all loads in flight together); it writes the sum
+  // over all slices and the sum over the slices in front of this one.
   constexpr int kMaxRanks = 8;
-  int part_mass[kBins][kMaxRanks];
-  int part_count[kBins][kMaxRanks];
   auto gather = [&](const int* mass, const int* count) {
+    int part_mass[kBins][kMaxRanks];
+    int part_count[kBins][kMaxRanks];
 #pragma unroll
     for (int k = 0; k < kBins; ++k) {
 #pragma unroll
@@ -978,94 +1002,93 @@ __device__ __forceinline__ void select_cluster(const ckv_layer_args& a, int flat
     }
 #pragma unroll
     for (int k = 0; k < kBins; ++k) {
-      int total_mass = 0;
-      int total_count = 0;
+      int total_mass = 0, total_count = 0, before_mass = 0, before_count = 0;
 #pragma unroll
       for (int r = 0; r < kMaxRanks; ++r) {
         total_mass += part_mass[k][r];
         total_count += part_count[k][r];
+        if (r < rank) {
+          before_mass += part_mass[k][r];
+          before_count += part_count[k][r];
+        }
       }
       sm.sum_mass[tid + k * kThreads] = total_mass;
       sm.sum_count[tid + k * kThreads] = total_count;
+      sm.before_mass[tid + k * kThreads] = before_mass;
+      sm.before_count[tid + k * kThreads] = before_count;
     }
     __syncthreads();
   };
-  // (count, mass) over the bins above `bin`: all slices, and the slices before this one
-  auto above = [&](int bin) {
-    Quad v = {0, 0, 0, 0};
+  // Warp 0: the threshold bin of the summed histogram, the totals above it, and the totals
+  // above it of the slices in front of this one.
+  auto find = [&](int start_mass, int start_count) {
+    if (tid < 32) {
+      find_threshold_bin(sm.sum_mass, sm.sum_count, budget, limit, start_mass, start_count, &sm.bin,
+                         &sm.mass, &sm.count);
+      __syncwarp();
+      const int bin = sm.bin;
+      int mass = 0, count = 0;
 #pragma unroll
-    for (int k = 0; k < kBins; ++k) {
-      if (tid + k * kThreads > bin) {
-#pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r) {
-          v.high_count += part_count[k][r];
-          v.high_mass += part_mass[k][r];
-          if (r < rank) {
-            v.equal_count += part_count[k][r];
-            v.equal_mass += part_mass[k][r];
-          }
+      for (int b = 0; b < 8; ++b) {
+        if (tid * 8 + b > bin) {
+          mass += sm.before_mass[tid * 8 + b];
+          count += sm.before_count[tid * 8 + b];
         }
       }
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1) {
+        mass += __shfl_xor_sync(0xffffffffu, mass, offset);
+        count += __shfl_xor_sync(0xffffffffu, count, offset);
+      }
+      if (tid == 0) {
+        sm.front_mass = mass;
+        sm.front_count = count;
+      }
     }
-    Quad total;
-    block_scan<kThreads / 32>(v, sm.scan_scratch, &sm.scan_total);
-    total = sm.scan_total;
-    __syncthreads();  // scan_total is reused
-    return total;
+    __syncthreads();
   };
 
   gather(sm.hist_mass, sm.hist_count);
-  if (tid < 32) {
-    find_threshold_bin(sm.sum_mass, sm.sum_count, budget, limit, 0, 0, &sm.bin, &sm.mass, &sm.count);
-  }
-  __syncthreads();
+  find(0, 0);
   const int high_bin = sm.bin;
   const int mass_above = sm.mass;
   const int count_above = sm.count;
-  const Quad coarse = above(high_bin);
-  // Pass 2: low byte inside the chosen high bin, this slice only.
-  for (int i = tid; i < rows; i += kThreads) {
-    const int size = sm.size[i];
-    const int key = sm.key[i];
-    if (size > 0 && (key >> 8) == high_bin) {
-      atomicAdd(&sm.low_mass[key & 0xff], size);
-      atomicAdd(&sm.low_count[key & 0xff], 1);
+  const int coarse_front_mass = sm.front_mass;
+  const int coarse_front_count = sm.front_count;
+  __syncthreads();  // the find results are read before the next find overwrites them
+  // Pass 2: low byte inside the chosen high bin, this slice only - unless scoring has
+  // already counted exactly that bin (every CTA sees the same high bin and the same guess,
+  // so all of them take the same branch, and the slices' low histograms were complete at
+  // the barrier above: no second barrier is needed then).
+  if (high_bin != guess_bin) {
+    if (guess_bin >= 0) {
+      for (int bin = tid; bin < 256; bin += kThreads) {
+        sm.low_mass[bin] = 0;
+        sm.low_count[bin] = 0;
+      }
+      __syncthreads();
     }
-  }
-  cluster_sync_all();
-  phase_stamp(a, flat, rank, 3);
-  gather(sm.low_mass, sm.low_count);
-  if (tid < 32) {
-    find_threshold_bin(sm.sum_mass, sm.sum_count, budget, limit, mass_above, count_above, &sm.bin,
-                       &sm.mass, &sm.count);
-  }
-  __syncthreads();
-  const int low_bin = sm.bin;
-  const int threshold = (high_bin << 8) | low_bin;
-  const Quad fine = above(low_bin);
-  // at-threshold communities of the slices before this one: the owner of that bin knows
-  if (tid == (low_bin % kThreads)) {
-    const int k = low_bin / kThreads;
-    int count_before = 0;
-    int mass_before = 0;
-#pragma unroll
-    for (int kk = 0; kk < kBins; ++kk) {
-#pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r) {
-        if (kk == k && r < rank) {
-          count_before += part_count[kk][r];
-          mass_before += part_mass[kk][r];
-        }
+    for (int i = tid; i < rows; i += kThreads) {
+      const int size = sm.size[i];
+      const int key = sm.key[i];
+      if (size > 0 && (key >> 8) == high_bin) {
+        atomicAdd(&sm.low_mass[key & 0xff], size);
+        atomicAdd(&sm.low_count[key & 0xff], 1);
       }
     }
-    sm.count = count_before;
-    sm.mass = mass_before;
+    cluster_sync_all();
   }
-  __syncthreads();
-  const Quad before = {coarse.equal_count + fine.equal_count, coarse.equal_mass + fine.equal_mass,
-                       sm.count, sm.mass};
-  const int total_high_count = coarse.high_count + fine.high_count;
-  const int total_high_mass = coarse.high_mass + fine.high_mass;
+  phase_stamp(a, flat, rank, 3);
+  gather(sm.low_mass, sm.low_count);
+  find(mass_above, count_above);
+  const int low_bin = sm.bin;
+  const int threshold = (high_bin << 8) | low_bin;
+  // above the threshold: all slices (the search counted on from the coarse totals), and the
+  // slices in front of this one; at the threshold: the slices in front of this one
+  const int total_high_count = sm.count;
+  const int total_high_mass = sm.mass;
+  const Quad before = {coarse_front_count + sm.front_count, coarse_front_mass + sm.front_mass,
+                       sm.before_count[low_bin], sm.before_mass[low_bin]};
 
   // Pass 3: this slice in index order.
   const int per_thread = (rows + kThreads - 1) / kThreads;
