@@ -64,6 +64,7 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--layers-per-launch", type=int, default=1)
     parser.add_argument("--cpu-seconds", type=float, default=15.0)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-prefill", action="store_true", help="skip the prefill kernel's sub-record")
     parser.add_argument("--seed", type=int, default=0)
     parser.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                         help="N>1: head outputs by in-kernel peer stores (default) or an NCCL all-gather per layer")
@@ -639,7 +640,13 @@ def run_b200(args: argparse.Namespace) -> None:
     centroid_bytes = sum(work.community_counts) * HEAD_DIM
     step_bytes = centroid_bytes + launches * units_per_launch * kv_bytes_per_unit
     layer_bytes = step_bytes // launches  # centroids + selected KV of one launch (mean over layers)
-    layer_gbs = layer_bytes / (layer_launch_ms * 1e-3) / 1e9
+    # Average duration of a layer launch inside the timed region: the launches of a step run
+    # back to back on the stream, each starting its prologue under the tail of the one before
+    # (programmatic dependent launch), so the step time divided by the launches is what one
+    # launch costs there.  `launch_ms_isolated` is the same launch bracketed by events of its own.
+    launch_ms_in_step = ms_per_step / launches
+    layer_gbs = layer_bytes / (launch_ms_in_step * 1e-3) / 1e9
+    isolated_gbs = layer_bytes / (layer_launch_ms * 1e-3) / 1e9
     step_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
 
     traffic, traffic_source = measured_traffic(units_per_launch, kernels_per_layer)
@@ -677,7 +684,9 @@ def run_b200(args: argparse.Namespace) -> None:
             "traffic": traffic,
             "traffic_source": traffic_source,
             "algorithmic_bytes_per_launch": layer_bytes,
-            "launch_ms": layer_launch_ms,
+            "launch_ms": launch_ms_in_step,
+            "launch_ms_isolated": layer_launch_ms,
+            "frac_isolated": isolated_gbs / peak,
             "kernels_per_layer": kernels_per_layer,
             "attention_kernel_alone": {
                 "achieved": attention_gbs,
@@ -706,8 +715,14 @@ def run_b200(args: argparse.Namespace) -> None:
         "clocks": clocks,
         "build_seconds": build_seconds,
     }
+    if world == 1 and not args.no_prefill:
+        # the other kernel of the path, measured in the same run: prefill score-graph emission
+        del work, packed, attend_args, update_args, solo, attn_args
+        torch.cuda.empty_cache()
+        line["prefill"] = measure_prefill(args, device, steps=5, warmup=3)
+        work = None
     if world == 1 and not args.no_cpu_baseline:
-        del work
+        work = None
         torch.cuda.empty_cache()
         line["cpu_baseline"] = cpu_baseline(args.cpu_seconds, args.context, args.layers)
     print(json.dumps(line), flush=True)
@@ -729,15 +744,13 @@ def finish(world: int, dist) -> None:
         os._exit(0)
 
 
-def run_prefill(args: argparse.Namespace) -> None:
-    """Prefill score-graph emission: one layer, 32/8 heads, causal, planted clusters."""
+def measure_prefill(args: argparse.Namespace, device, steps: int, warmup: int) -> dict:
+    """Times the prefill score-graph emission kernel: one layer, 32/8 heads, causal, planted key clusters."""
 
     import torch
 
     from community_kv_b200.prefill import prefill_attention, prefill_attention_edges, prefill_attention_topk
 
-    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(device)
     length = args.prefill_length
     generator = torch.Generator(device=device).manual_seed(args.seed)
     centres = torch.randn((KV_HEADS, 256, HEAD_DIM), generator=generator, device=device)
@@ -755,27 +768,58 @@ def run_prefill(args: argparse.Namespace) -> None:
         "exact_top16_per_kv_head": lambda: prefill_attention_edges(
             query, key, value, softmax_scale=SCALE, num_sink=NUM_SINK, edges_per_row=16),
     }
-    sampler = ClockSampler(device.index or 0)
-    sampler.start()
     timings = {}
     rescanned = None
     for name, run in variants.items():
-        for _ in range(max(args.warmup, 3)):
+        for _ in range(max(warmup, 3)):
             result = run()
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             result = run()
         end.record()
         torch.cuda.synchronize()
-        timings[name] = begin.elapsed_time(end) / args.steps
+        timings[name] = begin.elapsed_time(end) / steps
         if name == "exact_top16_per_kv_head":
             rescanned = int(result[4].sum())
-    clocks = sampler.stop()
     headline = timings["exact_top16_per_kv_head"]
+    return {
+        "workload": "prefill score-graph emission: 1 layer, 32 Q / 8 KV heads, head_dim 128, "
+                    f"S={length}, causal, 256 planted key clusters",
+        "variants_ms": timings,
+        "rows_rescanned": rescanned,
+        "steps": steps,
+        "flops": flops,
+        "roofline": {
+            "kernel": "prefill_kernel (tcgen05 Q.K^T and P.V)",
+            "bound": "tensor",
+            "achieved": flops / (timings["attention_only"] * 1e-3) / 1e12,
+            "achieved_with_reference_top8": flops / (timings["reference_top8"] * 1e-3) / 1e12,
+            "achieved_with_edges": flops / (headline * 1e-3) / 1e12,
+            "peak": peak,
+            "unit": "TFLOP/s",
+            "frac": flops / (timings["attention_only"] * 1e-3) / 1e12 / peak,
+            "traffic": None,
+        },
+    }
+
+
+def run_prefill(args: argparse.Namespace) -> None:
+    """Prefill score-graph emission as a line of its own."""
+
+    import torch
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    record = measure_prefill(args, device, args.steps, args.warmup)
+    clocks = sampler.stop()
+    headline = record["variants_ms"]["exact_top16_per_kv_head"]
     line = {
-        "metric": "prefill score-graph emission, ms per layer (S=%d, 32/8 heads, top-16 edges per KV head)" % length,
+        "metric": "prefill score-graph emission, ms per layer (S=%d, 32/8 heads, top-16 edges per KV head)"
+                  % args.prefill_length,
         "value": headline,
         "unit": "ms",
         "n_gpus": 1,
@@ -787,20 +831,10 @@ def run_prefill(args: argparse.Namespace) -> None:
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": "prefill score-graph emission: 1 layer, 32 Q / 8 KV heads, head_dim 128, "
-                               f"S={length}, causal, 256 planted key clusters", "l2": "each step streams 2*S*8*256 B of K/V per query tile"},
-        "variants_ms": timings,
-        "rows_rescanned": rescanned,
-        "roofline": {
-            "kernel": "prefill_kernel (tcgen05 Q.K^T and P.V)",
-            "bound": "tensor",
-            "achieved": flops / (timings["attention_only"] * 1e-3) / 1e12,
-            "achieved_with_edges": flops / (headline * 1e-3) / 1e12,
-            "peak": peak,
-            "unit": "TFLOP/s",
-            "frac": flops / (timings["attention_only"] * 1e-3) / 1e12 / peak,
-            "traffic": None,
-        },
+        "config": {"workload": record["workload"], "l2": "each step streams 2*S*8*256 B of K/V per query tile"},
+        "variants_ms": record["variants_ms"],
+        "rows_rescanned": record["rows_rescanned"],
+        "roofline": record["roofline"],
         "gpu_launches": args.steps * 3,
         "clocks": clocks,
     }

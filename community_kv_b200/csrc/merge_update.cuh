@@ -214,17 +214,23 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
       free_chunk = a.next_free_chunk[graph_slot];
       free_position = a.next_free_position[graph_slot];
     }
+    // eight rounds of "warp-wide maximum, then retire it"; only the registers that hold
+    // candidates take part (two of the eight with up to eight splits)
     for (int k = 0; k < kKappa && !update_only; ++k) {
       uint64_t local = 0ull;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        local = mine[i] > local ? mine[i] : local;
+        if (32 * i < total) {
+          local = mine[i] > local ? mine[i] : local;
+        }
       }
       const uint64_t best = warp_max_u64(local);
       if (best != 0ull) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          mine[i] = mine[i] == best ? 0ull : mine[i];
+          if (32 * i < total) {
+            mine[i] = mine[i] == best ? 0ull : mine[i];
+          }
         }
       }
       if (lane == k) {
