@@ -27,188 +27,9 @@
 // columns j % G == lane, and a second kernel re-scores that short list in the
 // fixed fp32 order shared with the CPU oracle and emits the exact top-m.
 
-#include <cuda.h>
-#include <cudaTypedefs.h>
-
-#include "ckv_device.cuh"
+#include "tc_primitives.cuh"
 
 namespace ckv {
-
-constexpr int kPfThreads = 256;
-constexpr int kPfRows = 128;
-constexpr int kPfKeys = 128;
-constexpr int kTileBytes = kPfRows * kHeadDim * 2;  // 32 KiB
-constexpr int kLocalK = 6;
-constexpr int kExactKeep = 16;
-constexpr uint32_t kBarrierPolls = 1u << 22;
-
-__device__ __forceinline__ uint32_t core_offset(int row, int chunk) {
-  // 8 rows x 16 bytes form one contiguous 128-byte core matrix; the row groups of
-  // one 16-byte column chunk are adjacent (so a chunk is 128 rows x 16 B = 2048 B,
-  // exactly what one slice of the K/V tensor-map box writes), chunks are 2048
-  // bytes apart.
-  return static_cast<uint32_t>(chunk * 2048 + row * 16);
-}
-
-__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t leading_bytes,
-                                                    uint32_t stride_bytes) {
-  return static_cast<uint64_t>((address & 0x3ffffu) >> 4) |
-         (static_cast<uint64_t>(leading_bytes >> 4) << 16) |
-         (static_cast<uint64_t>(stride_bytes >> 4) << 32) | (1ull << 46);
-}
-
-// bf16 x bf16 -> fp32, M = 128, N = 128
-__device__ __forceinline__ uint32_t instruction_descriptor(bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) |
-         ((kPfKeys >> 3) << 17) | ((kPfRows >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                     uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n"
-      "}\n" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    v[i] = __uint_as_float(r[i]);
-  }
-}
-
-__device__ __forceinline__ void tmem_load64(uint32_t taddr, float (&v)[64]) {
-  uint32_t r[64];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,"
-      "%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,"
-      "%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]),
-        "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]),
-        "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
-        "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
-        "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]),
-        "=r"(r[63])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 64; ++i) {
-    v[i] = __uint_as_float(r[i]);
-  }
-}
-
-__device__ __forceinline__ void tmem_store64(uint32_t taddr, const float (&v)[64]) {
-  uint32_t r[64];
-#pragma unroll
-  for (int i = 0; i < 64; ++i) {
-    r[i] = __float_as_uint(v[i]);
-  }
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x64.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63,%64};\n" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(r[32]), "r"(r[33]), "r"(r[34]), "r"(r[35]), "r"(r[36]), "r"(r[37]), "r"(r[38]), "r"(r[39]), "r"(r[40]), "r"(r[41]), "r"(r[42]), "r"(r[43]), "r"(r[44]), "r"(r[45]), "r"(r[46]), "r"(r[47]), "r"(r[48]), "r"(r[49]), "r"(r[50]), "r"(r[51]), "r"(r[52]), "r"(r[53]), "r"(r[54]), "r"(r[55]), "r"(r[56]), "r"(r[57]), "r"(r[58]), "r"(r[59]), "r"(r[60]), "r"(r[61]), "r"(r[62]), "r"(r[63])
-      : "memory");
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-
-// Polls a completion barrier a bounded number of times.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t poll = 0; poll < kBarrierPolls; ++poll) {
-    uint32_t done;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) {
-      return true;
-    }
-    if (poll > 64) {
-      __nanosleep(32);
-    }
-  }
-  return false;
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-
-// One 128-row x 128-column bf16 tile (rows row0.. of one KV head) into shared memory
-// in the operand layout; rows past the end of the sequence arrive as zeros.  The
-// tensor map's dimensions are (8 elements, rows, 16 column chunks, KV heads, batch).
-__device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                              int row0, int kv_head, int batch) {
-  mbar_expect_tx(bar, kTileBytes);
-  asm volatile(
-      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
-      "l"(map), "r"(0), "r"(row0), "r"(0), "r"(kv_head), "r"(batch), "r"(bar)
-      : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void async_proxy_fence() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
-__device__ __forceinline__ uint32_t quantised_key(float raw) {
-  int key = __float2int_rn((raw + 48.0f) * 256.0f);
-  key = max(0, min(key, 32767));
-  return static_cast<uint32_t>(key);
-}
-
-template <int kDepth>
-__device__ __forceinline__ void queue_insert(uint32_t (&queue)[kDepth], uint32_t candidate) {
-#pragma unroll
-  for (int k = 0; k < kDepth; ++k) {
-    const uint32_t resident = queue[k];
-    queue[k] = max(candidate, resident);
-    candidate = min(candidate, resident);
-  }
-}
 
 // Returns the key that fell off the end (the candidate itself when it did not enter).
 __device__ __forceinline__ uint64_t queue_insert64(uint64_t (&queue)[kExactKeep], uint64_t candidate) {
@@ -1093,10 +914,6 @@ __device__ __forceinline__ void tmem_load16_issue(uint32_t taddr, uint32_t (&r)[
       : "r"(taddr));
 }
 
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
 template <int kKeep>
 __device__ __forceinline__ uint64_t list_insert(uint64_t (&list)[kKeep], uint64_t candidate) {
 #pragma unroll
@@ -1378,6 +1195,8 @@ PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
   return encoder;
 }
 
+}  // namespace
+
 // K or V [batch, rows, kv heads, 128] bf16 seen as (8 elements, rows, 16 chunks of
 // 16 bytes, kv heads, batch): one box of (8, 128, 16, 1, 1) lands in shared memory as
 // 16 chunks of 128 rows x 16 bytes, which is the tensor-core operand layout.
@@ -1406,8 +1225,14 @@ bool tile_map(CUtensorMap* map, const void* base, const ckv_prefill_args& a, int
                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+namespace {
+
 template <int kGroup>
 cudaError_t launch_for_group(const ckv_prefill_args& a, cudaStream_t stream) {
+  if constexpr (kGroup % 2 == 0) {
+    // attention alone or with the top-8 rule: two heads of the group per CTA
+    if (a.mode != 2) return launch_prefill_pair(a, stream);
+  }
   constexpr int kSmem = PrefillSmem::kTotal;
   const dim3 grid((a.seq_len + kPfRows / kGroup - 1) / (kPfRows / kGroup), a.kv_heads, a.batch);
   CUtensorMap map_k, map_v;
