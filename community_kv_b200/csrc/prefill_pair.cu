@@ -38,13 +38,46 @@ struct PairSmem {
   static constexpr int kTotal = kBars + 256;
 };
 
+// Operand tiles sit in the 128-byte swizzled layout: [half of the 128 dims][row][128
+// bytes], the 16-byte chunks of a row XOR-ed with the row's low three bits (what a bulk
+// tensor copy with 128-byte swizzle writes); tiles start on 1024-byte boundaries.
+
+// tcgen05.mma with the descriptors given as 32-bit words (both operands share the high word)
+__device__ __forceinline__ void umma_words(uint32_t tmem_d, uint32_t a_low, uint32_t b_low,
+                                           uint32_t high, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 da, {%1, %3};\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, {%6, %6, %6, %6}, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "r"(a_low), "r"(b_low), "r"(high), "r"(idesc), "r"(accumulate ? 1u : 0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_words(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_low,
+                                              uint32_t high, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, {%6, %6, %6, %6}, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "r"(b_low), "r"(high), "r"(idesc), "r"(accumulate ? 1u : 0u), "r"(0u)
+      : "memory");
+}
+
 __device__ __forceinline__ float exp2_fast(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
-// Bounded wait that also gives up when another role of the CTA already has.
+// Bounded wait that also gives up when another role of the CTA already has.  One thread.
 __device__ __forceinline__ bool pair_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort) {
   for (uint32_t poll = 0; poll < kBarrierPolls; ++poll) {
     uint32_t done;
@@ -69,6 +102,30 @@ __device__ __forceinline__ bool pair_wait(uint32_t bar, uint32_t parity, volatil
   }
   *abort = 1u;
   return false;
+}
+
+// The same for a whole warp: lane 0 polls, the others take its word.  The barrier's
+// completion is made visible to the waiting lanes by one successful test of their own.
+__device__ __forceinline__ bool pair_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort) {
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) {
+    ok = pair_wait(bar, parity, abort);
+  }
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  if (ok) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    (void)done;
+  }
+  return ok;
 }
 
 template <int kMode>
@@ -171,22 +228,34 @@ __global__ void __launch_bounds__(kPairThreads, 1)
     if (lane == 0) {
       const uint32_t idesc_qk = instruction_descriptor(false);
       const uint32_t idesc_pv = instruction_descriptor(true);
+      // Descriptors as (low, high) words: the high word (stride between 8-row groups,
+      // version, swizzle mode) is the same for every operand, the low word is the
+      // address in 16-byte units plus the leading-dimension offset; a step along the
+      // reduction only adds a constant to the low word.
+      const uint32_t desc_high = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t q_low = ((q_addr & 0x3ffffu) >> 4) | (1u << 16);
+      const uint32_t k_low = ((k_addr & 0x3ffffu) >> 4) | (1u << 16);
+      const uint32_t v_low = ((v_addr & 0x3ffffu) >> 4) | (((kTileBytes / 2) >> 4) << 16);
       auto issue_qk = [&](int t, int stage) {
+        const uint32_t a_low = q_low + t * (kTileBytes >> 4);
+        const uint32_t b_low = k_low + stage * (kTileBytes >> 4);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t desc_q = smem_descriptor(q_addr + t * kTileBytes + ks * 4096, 2048, 128);
-          const uint64_t desc_k = smem_descriptor(k_addr + stage * kTileBytes + ks * 4096, 2048, 128);
-          umma(tmem + t * 128u, desc_q, desc_k, idesc_qk, ks > 0 ? 1u : 0u);
+          // dims 16 ks .. 16 ks + 15: 32 bytes into the row of the half that holds them
+          const uint32_t within = ((ks >> 2) * (kTileBytes / 2) + (ks & 3) * 32) >> 4;
+          umma_words(tmem + t * 128u, a_low + within, b_low + within, desc_high, idesc_qk, ks > 0);
         }
         umma_commit(bar_s_full + 8 * t);
       };
       auto issue_pv = [&](int t, int stage, bool accumulate) {
+        const uint32_t b_low = v_low + stage * (kTileBytes >> 4);
+        // keys 16 ks .. 16 ks + 15: eight packed columns of P, sixteen 128-byte rows of
+        // V in each half (the halves are the leading dimension, 8-key groups the stride)
+        umma_ts_words(tmem + 256u + t * 128u, tmem + t * 128u, b_low, desc_high, idesc_pv, accumulate);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          // keys 16 ks .. 16 ks + 15: eight packed columns of P, sixteen rows of V
-          const uint64_t desc_v = smem_descriptor(v_addr + stage * kTileBytes + ks * 256, 128, 2048);
-          umma_ts(tmem + 256u + t * 128u, tmem + t * 128u + ks * 8u, desc_v, idesc_pv,
-                  (ks > 0 || accumulate) ? 1u : 0u);
+        for (int ks = 1; ks < 8; ++ks) {
+          umma_ts_words(tmem + 256u + t * 128u, tmem + t * 128u + ks * 8u, b_low + ks * (2048 >> 4),
+                        desc_high, idesc_pv, true);
         }
         umma_commit(bar_o_full + 8 * t);
       };
@@ -257,7 +326,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
 
     for (int block = 0; block < blocks; ++block) {
       const int key0 = block * kPfKeys;
-      if (!__all_sync(0xffffffffu, pair_wait(bar_s_full + 8 * t, block & 1, abort))) {
+      if (!pair_wait_warp(bar_s_full + 8 * t, block & 1, abort)) {
         failed = true;
         break;
       }
@@ -280,11 +349,21 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           s[c] = c <= row ? s[c] : -INFINITY;
         }
       }
-      float tile_max = s[0];
+      // eight independent chains (the compiler keeps the order of a single one)
+      float part_max[8];
 #pragma unroll
-      for (int c = 1; c < 128; ++c) {
-        tile_max = fmaxf(tile_max, s[c]);
+      for (int i = 0; i < 8; ++i) {
+        part_max[i] = fmaxf(s[i], s[i + 8]);
       }
+#pragma unroll
+      for (int c = 16; c < 128; c += 16) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          part_max[i] = fmaxf(part_max[i], fmaxf(s[c + i], s[c + i + 8]));
+        }
+      }
+      const float tile_max = fmaxf(fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])),
+                                   fmaxf(fmaxf(part_max[4], part_max[5]), fmaxf(part_max[6], part_max[7])));
 
       if constexpr (kMode == 1) {
         if (key0 >= a.num_sink) {
@@ -360,7 +439,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         run_sum *= corr;
       }
       if (block > 0 && __any_sync(0xffffffffu, move)) {
-        if (!__all_sync(0xffffffffu, pair_wait(bar_o_full + 8 * t, (block - 1) & 1, abort))) {
+        if (!pair_wait_warp(bar_o_full + 8 * t, (block - 1) & 1, abort)) {
           failed = true;
           break;
         }
@@ -380,6 +459,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       }
       // ---- probabilities, bf16 pairs, over the first 64 columns of this S buffer ----
       const float offset = (run_max == -INFINITY ? 0.f : run_max) * scale_log2;
+      float part_sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int part = 0; part < 2; ++part) {
         uint32_t packed[32];
@@ -388,18 +468,19 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           const int c = part * 64 + 2 * e;
           const float p0 = exp2_fast(fmaf(s[c], scale_log2, -offset));
           const float p1 = exp2_fast(fmaf(s[c + 1], scale_log2, -offset));
-          run_sum += p0 + p1;
+          part_sum[e & 3] += p0 + p1;
           packed[e] = pack_bf16(p0, p1);
         }
         tmem_store32_issue(s_addr + part * 32u, packed);
       }
+      run_sum += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
       tmem_wait_store();
       tc_fence_before();
       mbar_arrive(bar_p_full + 8 * t);
     }
 
     if (!failed) {
-      if (!__all_sync(0xffffffffu, pair_wait(bar_o_full + 8 * t, (blocks - 1) & 1, abort))) {
+      if (!pair_wait_warp(bar_o_full + 8 * t, (blocks - 1) & 1, abort)) {
         failed = true;
       }
     }
@@ -488,9 +569,9 @@ cudaError_t launch_prefill_pair(const ckv_prefill_args& a, cudaStream_t stream) 
     return cudaErrorInvalidValue;
   }
   CUtensorMap map_q, map_k, map_v;
-  if (!tile_map(&map_q, a.query, a, a.query_heads, a.q_row_stride, a.q_head_stride, a.q_batch_stride) ||
-      !tile_map(&map_k, a.key, a, a.kv_heads, a.k_row_stride, a.k_head_stride, a.k_batch_stride) ||
-      !tile_map(&map_v, a.value, a, a.kv_heads, a.v_row_stride, a.v_head_stride, a.v_batch_stride)) {
+  if (!tile_map(&map_q, a.query, a, a.query_heads, a.q_row_stride, a.q_head_stride, a.q_batch_stride, true) ||
+      !tile_map(&map_k, a.key, a, a.kv_heads, a.k_row_stride, a.k_head_stride, a.k_batch_stride, true) ||
+      !tile_map(&map_v, a.value, a, a.kv_heads, a.v_row_stride, a.v_head_stride, a.v_batch_stride, true)) {
     return cudaErrorInvalidValue;
   }
   const dim3 grid((a.seq_len + kPfRows - 1) / kPfRows, a.kv_heads * (group / 2), a.batch);

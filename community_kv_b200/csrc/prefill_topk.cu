@@ -1201,7 +1201,7 @@ PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
 // 16 bytes, kv heads, batch): one box of (8, 128, 16, 1, 1) lands in shared memory as
 // 16 chunks of 128 rows x 16 bytes, which is the tensor-core operand layout.
 bool tile_map(CUtensorMap* map, const void* base, const ckv_prefill_args& a, int heads,
-              int64_t row_stride, int64_t head_stride, int64_t batch_stride) {
+              int64_t row_stride, int64_t head_stride, int64_t batch_stride, bool swizzled) {
   const auto encoder = tensor_map_encoder();
   if (encoder == nullptr || (reinterpret_cast<uintptr_t>(base) & 15u) != 0) {
     return false;
@@ -1215,13 +1215,15 @@ bool tile_map(CUtensorMap* map, const void* base, const ckv_prefill_args& a, int
   if (row_stride <= 0 || (row_bytes & 15u) || (head_bytes & 15u) || (batch_bytes & 15u)) {
     return false;
   }
-  const cuuint64_t extent[5] = {8, static_cast<cuuint64_t>(a.seq_len), 16,
+  const cuuint32_t inner = swizzled ? 64 : 8;  // elements per row piece: 128 or 16 bytes
+  const cuuint64_t extent[5] = {inner, static_cast<cuuint64_t>(a.seq_len), 128 / inner,
                                 static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(a.batch)};
-  const cuuint64_t strides[4] = {row_bytes, 16, head_bytes, batch_bytes};
-  const cuuint32_t box[5] = {8, kPfKeys, 16, 1, 1};
+  const cuuint64_t strides[4] = {row_bytes, inner * 2, head_bytes, batch_bytes};
+  const cuuint32_t box[5] = {inner, kPfKeys, 128 / inner, 1, 1};
   const cuuint32_t steps[5] = {1, 1, 1, 1, 1};
   return encoder(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), extent, strides,
-                 box, steps, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                 box, steps, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                 swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

@@ -235,10 +235,12 @@ __device__ __forceinline__ void tma_issue_tile(uint32_t dst, const CUtensorMap* 
       : "memory");
 }
 
-// K, V or Q [batch, rows, heads, 128] bf16 as a five-dimensional tensor map whose
-// (8, 128, 16, 1, 1) box lands in shared memory in the tensor-core operand layout.
+// K, V or Q [batch, rows, heads, 128] bf16 as a five-dimensional tensor map whose box of
+// 128 rows x 128 dims lands in shared memory in a tensor-core operand layout: 16 chunks
+// of 128 rows x 16 bytes (box (8, 128, 16, 1, 1), no swizzle), or with `swizzled` two
+// halves of 128 rows x 128 bytes in the 128-byte swizzle (box (64, 128, 2, 1, 1)).
 bool tile_map(CUtensorMap* map, const void* base, const ckv_prefill_args& a, int heads,
-              int64_t row_stride, int64_t head_stride, int64_t batch_stride);
+              int64_t row_stride, int64_t head_stride, int64_t batch_stride, bool swizzled = false);
 
 // Attention (mode 0) or attention with the reference's top-8 rule (mode 1) for an even
 // number of query heads per KV head: one CTA per (128 positions, two heads of a group).
