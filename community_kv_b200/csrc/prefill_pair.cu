@@ -34,7 +34,7 @@ struct PairSmem {
   static constexpr int kQ = 0;                  // two query tiles
   static constexpr int kK = 2 * kTileBytes;     // two key stages
   static constexpr int kV = 4 * kTileBytes;     // two value stages
-  static constexpr int kBars = 6 * kTileBytes;  // 15 barriers, the TMEM slot, the abort flag
+  static constexpr int kBars = 6 * kTileBytes;  // barriers, the TMEM slot, the abort flag
   static constexpr int kTotal = kBars + 256;
 };
 
@@ -77,14 +77,36 @@ __device__ __forceinline__ float exp2_fast(float x) {
   return y;
 }
 
+// Two fp32 lanes per instruction (fma.rn.f32x2 / add.f32x2)
+__device__ __forceinline__ uint64_t pack_pair(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_pair(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_pair(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_pair(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 // Bounded wait that also gives up when another role of the CTA already has.  One thread.
+// try_wait parks the thread in hardware for a while instead of spinning.
+constexpr uint32_t kPairPolls = 1u << 18;
 __device__ __forceinline__ bool pair_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort) {
-  for (uint32_t poll = 0; poll < kBarrierPolls; ++poll) {
+  for (uint32_t poll = 0; poll < kPairPolls; ++poll) {
     uint32_t done;
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(done)
@@ -93,11 +115,8 @@ __device__ __forceinline__ bool pair_wait(uint32_t bar, uint32_t parity, volatil
     if (done) {
       return true;
     }
-    if (poll > 32) {
-      __nanosleep(20);
-      if ((poll & 255u) == 0u && *abort != 0u) {
-        return false;
-      }
+    if ((poll & 15u) == 15u && *abort != 0u) {
+      return false;
     }
   }
   *abort = 1u;
@@ -157,8 +176,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   const uint32_t bar_q = smem_u32(bars);
   const uint32_t bar_k_full = smem_u32(bars + 1);   // two stages
   const uint32_t bar_v_full = smem_u32(bars + 3);   // two stages
-  const uint32_t bar_k_free = smem_u32(bars + 5);   // two stages
-  const uint32_t bar_v_free = smem_u32(bars + 7);   // two stages
+  const uint32_t bar_k_free = smem_u32(bars + 5);   // two stages: both tiles' S of that block done
   const uint32_t bar_s_full = smem_u32(bars + 9);   // per tile: S written
   const uint32_t bar_p_full = smem_u32(bars + 11);  // per tile: P written by its 128 threads
   const uint32_t bar_o_full = smem_u32(bars + 13);  // per tile: P.V folded into O
@@ -208,14 +226,16 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       tma_issue_tile(q_addr + kTileBytes, &map_q, bar_q, pos0, head0 + 1, batch);
       for (int block = 0; block < blocks; ++block) {
         const int stage = block & 1;
-        const uint32_t parity = ((block >> 1) - 1) & 1;
-        if (block >= 2 && !pair_wait(bar_k_free + 8 * stage, parity, abort)) {
+        // K(block) goes where K(block - 2) was: free once both tiles' S(block - 2) is done
+        if (block >= 2 && !pair_wait(bar_k_free + 8 * stage, ((block >> 1) - 1) & 1, abort)) {
           failed = true;
           break;
         }
         tma_load_tile(k_addr + stage * kTileBytes, &map_k, bar_k_full + 8 * stage, block * kPfKeys,
                       kv_head, batch);
-        if (block >= 2 && !pair_wait(bar_v_free + 8 * stage, parity, abort)) {
+        // V(block) goes where V(block - 2) was.  S(block - 1) is committed after both
+        // P.V(block - 2) were issued, so that barrier covers the products that read the stage.
+        if (block >= 2 && !pair_wait(bar_k_free + 8 * (stage ^ 1), ((block - 1) >> 1) & 1, abort)) {
           failed = true;
           break;
         }
@@ -246,6 +266,9 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           umma_words(tmem + t * 128u, a_low + within, b_low + within, desc_high, idesc_qk, ks > 0);
         }
         umma_commit(bar_s_full + 8 * t);
+        if (t == 1) {
+          umma_commit(bar_k_free + 8 * stage);
+        }
       };
       auto issue_pv = [&](int t, int stage, bool accumulate) {
         const uint32_t b_low = v_low + stage * (kTileBytes >> 4);
@@ -257,13 +280,11 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           umma_ts_words(tmem + 256u + t * 128u, tmem + t * 128u + ks * 8u, b_low + ks * (2048 >> 4),
                         desc_high, idesc_pv, true);
         }
-        umma_commit(bar_o_full + 8 * t);
       };
       if (pair_wait(bar_q, 0, abort) && pair_wait(bar_k_full, 0, abort)) {
         tc_fence_after();
         issue_qk(0, 0);
         issue_qk(1, 0);
-        umma_commit(bar_k_free);
         for (int block = 0; block < blocks && !failed; ++block) {
           const int stage = block & 1;
           const bool more = block + 1 < blocks;
@@ -279,19 +300,15 @@ __global__ void __launch_bounds__(kPairThreads, 1)
             }
             tc_fence_after();
             issue_pv(t, stage, block > 0);
-            if (t == 1) {
-              umma_commit(bar_v_free + 8 * stage);
-            }
-            if (more) {
+            if (!more) {
+              umma_commit(bar_o_full + 8 * t);
+            } else {
               if (t == 0 && !pair_wait(bar_k_full + 8 * (stage ^ 1), ((block + 1) >> 1) & 1, abort)) {
                 failed = true;
                 break;
               }
               tc_fence_after();
               issue_qk(t, stage ^ 1);
-              if (t == 1) {
-                umma_commit(bar_k_free + 8 * (stage ^ 1));
-              }
             }
           }
         }
@@ -439,11 +456,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         run_sum *= corr;
       }
       if (block > 0 && __any_sync(0xffffffffu, move)) {
-        if (!pair_wait_warp(bar_o_full + 8 * t, (block - 1) & 1, abort)) {
-          failed = true;
-          break;
-        }
-        tc_fence_after();
+        // P.V of the last block is done: this block's S was committed after it
 #pragma unroll
         for (int part = 0; part < 4; ++part) {
           uint32_t o[32];
@@ -459,28 +472,37 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       }
       // ---- probabilities, bf16 pairs, over the first 64 columns of this S buffer ----
       const float offset = (run_max == -INFINITY ? 0.f : run_max) * scale_log2;
-      float part_sum[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint64_t scale_pair = pack_pair(scale_log2, scale_log2);
+      const uint64_t offset_pair = pack_pair(-offset, -offset);
+      uint64_t sum_pair[2] = {0ull, 0ull};
 #pragma unroll
       for (int part = 0; part < 2; ++part) {
         uint32_t packed[32];
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           const int c = part * 64 + 2 * e;
-          const float p0 = exp2_fast(fmaf(s[c], scale_log2, -offset));
-          const float p1 = exp2_fast(fmaf(s[c + 1], scale_log2, -offset));
-          part_sum[e & 3] += p0 + p1;
+          float x0, x1;
+          unpack_pair(fma_pair(pack_pair(s[c], s[c + 1]), scale_pair, offset_pair), x0, x1);
+          const float p0 = exp2_fast(x0);
+          const float p1 = exp2_fast(x1);
+          sum_pair[e & 1] = add_pair(sum_pair[e & 1], pack_pair(p0, p1));
           packed[e] = pack_bf16(p0, p1);
         }
         tmem_store32_issue(s_addr + part * 32u, packed);
       }
-      run_sum += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
+      {
+        float a0, a1, b0, b1;
+        unpack_pair(sum_pair[0], a0, a1);
+        unpack_pair(sum_pair[1], b0, b1);
+        run_sum += (a0 + a1) + (b0 + b1);
+      }
       tmem_wait_store();
       tc_fence_before();
       mbar_arrive(bar_p_full + 8 * t);
     }
 
     if (!failed) {
-      if (!pair_wait_warp(bar_o_full + 8 * t, (blocks - 1) & 1, abort)) {
+      if (!pair_wait_warp(bar_o_full + 8 * t, 0, abort)) {
         failed = true;
       }
     }
