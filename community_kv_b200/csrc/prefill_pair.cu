@@ -147,6 +147,27 @@ __device__ __forceinline__ bool pair_wait_warp(uint32_t bar, uint32_t parity, vo
   return ok;
 }
 
+// Insertion into a descending list by position: every slot decides by two comparisons
+// whether it keeps its entry, takes the candidate or takes its left neighbour's entry.
+template <int kDepth>
+__device__ __forceinline__ void sorted_insert(uint32_t (&queue)[kDepth], uint32_t candidate) {
+  bool keeps[kDepth];
+#pragma unroll
+  for (int k = 0; k < kDepth; ++k) {
+    keeps[k] = queue[k] >= candidate;
+  }
+  uint32_t next[kDepth];
+  next[0] = keeps[0] ? queue[0] : candidate;
+#pragma unroll
+  for (int k = 1; k < kDepth; ++k) {
+    next[k] = keeps[k] ? queue[k] : (keeps[k - 1] ? candidate : queue[k - 1]);
+  }
+#pragma unroll
+  for (int k = 0; k < kDepth; ++k) {
+    queue[k] = next[k];
+  }
+}
+
 template <int kMode>
 __global__ void __launch_bounds__(kPairThreads, 1)
     prefill_pair_kernel(const ckv_prefill_args a, const __grid_constant__ CUtensorMap map_q,
@@ -382,68 +403,6 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       const float tile_max = fmaxf(fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])),
                                    fmaxf(fmaxf(part_max[4], part_max[5]), fmaxf(part_max[6], part_max[7])));
 
-      if constexpr (kMode == 1) {
-        if (key0 >= a.num_sink) {
-          // A key that is below eight keys already held can never reach the output:
-          // the second-best entries of the four classes are eight such keys, and so
-          // are the top four of the two best classes.
-          const uint32_t third0 = q32[0][3], third1 = q32[1][3], third2 = q32[2][3], third3 = q32[3][3];
-          const uint32_t second_of_fourths =
-              max(min(max(third0, third1), max(third2, third3)),
-                  max(min(third0, third1), min(third2, third3)));
-          const uint32_t row_floor = max(min(min(q32[0][1], q32[1][1]), min(q32[2][1], q32[3][1])),
-                                         second_of_fourths);
-          // smallest raw score whose quantised key can reach the floor, a little low
-          const float gate = (row_floor >> 17) == 0u
-                                 ? -3.0e38f
-                                 : (static_cast<float>(row_floor >> 17) - 0.75f) * (1.0f / 256.0f) - 48.0f;
-          // Class by class (32 of the 128 columns each): the columns that reach the gate
-          // as a bit mask, then insertion in rounds - every lane with a pending column
-          // inserts its next one per round.
-          if (__any_sync(0xffffffffu, tile_max >= gate)) {
-#pragma unroll
-            for (int cls = 0; cls < 4; ++cls) {
-              uint32_t takers = 0u;
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const int c = (i >> 1) * 8 + cls * 2 + (i & 1);
-                takers |= (s[c] >= gate ? 1u : 0u) << i;
-              }
-              while (__any_sync(0xffffffffu, takers != 0u)) {
-                if (takers != 0u) {
-                  const int i = __ffs(takers) - 1;
-                  takers &= takers - 1;
-                  float v = s[cls * 2];
-#pragma unroll
-                  for (int k = 1; k < 32; ++k) {
-                    v = i == k ? s[(k >> 1) * 8 + cls * 2 + (k & 1)] : v;
-                  }
-                  const int c = (i >> 1) * 8 + cls * 2 + (i & 1);
-                  const uint32_t candidate =
-                      (quantised_key(v) << 17) | (static_cast<uint32_t>(key0 + c) & 0x1ffffu);
-                  if (candidate > q32[cls][kLocalK - 1]) {
-                    queue_insert<kLocalK>(q32[cls], candidate);
-                  }
-                }
-              }
-            }
-          }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 128; ++c) {
-            const int j = key0 + c;
-            if (s[c] > -INFINITY && j >= a.num_sink) {
-              const uint32_t candidate =
-                  (quantised_key(s[c]) << 17) | (static_cast<uint32_t>(j) & 0x1ffffu);
-              uint32_t(&queue)[kLocalK] = q32[(c & 7) >> 1];
-              if (candidate > queue[kLocalK - 1]) {
-                queue_insert<kLocalK>(queue, candidate);
-              }
-            }
-          }
-        }
-      }
-
       // The running maximum only moves when the new one lies more than 2^8 above it
       // (probabilities up to 256 are harmless in bf16 / fp32); moving it means rescaling
       // the row of O in tensor memory, once the product that still adds to it is done.
@@ -499,6 +458,80 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       tmem_wait_store();
       tc_fence_before();
       mbar_arrive(bar_p_full + 8 * t);
+
+      // The candidate bookkeeping runs from the scores still in registers while the tensor
+      // cores work on this tile's P.V and next S: it is off the path between two blocks.
+      if constexpr (kMode == 1) {
+        if (key0 >= a.num_sink) {
+          // A key that is below eight keys already held can never reach the output:
+          // the second-best entries of the four classes are eight such keys, and so
+          // are the top four of the two best classes.
+          const uint32_t third0 = q32[0][3], third1 = q32[1][3], third2 = q32[2][3], third3 = q32[3][3];
+          const uint32_t second_of_fourths =
+              max(min(max(third0, third1), max(third2, third3)),
+                  max(min(third0, third1), min(third2, third3)));
+          const uint32_t row_floor = max(min(min(q32[0][1], q32[1][1]), min(q32[2][1], q32[3][1])),
+                                         second_of_fourths);
+          // smallest raw score whose quantised key can reach the floor, a little low
+          const float gate = (row_floor >> 17) == 0u
+                                 ? -3.0e38f
+                                 : (static_cast<float>(row_floor >> 17) - 0.75f) * (1.0f / 256.0f) - 48.0f;
+          // Class by class (32 of the 128 columns each; the larger of two partial maxima
+          // is the class maximum, so a class without a taker in any row of the warp costs
+          // one vote): the columns that reach the gate as a bit mask, then insertion in
+          // rounds - every lane with a pending column inserts its next one per round.
+          // Both the pick of the column's score (a binary tree over the index bits) and
+          // the insertion (position by comparison) are shallow: one warp runs this alone
+          // on its scheduler, so the depth of the dependency chain is what it costs.
+#pragma unroll
+          for (int cls = 0; cls < 4; ++cls) {
+            if (!__any_sync(0xffffffffu, fmaxf(part_max[2 * cls], part_max[2 * cls + 1]) >= gate)) {
+              continue;
+            }
+            uint32_t takers = 0u;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int c = (i >> 1) * 8 + cls * 2 + (i & 1);
+              takers |= (s[c] >= gate ? 1u : 0u) << i;
+            }
+            while (__any_sync(0xffffffffu, takers != 0u)) {
+              if (takers != 0u) {
+                const int i = __ffs(takers) - 1;
+                takers &= takers - 1;
+                float pick[16];
+#pragma unroll
+                for (int m = 0; m < 16; ++m) {
+                  pick[m] = (i & 1) ? s[m * 8 + cls * 2 + 1] : s[m * 8 + cls * 2];
+                }
+#pragma unroll
+                for (int width = 8, bit = 2; width >= 1; width >>= 1, bit <<= 1) {
+#pragma unroll
+                  for (int m = 0; m < width; ++m) {
+                    pick[m] = (i & bit) ? pick[2 * m + 1] : pick[2 * m];
+                  }
+                }
+                const int c = (i >> 1) * 8 + cls * 2 + (i & 1);
+                const uint32_t candidate =
+                    (quantised_key(pick[0]) << 17) | (static_cast<uint32_t>(key0 + c) & 0x1ffffu);
+                sorted_insert<kLocalK>(q32[cls], candidate);
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 128; ++c) {
+            const int j = key0 + c;
+            if (s[c] > -INFINITY && j >= a.num_sink) {
+              const uint32_t candidate =
+                  (quantised_key(s[c]) << 17) | (static_cast<uint32_t>(j) & 0x1ffffu);
+              uint32_t(&queue)[kLocalK] = q32[(c & 7) >> 1];
+              if (candidate > queue[kLocalK - 1]) {
+                queue_insert<kLocalK>(queue, candidate);
+              }
+            }
+          }
+        }
+      }
     }
 
     if (!failed) {
