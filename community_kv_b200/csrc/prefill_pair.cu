@@ -147,6 +147,15 @@ __device__ __forceinline__ bool pair_wait_warp(uint32_t bar, uint32_t parity, vo
   return ok;
 }
 
+// The candidate key of the top-8 rule, clamp(rn((raw + 48) * 256)) to 15 bits, without the
+// conversion instruction (it shares the special-function unit with the other tile's
+// exponentials and would queue behind them): adding 1.5 * 2^23 leaves the integer, rounded
+// to nearest even, in the low mantissa bits.
+__device__ __forceinline__ uint32_t quantised_key_fma(float raw) {
+  const float scaled = fminf(fmaxf(fmaf(raw, 256.0f, 12288.0f), 0.0f), 32767.0f);
+  return __float_as_uint(scaled + 12582912.0f) & 0x7fffu;
+}
+
 // Insertion into a descending list by position: every slot decides by two comparisons
 // whether it keeps its entry, takes the candidate or takes its left neighbour's entry.
 template <int kDepth>
@@ -234,6 +243,10 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   const uint32_t tmem = *tmem_slot;
   bool failed = false;
 
+  // Register hand-over between the warpgroups.  setmaxnreg.inc blocks until the registers
+  // are free, without any bound: the totals must never exceed what the launch allocated
+  // (384 threads x 168 registers = 256 x 216 + 128 x 72).
+  static_assert(256 * 216 + 128 * 72 <= kPairThreads * 168, "register hand-over exceeds the launch allocation");
   if (warp >= 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   }
@@ -512,7 +525,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
                 }
                 const int c = (i >> 1) * 8 + cls * 2 + (i & 1);
                 const uint32_t candidate =
-                    (quantised_key(pick[0]) << 17) | (static_cast<uint32_t>(key0 + c) & 0x1ffffu);
+                    (quantised_key_fma(pick[0]) << 17) | (static_cast<uint32_t>(key0 + c) & 0x1ffffu);
                 sorted_insert<kLocalK>(q32[cls], candidate);
               }
             }
