@@ -749,7 +749,12 @@ def measure_prefill(args: argparse.Namespace, device, steps: int, warmup: int) -
 
     import torch
 
-    from community_kv_b200.prefill import prefill_attention, prefill_attention_edges, prefill_attention_topk
+    from community_kv_b200.prefill import (
+        check_status,
+        prefill_attention,
+        prefill_attention_edges,
+        prefill_attention_topk,
+    )
 
     length = args.prefill_length
     generator = torch.Generator(device=device).manual_seed(args.seed)
@@ -762,11 +767,15 @@ def measure_prefill(args: argparse.Namespace, device, steps: int, warmup: int) -
     flops = 2.0 * length * length * HEAD_DIM * QUERY_HEADS  # causal Q.K^T + P.V
     peaks_path = ROOT / "MEASURED_PEAKS.json"
     peak = float(json.loads(peaks_path.read_text())["bf16_tflops"]) if peaks_path.exists() else 1590.0
+    # one status word for the whole run: the calls queue without a host round trip and the
+    # word is read after each timed loop
+    status = torch.zeros((1,), dtype=torch.int32, device=device)
     variants = {
-        "attention_only": lambda: prefill_attention(query, key, value, softmax_scale=SCALE),
-        "reference_top8": lambda: prefill_attention_topk(query, key, value, softmax_scale=SCALE, num_sink=NUM_SINK),
+        "attention_only": lambda: prefill_attention(query, key, value, softmax_scale=SCALE, status=status),
+        "reference_top8": lambda: prefill_attention_topk(
+            query, key, value, softmax_scale=SCALE, num_sink=NUM_SINK, status=status),
         "exact_top16_per_kv_head": lambda: prefill_attention_edges(
-            query, key, value, softmax_scale=SCALE, num_sink=NUM_SINK, edges_per_row=16),
+            query, key, value, softmax_scale=SCALE, num_sink=NUM_SINK, edges_per_row=16, status=status),
     }
     timings = {}
     rescanned = None
@@ -781,6 +790,7 @@ def measure_prefill(args: argparse.Namespace, device, steps: int, warmup: int) -
         end.record()
         torch.cuda.synchronize()
         timings[name] = begin.elapsed_time(end) / steps
+        check_status(status)
         if name == "exact_top16_per_kv_head":
             rescanned = int(result[4].sum())
     headline = timings["exact_top16_per_kv_head"]
@@ -792,7 +802,7 @@ def measure_prefill(args: argparse.Namespace, device, steps: int, warmup: int) -
         "steps": steps,
         "flops": flops,
         "roofline": {
-            "kernel": "prefill_kernel (tcgen05 Q.K^T and P.V)",
+            "kernel": "prefill_pair_kernel (tcgen05 Q.K^T and P.V, P in tensor memory)",
             "bound": "tensor",
             "achieved": flops / (timings["attention_only"] * 1e-3) / 1e12,
             "achieved_with_reference_top8": flops / (timings["reference_top8"] * 1e-3) / 1e12,

@@ -22,7 +22,7 @@ TOPK = 8
 EXACT_KEEP = 16
 
 
-def _pack(query, key, value, *, softmax_scale, num_sink, mode, edges_per_row=0, exact_slack=0.0):
+def _pack(query, key, value, *, softmax_scale, num_sink, mode, edges_per_row=0, exact_slack=0.0, status=None):
     if query.ndim != 4 or key.ndim != 4 or value.shape != key.shape:
         raise ValueError("query/key/value must have shape [B, S, H, 128]")
     if query.shape[-1] != HEAD_DIM or key.shape[-1] != HEAD_DIM:
@@ -48,7 +48,10 @@ def _pack(query, key, value, *, softmax_scale, num_sink, mode, edges_per_row=0, 
     device = query.device
     out = torch.empty((batch, length, heads, HEAD_DIM), dtype=torch.bfloat16, device=device)
     lse = torch.empty((batch, heads, length), dtype=torch.float32, device=device)
-    status = torch.zeros((1,), dtype=torch.int32, device=device)
+    if status is None:
+        status = torch.zeros((1,), dtype=torch.int32, device=device)
+    elif status.dtype != torch.int32 or status.numel() != 1 or status.device != device:
+        raise ValueError("status must be a one-element int32 tensor on the inputs' device")
     args = native.PrefillArgs()
     native.fill(
         args,
@@ -72,6 +75,26 @@ def _pack(query, key, value, *, softmax_scale, num_sink, mode, edges_per_row=0, 
     return args, out, lse, status, (query, key, value)
 
 
+def check_status(status: torch.Tensor) -> None:
+    """Raise if a bounded wait inside the kernels ran out (the outputs are then invalid).
+
+    Every entry point below checks its own status word after the launch, which synchronises
+    with the stream.  A caller that wants to queue several calls without a host round trip
+    passes its own ``status`` tensor (one int32, zero-initialised; the kernels OR their flags
+    into it) and calls this function once at the end.  The check is skipped while the stream
+    is being captured into a CUDA graph.
+    """
+
+    if torch.cuda.is_current_stream_capturing():
+        return
+    word = int(status.item())
+    if word != 0:
+        raise RuntimeError(
+            f"prefill kernels reported device status {word:#x}: a bounded wait on a copy or "
+            "tensor-core barrier ran out; the outputs of this call are invalid"
+        )
+
+
 def prefill_attention_topk(
     query: torch.Tensor,
     key: torch.Tensor,
@@ -79,6 +102,7 @@ def prefill_attention_topk(
     *,
     softmax_scale: float,
     num_sink: int = 10,
+    status: torch.Tensor | None = None,
 ):
     """Causal grouped-query attention plus the reference's row-wise top-8 edges.
 
@@ -87,8 +111,9 @@ def prefill_attention_topk(
     than eight eligible keys are omitted, as in the reference).
     """
 
+    own_status = status is None
     args, out, lse, status, keep = _pack(
-        query, key, value, softmax_scale=softmax_scale, num_sink=num_sink, mode=1
+        query, key, value, softmax_scale=softmax_scale, num_sink=num_sink, mode=1, status=status
     )
     batch, length, heads, _ = out.shape
     rows = max(0, length - (num_sink + TOPK - 1))
@@ -97,6 +122,8 @@ def prefill_attention_topk(
     args.topk_val = topk_val.data_ptr()
     args.topk_idx = topk_idx.data_ptr()
     native.call("ckv_prefill_topk", args, native.current_stream(out.device))
+    if own_status:
+        check_status(status)
     del keep
     return out, lse, None, None, topk_val, topk_idx
 
@@ -110,6 +137,7 @@ def prefill_attention_edges(
     num_sink: int = 10,
     edges_per_row: int = 16,
     exact_slack: float = 1e-3,
+    status: torch.Tensor | None = None,
 ):
     """Causal attention plus the exact top-``edges_per_row`` keys per KV head and row.
 
@@ -123,9 +151,10 @@ def prefill_attention_edges(
 
     if not 1 <= edges_per_row <= EXACT_KEEP:
         raise ValueError("edges_per_row must be in [1, 16]")
+    own_status = status is None
     args, out, lse, status, keep = _pack(
         query, key, value, softmax_scale=softmax_scale, num_sink=num_sink, mode=2,
-        edges_per_row=edges_per_row, exact_slack=exact_slack,
+        edges_per_row=edges_per_row, exact_slack=exact_slack, status=status,
     )
     batch, length, heads, _ = out.shape
     kv_heads = keep[1].shape[2]
@@ -146,19 +175,24 @@ def prefill_attention_edges(
         rescan_list=rescan_list.data_ptr(),
     )
     native.call("ckv_prefill_topk", args, native.current_stream(device))
+    if own_status:
+        check_status(status)
     del keep
     return out, lse, edge_idx, edge_score, flags
 
 
-def prefill_attention(query, key, value, *, softmax_scale: float):
+def prefill_attention(query, key, value, *, softmax_scale: float, status: torch.Tensor | None = None):
     """Causal grouped-query attention only: ``(out, lse)``."""
 
+    own_status = status is None
     args, out, lse, status, keep = _pack(
-        query, key, value, softmax_scale=softmax_scale, num_sink=0, mode=0
+        query, key, value, softmax_scale=softmax_scale, num_sink=0, mode=0, status=status
     )
     native.call("ckv_prefill_topk", args, native.current_stream(out.device))
+    if own_status:
+        check_status(status)
     del keep
     return out, lse
 
 
-__all__ = ["prefill_attention", "prefill_attention_edges", "prefill_attention_topk"]
+__all__ = ["check_status", "prefill_attention", "prefill_attention_edges", "prefill_attention_topk"]

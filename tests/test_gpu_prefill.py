@@ -7,6 +7,7 @@ import pytest
 import torch
 
 from community_kv_b200.prefill import (
+    check_status,
     prefill_attention,
     prefill_attention_edges,
     prefill_attention_topk,
@@ -120,6 +121,16 @@ def test_batch_and_validation():
     for b in range(2):
         want_out, want_lse, _ = oracle.causal_attention(q[b].float().numpy(), k[b].float().numpy(), v[b].float().numpy(), SCALE)
         _check_attention(out[b], lse[b], q, k, v, want_out, want_lse)
+    # caller-owned status word: the calls queue without a host round trip, one check at the end
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    again, _ = prefill_attention(q.cuda(), k.cuda(), v.cuda(), softmax_scale=SCALE, status=status)
+    prefill_attention_topk(q.cuda(), k.cuda(), v.cuda(), softmax_scale=SCALE, num_sink=4, status=status)
+    check_status(status)
+    assert torch.equal(again, out)
+    with pytest.raises(ValueError):
+        prefill_attention(q.cuda(), k.cuda(), v.cuda(), softmax_scale=SCALE, status=status.to(torch.int64))
+    with pytest.raises(RuntimeError):
+        check_status(torch.full((1,), 4, dtype=torch.int32, device="cuda"))
     with pytest.raises(TypeError):
         prefill_attention(q.cuda().float(), k.cuda(), v.cuda(), softmax_scale=SCALE)
     with pytest.raises(ValueError):
