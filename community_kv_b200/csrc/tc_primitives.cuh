@@ -16,7 +16,6 @@ constexpr int kPfKeys = 128;
 constexpr int kTileBytes = kPfRows * kHeadDim * 2;  // 32 KiB
 constexpr int kLocalK = 6;
 constexpr int kExactKeep = 16;
-constexpr uint32_t kBarrierPolls = 1u << 22;
 
 __device__ __forceinline__ uint32_t core_offset(int row, int chunk) {
   // 8 rows x 16 bytes form one contiguous 128-byte core matrix; the row groups of
@@ -119,14 +118,17 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
 
-// Polls a completion barrier a bounded number of times.
+// Waits for a completion barrier a bounded number of times.  try_wait parks the thread in
+// hardware until the phase completes or a system time limit passes, so a waiting thread
+// neither spins on the issue port nor oversleeps.
+constexpr uint32_t kBarrierTries = 1u << 18;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t poll = 0; poll < kBarrierPolls; ++poll) {
+  for (uint32_t poll = 0; poll < kBarrierTries; ++poll) {
     uint32_t done;
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(done)
@@ -134,9 +136,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     if (done) {
       return true;
-    }
-    if (poll > 64) {
-      __nanosleep(32);
     }
   }
   return false;
