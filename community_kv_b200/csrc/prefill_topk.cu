@@ -914,16 +914,29 @@ __device__ __forceinline__ void tmem_load16_issue(uint32_t taddr, uint32_t (&r)[
       : "r"(taddr));
 }
 
+// Insertion into a descending list by position: every slot decides from two comparisons
+// whether it keeps its entry, takes the candidate or takes its left neighbour's entry, so
+// the dependency chain is two operations deep whatever the length.  Returns what fell off
+// the end (the candidate itself when it did not enter).
 template <int kKeep>
 __device__ __forceinline__ uint64_t list_insert(uint64_t (&list)[kKeep], uint64_t candidate) {
+  bool keeps[kKeep];
 #pragma unroll
   for (int k = 0; k < kKeep; ++k) {
-    const uint64_t resident = list[k];
-    const bool greater = candidate > resident;
-    list[k] = greater ? candidate : resident;
-    candidate = greater ? resident : candidate;
+    keeps[k] = list[k] >= candidate;
   }
-  return candidate;
+  const uint64_t lost = keeps[kKeep - 1] ? candidate : list[kKeep - 1];
+  uint64_t next[kKeep];
+  next[0] = keeps[0] ? list[0] : candidate;
+#pragma unroll
+  for (int k = 1; k < kKeep; ++k) {
+    next[k] = keeps[k] ? list[k] : (keeps[k - 1] ? candidate : list[k - 1]);
+  }
+#pragma unroll
+  for (int k = 0; k < kKeep; ++k) {
+    list[k] = next[k];
+  }
+  return lost;
 }
 
 struct EdgeSmem {
@@ -1126,11 +1139,15 @@ __global__ void __launch_bounds__(kEdgeThreads, 1)
           if (takers != 0u) {
             const int i = __ffs(takers) - 1;
             takers &= takers - 1;
-            float v = best[0];
+            // the column's score by a binary tree over the index bits (four selects deep)
+            float pick[8];
 #pragma unroll
-            for (int k = 1; k < 16; ++k) {
-              v = i == k ? best[k] : v;
-            }
+            for (int m = 0; m < 8; ++m) pick[m] = (i & 1) ? best[2 * m + 1] : best[2 * m];
+#pragma unroll
+            for (int m = 0; m < 4; ++m) pick[m] = (i & 2) ? pick[2 * m + 1] : pick[2 * m];
+#pragma unroll
+            for (int m = 0; m < 2; ++m) pick[m] = (i & 4) ? pick[2 * m + 1] : pick[2 * m];
+            const float v = (i & 8) ? pick[1] : pick[0];
             if (v > floor_score) {
               const uint64_t candidate = (static_cast<uint64_t>(ordered_key32(v)) << 32) |
                                          (0xffffffffu - static_cast<uint32_t>(key0 + c0 + i));
