@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(const uint6
                                                                      float* weights_out) {
   __shared__ uint32_t digit_base[256];                     // where the tile's next item of a digit goes
   __shared__ uint32_t round_base[256];                     // the same, at the start of the current round
-  __shared__ uint16_t warp_count[kSortThreads / 32][256];  // this round, per warp and digit
+  __shared__ uint16_t warp_count[kSortThreads / 32][256];  // this sorting pass, per warp and digit
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   digit_base[threadIdx.x] = table[static_cast<int64_t>(threadIdx.x) * tiles + blockIdx.x];
