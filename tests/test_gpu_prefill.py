@@ -176,3 +176,58 @@ def test_full_size_properties():
         rest = best.scatter(1, got_idx, float("-inf"))
         assert bool((rest.amax(dim=1) <= got_score[:, -1] + 2e-5).all()), row
     assert int(flags.sum()) <= flags.numel() // 100
+
+
+def test_full_size_reference_topk_rule():
+    """The reference's top-8 rule at full size (S = 16384, 32 / 8 heads): for sampled rows the rule is
+    restated in fp32 torch arithmetic - key15 = clamp(rn((q.k + 48) * 256)), four column classes keep
+    their six best packed candidates, the row reports the eight largest.  The kernel's scores come from
+    the tensor cores, so a disagreement is accepted only where the keys involved sit within one
+    quantisation step of the cut; the reported probabilities must match exp(score * scale - lse)."""
+
+    device = torch.device("cuda", 0)
+    length, heads, kv_heads, sinks = 16384, 32, 8, 10
+    generator = torch.Generator(device=device).manual_seed(11)
+    centres = torch.randn((kv_heads, 256, 128), generator=generator, device=device)
+    labels = torch.randint(0, 256, (length, kv_heads), generator=generator, device=device)
+    key = centres[torch.arange(kv_heads, device=device), labels] + 0.3 * torch.randn(
+        (length, kv_heads, 128), generator=generator, device=device)
+    key = (key * SCALE).to(torch.bfloat16)[None]
+    value = (torch.randn((1, length, kv_heads, 128), generator=generator, device=device) * SCALE).to(torch.bfloat16)
+    query = torch.randn((1, length, heads, 128), generator=generator, device=device).to(torch.bfloat16)
+    out, lse, _, _, val, idx = prefill_attention_topk(query, key, value, softmax_scale=SCALE, num_sink=sinks)
+    torch.cuda.synchronize()
+    skip = sinks + 7
+    group = heads // kv_heads
+    rows = torch.randint(skip, length, (40,), generator=generator, device=device).tolist() + [skip, 127, 128, length - 1]
+    k32 = key[0].float()
+    exact_rows = 0
+    for row in rows:
+        q_row = query[0, row].float()  # [heads, 128]
+        raw = torch.einsum("hd,jhd->hj", q_row, k32[: row + 1].repeat_interleave(group, dim=1))  # [heads, keys]
+        keys = torch.clamp(torch.round((raw + 48.0) * 256.0), 0, 32767).long()
+        columns = torch.arange(row + 1, device=device)
+        packed = (keys << 17) | columns
+        packed[:, :sinks] = -1
+        kept = []
+        for cls in range(4):
+            members = packed[:, ((columns % 8) // 2) == cls]
+            kept.append(members.topk(min(6, members.shape[1]), dim=1).values)
+        want = torch.cat(kept, dim=1).topk(8, dim=1).values  # [heads, 8], descending
+        want_idx = want & 0x1FFFF
+        got_idx = idx[0, :, row - skip].long()
+        got_val = val[0, :, row - skip]
+        assert bool((got_idx >= sinks).all()) and bool((got_idx <= row).all()), row
+        for head in range(heads):
+            mine, theirs = set(got_idx[head].tolist()), set(want_idx[head].tolist())
+            assert len(mine) == 8, (row, head)
+            if got_idx[head].tolist() == want_idx[head].tolist():
+                exact_rows += 1
+            floor_key = int(want[head, -1] >> 17)
+            for j in mine ^ theirs:
+                assert abs(int(keys[head, j]) - floor_key) <= 1, (row, head, j)
+        # probabilities from the dequantised key of the column the kernel chose
+        chosen = keys.gather(1, got_idx).float() / 256.0 - 48.0
+        want_val = torch.exp(chosen * SCALE - lse[0, :, row].unsqueeze(1))
+        torch.testing.assert_close(got_val, want_val, rtol=3e-2, atol=1e-9)
+    assert exact_rows / (len(rows) * heads) > 0.9, exact_rows / (len(rows) * heads)
