@@ -42,10 +42,18 @@ class CommunityKVConfig:
     aggregation: GraphAggregation = GraphAggregation.PER_QUERY_HEAD
     leiden_resolution: float = 1.0
     leiden_seed: int = 0
+    # Not in the reference: how a decoded token picks its community.  "modularity" is the
+    # reference's rule (largest modularity gain among the communities of the token's eight
+    # strongest neighbours, a new community when no gain is positive); "nearest_centroid"
+    # joins the live community whose centroid has the largest inner product with the token's
+    # key (ties: smallest id) - one more centroid scan per layer and step.
+    online_assignment: str = "modularity"
 
     def __post_init__(self) -> None:
         object.__setattr__(self, "aggregation", GraphAggregation(self.aggregation))
         problems = []
+        if self.online_assignment not in ("modularity", "nearest_centroid"):
+            problems.append("online_assignment must be 'modularity' or 'nearest_centroid'")
         if self.token_budget <= 0 or self.token_budget % 64 != 0:
             problems.append("token_budget must be a positive multiple of 64")
         elif self.num_sink < 0 or self.num_sink + 1 >= self.token_budget:

@@ -359,8 +359,16 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
     for (int offset = 16; offset > 0; offset >>= 1) {
       best_community = min(best_community, __shfl_xor_sync(0xffffffffu, best_community, offset));
     }
-    const bool join = best_delta > 0.f;
-    const int assigned = join ? best_community : active;
+    bool join = best_delta > 0.f;
+    int assigned = join ? best_community : active;
+    if (a.forced_community != nullptr) {
+      // the caller's choice (nearest-centroid variant) replaces the rule's, if it is a live community
+      const int forced = a.forced_community[graph_slot];
+      if (forced >= 0 && forced < active) {
+        join = true;
+        assigned = forced;
+      }
+    }
     const bool community_overflow = assigned >= capacity;
     const int safe_assigned = min(max(assigned, 0), capacity - 1);
 

@@ -112,6 +112,7 @@ class LayerArgs(ctypes.Structure):
         ("topk_unit_stride", _i64),
         ("topk_split_stride", _i64),
         ("merged_topk", _ptr),
+        ("forced_community", _ptr),
     ]
 
 

@@ -211,8 +211,13 @@ def score_centroids(
     community_sizes: torch.Tensor,
     community_counts: torch.Tensor,
     workspace: CentroidSelectionWorkspace,
+    exact: bool = False,
 ) -> torch.Tensor:
-    """Score each contiguous query group against its centroid table (fp16 out)."""
+    """Score each contiguous query group against its centroid table (fp16 out).
+
+    ``exact``: use the fixed-order CUDA-core sum for this call whatever the process-wide
+    switch says (a CPU can reproduce it bit for bit).
+    """
 
     args = native.LayerArgs()
     _score_args(
@@ -232,7 +237,7 @@ def score_centroids(
         graphs=workspace.kv_heads,
         retrieval_to_graph=native.pointer(mapping),
         retrieval_to_kv=native.pointer(mapping),
-        flags=_layout_flags(),
+        flags=_layout_flags() & ~(native.FLAG_TENSOR_SCORES if exact else 0),
     )
     native.call("ckv_score_centroids", args, native.current_stream(device))
     return workspace.scores

@@ -23,6 +23,7 @@ import torch
 from community_kv_b200 import native, ops
 from community_kv_b200.config import CommunityKVConfig, GraphAggregation, PartitionConfig
 from community_kv_b200.state import (
+    CentroidSelectionWorkspace,
     ATTENTION_TILE,
     HEAD_DIM,
     DecodeDeltaChunks,
@@ -68,6 +69,9 @@ class DecodeLayerState:
     args: native.LayerArgs | None = None
     cache_key: tuple[int, ...] | None = None
     update_done: Any = None  # deferred update: event of the layer's last online assignment
+    # nearest-centroid assignment variant: scores of the new token's key, the arg-max per graph
+    nearest: Any = None
+    forced: torch.Tensor | None = None
 
 
 def _pad_member_offsets(member_offsets: torch.Tensor, *, community_capacity: int) -> torch.Tensor:
@@ -335,6 +339,8 @@ class DecodeRuntime:
             )
             layer.cache_key = cache_key
         layer.args.query = flat_query.data_ptr()
+        if self.config.online_assignment == "nearest_centroid":
+            self._nearest_centroid(layer, key[0])
         if self.defer_update:
             if self._deferred is None:
                 self._deferred = ops.DeferredUpdate(query.device)
@@ -342,6 +348,44 @@ class DecodeRuntime:
         else:
             native.call("ckv_decode_layer", layer.args, native.current_stream(query.device))
         return layer.workspace.attention.output.view(1, 1, heads, HEAD_DIM)
+
+    def _nearest_centroid(self, layer: DecodeLayerState, key: torch.Tensor) -> None:
+        """The variant of the online assignment that is not in the reference: the token joins
+        the live community whose centroid has the largest inner product with its key.
+
+        The key row of the token being decoded (already in the cache at the graph's cursor) is
+        scored against the centroid table by the scoring kernel itself - as a query group whose
+        rows are all that key, in the fixed summation order, so that a CPU reproduces the fp16
+        scores bit for bit - and the first maximum per leader head is handed to the update as
+        ``forced_community``.  Everything stays on the device and on the caller's stream.
+        """
+
+        mutable = layer.converted.mutable
+        heads = mutable.retrieval_head_count
+        device = mutable.centroids.device
+        if layer.nearest is None:
+            layer.nearest = CentroidSelectionWorkspace.allocate(
+                kv_heads=heads, community_capacity=mutable.community_capacity,
+                token_budget=layer.workspace.selection.token_budget, num_sink=self.config.num_sink,
+                device=device,
+            )
+            layer.forced = torch.full((mutable.graph_count,), -1, dtype=torch.int32, device=device)
+        layer.args.forced_community = layer.forced.data_ptr()  # the block is rebuilt when the cache moves
+        if layer.update_done is not None:
+            # the previous step's deferred update still reads `forced`
+            torch.cuda.current_stream(device).wait_event(layer.update_done)
+        cursor = layer.converted.current_position.long()[mutable.retrieval_to_graph.long()]
+        rows = key[mutable.retrieval_to_kv.long(), cursor.clamp(max=key.shape[1] - 1)]  # [R, 128]
+        group = layer.converted.group_size
+        scores = ops.score_centroids(
+            query=rows.repeat_interleave(group, dim=0).contiguous(), centroids=mutable.centroids,
+            community_sizes=mutable.community_sizes, community_counts=mutable.community_counts,
+            workspace=layer.nearest, exact=True,
+        )
+        best = scores.float().max(dim=1)
+        nearest = torch.where(torch.isinf(best.values) & (best.values < 0), -1, best.indices).to(torch.int32)
+        # the leader of graph g is retrieval head g
+        layer.forced.copy_(nearest[: mutable.graph_count])
 
     def assert_no_overflow(self) -> None:
         self.synchronize_updates()

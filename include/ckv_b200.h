@@ -206,6 +206,15 @@ typedef struct ckv_layer_args {
   uint64_t* merged_topk;        /* optional [batch, R, 8]: with `merged`, the packed eight best
                                    neighbour candidates of every unit (ordered fp32 score << 32 |
                                    0xffffffff - position; 0: none), for a cross-GPU combine */
+  const int32_t* forced_community; /* optional [batch, graphs]: the community the new token joins.
+                                  When set and 0 <= value < the leader head's community count,
+                                  the online assignment joins it instead of applying the dQ rule
+                                  of A5 (weights, sizes, centroid, labels and delta chunks are
+                                  updated exactly as for a join the rule had chosen); a negative
+                                  value leaves that graph to the rule.  Carries the
+                                  nearest-centroid assignment variant: the caller scores the new
+                                  token's key against the centroids (ckv_score_centroids) and
+                                  passes the arg-max.  No reference counterpart. */
 } ckv_layer_args;
 
 /* Arguments of the prefill score-graph kernel.  Q, K, V, O are bf16 with a

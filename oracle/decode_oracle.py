@@ -454,8 +454,13 @@ def online_update(
     lam: float,
     assigned_out: torch.Tensor,
     overflow_out: torch.Tensor,
+    forced_community: int = -1,
 ) -> None:
-    """Leader-program half of the reduce/update kernel (segmented_attention.py:546-864)."""
+    """Leader-program half of the reduce/update kernel (segmented_attention.py:546-864).
+
+    ``forced_community`` (not in the reference): a live community the token joins instead of
+    the one the dQ rule picks - the nearest-centroid assignment variant.
+    """
 
     one = np.float32(1.0)
     lam32 = np.float32(lam)
@@ -516,6 +521,9 @@ def online_update(
     best_community = int(community[tied].min()) if tied.any() else 0x7FFFFFFF
     join = bool(best_delta > 0.0)
     assigned = best_community if join else active
+    if 0 <= forced_community < active:
+        join = True
+        assigned = forced_community
     community_overflow = assigned >= community_capacity
     safe_assigned = min(max(assigned, 0), community_capacity - 1)
 
@@ -678,6 +686,7 @@ def decode_layer(
     update: bool = True,
     exact: bool = True,
     given_scores: torch.Tensor | None = None,
+    assignment: str = "modularity",
 ) -> LayerResult:
     """Score, select, attend, assign: the whole per-layer decode transition on CPU.
 
@@ -686,6 +695,11 @@ def decode_layer(
     of the tensor cores (hardware summation order, last fp16 bit not reproducible here)
     is checked - its scores against ``score_centroids`` to one unit in the last place,
     everything downstream bit for bit given its scores.
+
+    ``assignment="nearest_centroid"`` (not in the reference): the decoded token joins the live
+    community whose centroid has the largest inner product with its key - the scores are those
+    of ``score_centroids`` for a query group whose rows all equal the key, the first maximum
+    wins - instead of the community the dQ rule picks.
     """
 
     heads, capacity, _ = state.centroids.shape
@@ -774,12 +788,33 @@ def decode_layer(
         topk_scores[head] = torch.from_numpy(top_scores)
         topk_positions[head] = torch.from_numpy(top_positions)
 
+    nearest = None
+    if update and assignment == "nearest_centroid":
+        # the new token's key per retrieval head (already in the cache at the graph's cursor), as a
+        # query group of identical rows, against the centroids as they are before this update
+        rows = []
+        for head in range(heads):
+            graph = int(state.retrieval_to_graph[head])
+            cursor = min(int(current_position[graph]), key.shape[1] - 1)
+            rows.append(key[int(state.retrieval_to_kv[head]), cursor])
+        key_query = torch.stack(rows).repeat_interleave(group, dim=0)
+        key_scores = torch.zeros((heads, capacity), dtype=torch.float16)
+        score_centroids(
+            query=key_query, centroids=state.centroids, community_sizes=state.community_sizes,
+            community_counts=state.community_counts, scores=key_scores, cover=None, exact=True,
+        )
+        best = key_scores.float().max(dim=1)
+        nearest = torch.where(torch.isinf(best.values) & (best.values < 0), -1, best.indices)
     if update:
         for head in range(heads):
             graph = int(state.retrieval_to_graph[head])
             if head != graph:
                 continue
+            forced = -1
+            if assignment == "nearest_centroid":
+                forced = int(nearest[head])
             online_update(
+                forced_community=forced,
                 state=state,
                 retrieval_head=head,
                 graph=graph,

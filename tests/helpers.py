@@ -117,7 +117,7 @@ class OracleLayer:
         return scores
 
     def step(self, *, query, key, value, softmax_scale, lam, update=True, given_scores=None,
-             device_scores=None) -> oracle.LayerResult:
+             device_scores=None, assignment="modularity") -> oracle.LayerResult:
         """``device_scores``: the fp16 scores the device produced for this step.  When the library
         scores on the tensor cores (its default) they are checked against the fixed-order scores to
         one unit in the last place and the rest of the step is computed from them, so that everything
@@ -154,4 +154,5 @@ class OracleLayer:
             cover=self.cover,
             max_communities=self.max_communities,
             update=update,
+            assignment=assignment,
         )

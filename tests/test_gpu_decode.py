@@ -51,7 +51,7 @@ def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, def
         runtime.synchronize_updates()
         where = f"step {step}"
         want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=config.lam,
-                         device_scores=state.workspace.selection.scores)
+                         device_scores=state.workspace.selection.scores, assignment=config.online_assignment)
         assert_step_equal(
             selection=state.workspace.selection,
             attention=state.workspace.attention,
@@ -127,6 +127,27 @@ def test_deferred_update_gives_the_same_result(aggregation):
                        zipf_exponent=1.1)
     config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation=aggregation)
     _run_sequence(layer, config, steps=8, seed=2100, defer_update=True)
+
+
+@pytest.mark.parametrize(
+    "aggregation,defer", [(GraphAggregation.QUERY_GROUP, False), (GraphAggregation.QUERY_GROUP, True),
+                          (GraphAggregation.PER_QUERY_HEAD, False), (GraphAggregation.LAYER_WISE, False)]
+)
+def test_nearest_centroid_assignment_variant(aggregation, defer):
+    """Not in the reference: every decoded token joins the community whose centroid is nearest to its key
+    (largest inner product, first maximum).  State and outputs against the CPU restatement, bit for bit;
+    the variant never opens a community, and its choices differ from the modularity rule's."""
+
+    layer = make_layer(seed=23, seq_len=8192, communities=96, max_decode_tokens=12, aggregation=aggregation,
+                       zipf_exponent=1.1)
+    config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation=aggregation,
+                               online_assignment="nearest_centroid")
+    before = layer.to(torch.device("cuda", 0)).prepare_kwargs()["num_communities"].clone()
+    state, twin = _run_sequence(layer, config, steps=10, seed=2300, defer_update=defer)
+    counts = state.converted.mutable.community_counts
+    assert int(counts.max()) == int(before.max()) and int(counts.min()) == int(before.min())
+    with pytest.raises(ValueError):
+        CommunityKVConfig(online_assignment="nearest")
 
 
 def test_many_small_communities_and_delta_chains():

@@ -114,7 +114,7 @@ def _small_state(capacity=8, dim=128, decode=16, sequence=70_000) -> MutableGrap
     return state
 
 
-def _run_update(state, scores, positions, lse, key_row, current, lam):
+def _run_update(state, scores, positions, lse, key_row, current, lam, forced=-1):
     cache = torch.zeros((1, state.token_communities.shape[1], key_row.shape[-1]), dtype=torch.bfloat16)
     cache[0, current] = key_row
     cursor = torch.tensor([current], dtype=torch.int32)
@@ -137,6 +137,7 @@ def _run_update(state, scores, positions, lse, key_row, current, lam):
         lam=lam,
         assigned_out=assigned,
         overflow_out=overflow,
+        forced_community=forced,
     )
     return int(assigned[0]), int(overflow[0]), int(cursor[0])
 
@@ -173,6 +174,30 @@ def test_online_update_creates_singleton_without_positive_gain():
     assert int(state.community_sizes[0, 2]) == 1
     assert state.centroids[0, 2, :4].float().tolist() == [2.0, 4.0, 6.0, 8.0]
     assert state.deltas.members(0, 2).tolist() == [21]
+
+
+def test_online_update_with_a_forced_community():
+    """The nearest-centroid variant hands the update the community to join (no reference counterpart):
+    a live community replaces the rule's choice, anything else leaves the rule in charge."""
+
+    key = torch.zeros(128, dtype=torch.bfloat16)
+    key[:4] = torch.tensor([2.0, 4.0, 6.0, 8.0], dtype=torch.bfloat16)
+    # the rule alone would open community 2 (no positive gain): forced into community 1 instead
+    state = _small_state()
+    state.community_weight[0, :2] = 100.0
+    sizes_before = state.community_sizes[0, :2].tolist()
+    assigned, overflow, cursor = _run_update(state, [1.0, 0.5], [4, 5], 2.0, key, 21, 1.0, forced=1)
+    assert (assigned, overflow, cursor) == (1, 0, 22)
+    assert state.community_counts.tolist() == [2]
+    assert state.community_sizes[0, :2].tolist() == [sizes_before[0], sizes_before[1] + 1]
+    assert state.deltas.members(0, 1).tolist()[0] == 21
+    assert int(state.token_communities[0, 21]) == 1
+    # a community that is not live (or -1) is ignored
+    for forced in (2, 7, -1):
+        state = _small_state()
+        state.community_weight[0, :2] = 100.0
+        assigned, _, _ = _run_update(state, [1.0, 0.5], [4, 5], 2.0, key, 21, 1.0, forced=forced)
+        assert assigned == 2 and state.community_counts.tolist() == [3]
 
 
 def test_online_update_survives_many_appends():
