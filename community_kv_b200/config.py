@@ -48,10 +48,16 @@ class CommunityKVConfig:
     # joins the live community whose centroid has the largest inner product with the token's
     # key (ties: smallest id) - one more centroid scan per layer and step.
     online_assignment: str = "modularity"
+    # Not in the reference either: "fp32" keeps the centroid table unquantised (scores from the
+    # fixed-order fp32 sum, running mean stored as it is; four stand-alone kernels per layer
+    # call instead of the single cluster launch); "e4m3" is the reference's layout.
+    centroid_dtype: str = "e4m3"
 
     def __post_init__(self) -> None:
         object.__setattr__(self, "aggregation", GraphAggregation(self.aggregation))
         problems = []
+        if self.centroid_dtype not in ("e4m3", "fp32"):
+            problems.append("centroid_dtype must be 'e4m3' or 'fp32'")
         if self.online_assignment not in ("modularity", "nearest_centroid"):
             problems.append("online_assignment must be 'modularity' or 'nearest_centroid'")
         if self.token_budget <= 0 or self.token_budget % 64 != 0:

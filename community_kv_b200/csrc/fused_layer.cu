@@ -122,7 +122,8 @@ bool fused_layer_supported(const ckv_layer_args& a) {
   const int groups = (a.community_capacity + 15) / 16;
   const int rows_per_cta = 16 * ((groups + a.splits - 1) / (a.splits > 0 ? a.splits : 1));
   return a.graphs == a.retrieval_heads && a.splits >= 1 && a.splits <= 8 && rows_per_cta <= kStash &&
-         !(a.flags & (CKV_FLAG_ATTENTION_ONLY | CKV_FLAG_UPDATE_ONLY | CKV_FLAG_UNFUSED));
+         !(a.flags & (CKV_FLAG_ATTENTION_ONLY | CKV_FLAG_UPDATE_ONLY | CKV_FLAG_UNFUSED |
+                      CKV_FLAG_FP32_CENTROIDS));
 }
 
 cudaError_t launch_fused_layer(const ckv_layer_args& a, cudaStream_t stream) {

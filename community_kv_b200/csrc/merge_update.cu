@@ -54,6 +54,13 @@ __global__ void __launch_bounds__(kMergeThreads) sync_shared_kernel(const ckv_la
             : reinterpret_cast<const __nv_bfloat16*>(a.key) + u.batch * a.key_batch_stride +
                   u.kv * a.key_head_stride + static_cast<int64_t>(current) * a.key_row_stride;
     const float key_value = __bfloat162float(key_row[d]);
+    if (a.flags & CKV_FLAG_FP32_CENTROIDS) {
+      float* wide = reinterpret_cast<float*>(a.centroids) + size_index * kHeadDim + d;
+      *wide = old_size > 0 ? centroid_mean(*wide, old_size, key_value,
+                                           (a.flags & CKV_FLAG_REFERENCE_DIVISION) != 0)
+                           : key_value;
+      return;
+    }
     float updated = key_value;
     if (old_size > 0) {
       const __half_raw raw = __nv_cvt_fp8_to_halfraw(centroid[d], __NV_E4M3);

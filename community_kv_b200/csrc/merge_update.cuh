@@ -469,7 +469,16 @@ __device__ __forceinline__ void merge_update_unit(const ckv_layer_args& a, int f
   }
   __syncthreads();
   // ---- running centroid: fp32 mean stored back as saturating e4m3 ----
-  if (threadIdx.x < kHeadDim && decision.apply && decision.valid_position) {
+  if (threadIdx.x < kHeadDim && decision.apply && decision.valid_position &&
+      (a.flags & CKV_FLAG_FP32_CENTROIDS)) {
+    // fp32 table: the running mean is stored as it is
+    float* centroid = reinterpret_cast<float*>(a.centroids) +
+                      (static_cast<int64_t>(flat) * capacity + decision.assigned) * kHeadDim + threadIdx.x;
+    *centroid = decision.old_size > 0
+                    ? centroid_mean(*centroid, decision.old_size, key_value,
+                                    (a.flags & CKV_FLAG_REFERENCE_DIVISION) != 0)
+                    : key_value;
+  } else if (threadIdx.x < kHeadDim && decision.apply && decision.valid_position) {
     const int d = threadIdx.x;
     __nv_fp8_storage_t* centroid =
         reinterpret_cast<__nv_fp8_storage_t*>(a.centroids) +

@@ -89,6 +89,55 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_kernel(const ckv_layer
   }
 }
 
+// fp32 centroid table (CKV_FLAG_FP32_CENTROIDS).  Eight lanes share one centroid row, 16
+// dimensions each; every product and every sum is rounded on its own (multiply, then add),
+// in the order of the e4m3 path - 16 sequential terms per lane, then lanes (j, j^4),
+// (j, j^2), (j, j^1) - so that a CPU reproduces the fp16 score bit for bit.
+constexpr int kScoreFp32Threads = 256;
+
+__global__ void __launch_bounds__(kScoreFp32Threads) score_fp32_kernel(const ckv_layer_args a) {
+  const int flat = blockIdx.y;
+  const int capacity = a.community_capacity;
+  const int limit = score_limit(a, flat);
+  const int row = blockIdx.x * (kScoreFp32Threads / 8) + (threadIdx.x >> 3);
+  const int slice = threadIdx.x & 7;
+  const int safe_row = min(row, capacity - 1);  // every lane takes part in the shuffles below
+  const float4* source = reinterpret_cast<const float4*>(
+      reinterpret_cast<const float*>(a.centroids) +
+      (static_cast<int64_t>(flat) * capacity + safe_row) * kHeadDim + slice * 16);
+  float x[16];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 v = source[i];
+    x[4 * i] = v.x;
+    x[4 * i + 1] = v.y;
+    x[4 * i + 2] = v.z;
+    x[4 * i + 3] = v.w;
+  }
+  const int group = a.group_size;
+  const __nv_bfloat16* query = reinterpret_cast<const __nv_bfloat16*>(a.query) +
+                               static_cast<int64_t>(flat) * group * kHeadDim + slice * 16;
+  float best = -INFINITY;
+  for (int g = 0; g < group; ++g) {
+    const __nv_bfloat16* q = query + g * kHeadDim;
+    float acc = __fmul_rn(x[0], __bfloat162float(q[0]));
+#pragma unroll
+    for (int k = 1; k < 16; ++k) {
+      acc = __fadd_rn(acc, __fmul_rn(x[k], __bfloat162float(q[k])));
+    }
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+    best = fmaxf(best, acc);
+  }
+  if (slice == 0 && row < limit) {
+    const bool live = row < a.community_counts[flat] &&
+                      a.community_sizes[static_cast<int64_t>(flat) * capacity + row] > 0;
+    reinterpret_cast<__half*>(a.scores)[static_cast<int64_t>(flat) * capacity + row] =
+        __float2half_rn(live ? best : -INFINITY);
+  }
+}
+
 // Dynamic shared memory: one 256-bin (mass, count) histogram per warp, then the key/size
 // stash of `stash_capacity` entries (sizes first).
 constexpr int kSelectWarpHistBytes = (kSelectThreads / 32) * 256 * 2 * static_cast<int>(sizeof(int));
@@ -129,6 +178,11 @@ cudaError_t launch_score(const ckv_layer_args& a, cudaStream_t stream) {
   // two CTAs per SM are resident: one wave, but never finer than eight 16-row
   // groups (one per warp) per CTA
   const int units = a.batch * a.retrieval_heads;
+  if (a.flags & CKV_FLAG_FP32_CENTROIDS) {
+    const dim3 grid((a.community_capacity + kScoreFp32Threads / 8 - 1) / (kScoreFp32Threads / 8), units);
+    score_fp32_kernel<<<grid, kScoreFp32Threads, 0, stream>>>(a);
+    return cudaGetLastError();
+  }
   if (units > kScoreMaxUnits) {
     return cudaErrorInvalidConfiguration;
   }

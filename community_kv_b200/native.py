@@ -167,6 +167,7 @@ FLAG_ATTENTION_ONLY = 2
 FLAG_UPDATE_ONLY = 4
 # ckv_decode_layer: four stand-alone kernels instead of the single cluster launch
 FLAG_UNFUSED = 8
+FLAG_FP32_CENTROIDS = 64  # the centroid table is fp32 instead of e4m3 (four stand-alone kernels)
 FLAG_TENSOR_SCORES = 32  # centroid scoring with mma.sync instead of the fixed CUDA-core order
 FLAG_REFERENCE_DIVISION = 16  # centroid mean with the reference kernel's approximate division
 DEV_WAIT_TIMEOUT = 1
@@ -278,6 +279,7 @@ __all__ = [
     "FLAG_SKIP_UPDATE",
     "FLAG_REFERENCE_DIVISION",
     "FLAG_TENSOR_SCORES",
+    "FLAG_FP32_CENTROIDS",
     "FLAG_UNFUSED",
     "FLAG_UPDATE_ONLY",
     "LayerArgs",

@@ -74,8 +74,8 @@ def _score_args(
         raise ValueError("community_counts must have one entry per KV head")
     if query.dtype != torch.bfloat16:
         raise TypeError("query must use BF16")
-    if centroids.dtype != torch.float8_e4m3fn:
-        raise TypeError("centroids must use FP8 E4M3")
+    if centroids.dtype not in (torch.float8_e4m3fn, torch.float32):
+        raise TypeError("centroids must use FP8 E4M3 (the reference's layout) or FP32")
     if community_sizes.dtype != torch.int32:
         raise TypeError("community_sizes must use int32")
     if community_counts.dtype != torch.int32:
@@ -237,7 +237,7 @@ def score_centroids(
         graphs=workspace.kv_heads,
         retrieval_to_graph=native.pointer(mapping),
         retrieval_to_kv=native.pointer(mapping),
-        flags=_layout_flags() & ~(native.FLAG_TENSOR_SCORES if exact else 0),
+        flags=(_layout_flags() & ~(native.FLAG_TENSOR_SCORES if exact else 0)) | _centroid_flag(centroids),
     )
     native.call("ckv_score_centroids", args, native.current_stream(device))
     return workspace.scores
@@ -499,6 +499,12 @@ def tensor_scores_enabled() -> bool:
     return os.environ.get("CKV_TENSOR_SCORES", "1") != "0"
 
 
+def _centroid_flag(centroids: torch.Tensor) -> int:
+    """An fp32 centroid table (not the reference's layout) is announced to the kernels by a flag."""
+
+    return native.FLAG_FP32_CENTROIDS if centroids.dtype == torch.float32 else 0
+
+
 def _layout_flags() -> int:
     """Process-wide switches read from the environment.
 
@@ -562,6 +568,7 @@ def build_layer_args(
         token_budget=workspace.selection.token_budget,
     )
     native.fill(args, device=device.index or 0)
+    args.flags |= _centroid_flag(state.centroids)
     return args
 
 

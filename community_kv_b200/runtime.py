@@ -104,13 +104,19 @@ def convert_prefill_tensors(
     aggregation: GraphAggregation = GraphAggregation.PER_QUERY_HEAD,
     query_heads: int | None = None,
     kv_heads: int | None = None,
+    centroid_dtype: torch.dtype = torch.float8_e4m3fn,
 ) -> ConvertedPrefillState:
-    """Validate one layer's partition tensors and allocate its decode-delta pools."""
+    """Validate one layer's partition tensors and allocate its decode-delta pools.
+
+    ``centroid_dtype`` (not in the reference, whose table is always e4m3): ``torch.float32``
+    admits an fp32 centroid table (``CommunityKVConfig(centroid_dtype="fp32")``).
+    """
 
     if centroids.ndim != 3 or centroids.shape[-1] != HEAD_DIM:
         raise ValueError("centroids must have shape [retrieval heads, communities, 128]")
-    if centroids.dtype != torch.float8_e4m3fn:
-        raise TypeError("centroids must use FP8 E4M3")
+    if centroids.dtype != centroid_dtype:
+        raise TypeError("centroids must use FP8 E4M3" if centroid_dtype == torch.float8_e4m3fn
+                        else f"centroids must use {centroid_dtype}")
     heads, capacity, _ = centroids.shape
     graphs = member_offsets.shape[0]
     if min(heads, graphs, capacity) <= 0:
@@ -267,6 +273,8 @@ class DecodeRuntime:
 
         if layer_idx in self.layers:
             raise ValueError(f"layer {layer_idx} is already prepared")
+        tensors.setdefault(
+            "centroid_dtype", torch.float32 if self.config.centroid_dtype == "fp32" else torch.float8_e4m3fn)
         converted = convert_prefill_tensors(**tensors)
         mutable = converted.mutable
         budget = _effective_token_budget(

@@ -286,8 +286,8 @@ class MutableGraphState:
     def validate(self) -> None:
         if self.centroids.ndim != 3:
             raise ValueError("centroids must have shape [graphs, communities, dim]")
-        if self.centroids.dtype != torch.float8_e4m3fn:
-            raise TypeError("centroids must use FP8 E4M3")
+        if self.centroids.dtype not in (torch.float8_e4m3fn, torch.float32):
+            raise TypeError("centroids must use FP8 E4M3 (the reference's layout) or FP32")
         heads, capacity, _ = self.centroids.shape
         graphs = self.graph_count
         if self.community_sizes.shape != (heads, capacity):

@@ -80,6 +80,10 @@ typedef enum ckv_status {
 #define CKV_FLAG_TENSOR_SCORES 32  /* centroid scoring on the tensor cores (group size <= 8): the 128-long
                                      dot products are accumulated by mma.m16n8k16 in fp32 instead of in
                                      the fixed CUDA-core order; a score may differ in its last fp16 bit */
+#define CKV_FLAG_FP32_CENTROIDS 64  /* `centroids` is fp32 [batch, R, cap, 128] instead of e4m3: scores are
+                                      the fixed-order sum of products rounded one by one, the running
+                                      mean is stored unquantised.  ckv_decode_layer then runs the four
+                                      stand-alone kernels.  No reference counterpart (its table is e4m3) */
 #define CKV_FLAG_REFERENCE_DIVISION 16 /* running centroid mean (old*n + key)/(n+1): divide with the
                                      GPU's approximate full-range division (div.full.f32, at most 2 ulp
                                      off), which is what the reference's Triton kernel compiles `/` to

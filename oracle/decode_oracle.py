@@ -606,7 +606,8 @@ def online_update(
 
 
 def apply_centroid_update(state, retrieval_head: int, community: int, old_size: int, key_row: torch.Tensor) -> None:
-    """Running mean in fp32 stored back as saturating e4m3 (segmented_attention.py:685-717)."""
+    """Running mean in fp32 stored back as saturating e4m3 (segmented_attention.py:685-717);
+    stored as it is when the table is fp32 (not the reference's layout)."""
 
     old = f32(state.centroids[retrieval_head, community])
     key = f32(key_row)
@@ -615,7 +616,10 @@ def apply_centroid_update(state, retrieval_head: int, community: int, old_size: 
         updated = ((scaled + key).astype(np.float32) / np.float32(old_size + 1)).astype(np.float32)
     else:
         updated = key
-    state.centroids[retrieval_head, community] = to_fp8_saturating(updated)
+    if state.centroids.dtype == torch.float32:
+        state.centroids[retrieval_head, community] = torch.from_numpy(np.asarray(updated, dtype=np.float32))
+    else:
+        state.centroids[retrieval_head, community] = to_fp8_saturating(updated)
 
 
 def sync_shared_graph(

@@ -2,11 +2,13 @@
 
 from __future__ import annotations
 
+import ctypes
+
 import numpy as np
 import pytest
 import torch
 
-from community_kv_b200 import ops
+from community_kv_b200 import native, ops
 from community_kv_b200.batched import BatchedDecodeRuntime
 from community_kv_b200.config import CommunityKVConfig, GraphAggregation
 from community_kv_b200.runtime import DecodeRuntime, convert_prefill_tensors
@@ -23,7 +25,8 @@ def _cover(converted):
     return [min(capacity, c + converted.decode_capacity) for c in converted.initial_community_counts]
 
 
-def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, defer_update=False):
+def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, defer_update=False,
+                  exact_scores=False):
 
     device = torch.device("cuda", 0)
     runtime = DecodeRuntime(config, splits=splits, defer_update=defer_update)
@@ -50,6 +53,12 @@ def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, def
         assert out.shape == (1, 1, layer.query_heads, 128)
         runtime.synchronize_updates()
         where = f"step {step}"
+        if exact_scores:  # the device scores themselves, bit for bit, where the scan covers them
+            cover = torch.as_tensor(twin.cover)[:, None]
+            covered = torch.arange(twin.scores.shape[1])[None, :] < cover
+            want_scores = twin.exact_scores(query)
+            got_scores = state.workspace.selection.scores.cpu()
+            assert torch.equal(got_scores.view(torch.int16)[covered], want_scores.view(torch.int16)[covered]), where
         want = twin.step(query=query, key=layer.key, value=layer.value, softmax_scale=SCALE, lam=config.lam,
                          device_scores=state.workspace.selection.scores, assignment=config.online_assignment)
         assert_step_equal(
@@ -148,6 +157,25 @@ def test_nearest_centroid_assignment_variant(aggregation, defer):
     assert int(counts.max()) == int(before.max()) and int(counts.min()) == int(before.min())
     with pytest.raises(ValueError):
         CommunityKVConfig(online_assignment="nearest")
+
+
+@pytest.mark.parametrize("aggregation", [GraphAggregation.QUERY_GROUP, GraphAggregation.LAYER_WISE])
+def test_fp32_centroid_table(aggregation):
+    """Not the reference's layout: the centroid table in fp32.  The scores (fixed-order sum of products
+    rounded one by one), everything downstream and the unquantised running mean against the CPU
+    restatement, bit for bit; the call runs the four stand-alone kernels."""
+
+    layer = make_layer(seed=29, seq_len=8192, communities=80, max_decode_tokens=10, aggregation=aggregation)
+    table = layer.assembled.centroids.float()
+    generator = torch.Generator().manual_seed(291)
+    layer.assembled.centroids = table * 1.0009765625 + 1e-3 * torch.randn(table.shape, generator=generator)
+    config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation=aggregation,
+                               centroid_dtype="fp32")
+    with pytest.raises(TypeError, match="FP8"):  # the reference's layout unless asked otherwise
+        convert_prefill_tensors(**layer.prepare_kwargs())
+    state, twin = _run_sequence(layer, config, steps=8, seed=2900, exact_scores=True)
+    assert state.converted.mutable.centroids.dtype == torch.float32
+    assert native.library().ckv_decode_layer_kernels(ctypes.byref(state.args)) >= 4
 
 
 def test_many_small_communities_and_delta_chains():
