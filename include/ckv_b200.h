@@ -128,7 +128,7 @@ typedef struct ckv_layer_args {
   const int32_t* member_offsets;   /* [batch, graphs, capacity+1] */
   const int32_t* member_positions; /* [batch, graphs, member_capacity] */
   /* ---- mutable graph state ---- */
-  void* centroids;             /* e4m3 [batch, R, capacity, 128] */
+  void* centroids;             /* e4m3 [batch, R, capacity, 128]; fp32 with CKV_FLAG_FP32_CENTROIDS */
   int32_t* community_sizes;    /* [batch, R, capacity] */
   int32_t* community_counts;   /* [batch, R] */
   float* community_weight;     /* [batch, graphs, capacity] */
