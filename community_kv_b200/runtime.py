@@ -225,11 +225,16 @@ class DecodeRuntime:
     """Fixed-address per-layer decode states; one CUDA-library call per layer and token."""
 
     def __init__(self, config: CommunityKVConfig, *, splits: int | None = None,
-                 defer_update: bool = False) -> None:
+                 defer_update: bool = False, max_communities: int = 0) -> None:
         """``defer_update``: run each layer's online assignment on a second stream beside the
-        work that follows the layer's attention (see ``ops.DeferredUpdate``); same results."""
+        work that follows the layer's attention (see ``ops.DeferredUpdate``); same results.
+        ``max_communities`` (not in the reference): select at most that many communities per
+        retrieval head under the token budget ("top-k communities"; 0 = the budget alone)."""
 
+        if max_communities < 0:
+            raise ValueError("max_communities must be nonnegative")
         self.config = config
+        self.max_communities = max_communities
         self.splits = splits
         self.defer_update = defer_update
         self._deferred: ops.DeferredUpdate | None = None
@@ -297,6 +302,7 @@ class DecodeRuntime:
                 score_community_counts=converted.initial_community_counts,
                 score_headroom=converted.decode_capacity,
                 splits=self.splits,
+                max_communities=self.max_communities,
             ),
             sink_positions=torch.arange(self.config.num_sink, dtype=torch.int32, device=device),
         )

@@ -26,10 +26,10 @@ def _cover(converted):
 
 
 def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, defer_update=False,
-                  exact_scores=False):
+                  exact_scores=False, max_communities=0):
 
     device = torch.device("cuda", 0)
-    runtime = DecodeRuntime(config, splits=splits, defer_update=defer_update)
+    runtime = DecodeRuntime(config, splits=splits, defer_update=defer_update, max_communities=max_communities)
     state = runtime.prepare_layer(0, **layer.to(device).prepare_kwargs())
     twin = OracleLayer(
         state.converted.csr,
@@ -38,6 +38,7 @@ def _run_sequence(layer, config, steps, *, seed, integer=False, splits=None, def
         token_budget=state.workspace.selection.token_budget,
         num_sink=config.num_sink,
         cover=_cover(state.converted),
+        max_communities=max_communities,
     )
     key = layer.key.to(device)[None]
     value = layer.value.to(device)[None]
@@ -176,6 +177,30 @@ def test_fp32_centroid_table(aggregation):
     state, twin = _run_sequence(layer, config, steps=8, seed=2900, exact_scores=True)
     assert state.converted.mutable.centroids.dtype == torch.float32
     assert native.library().ckv_decode_layer_kernels(ctypes.byref(state.args)) >= 4
+
+
+def test_single_layer_configuration_as_worded():
+    """The single-layer configuration to the letter: ctx 8192, 32 / 8 heads, 64 planted clusters, the
+    centroids the per-community mean keys in fp32, the eight best communities per KV head, budget 1024.
+    Scores, selection, attention output, neighbour candidates and the online update against the CPU
+    restatement (scores and state bit for bit)."""
+
+    layer = make_layer(seed=0, seq_len=8192, communities=64, max_decode_tokens=8, aggregation="query_group")
+    assembled = layer.assembled
+    heads, capacity, _ = assembled.centroids.shape
+    labels = assembled.token_communities[:, : layer.prefill_seq_len].long()  # [graphs, S]
+    means = torch.zeros((heads, capacity, 128), dtype=torch.float32)
+    for head in range(heads):
+        graph, kv = int(assembled.retrieval_to_graph[head]), int(assembled.retrieval_to_kv[head])
+        keep = torch.arange(layer.prefill_seq_len) >= 10  # the ten sink positions are not members
+        means[head].index_add_(0, labels[graph][keep], layer.key[kv, : layer.prefill_seq_len][keep].float())
+        sizes = assembled.community_sizes[head].clamp(min=1).float()
+        means[head] /= sizes[:, None]
+    assembled.centroids = means
+    config = CommunityKVConfig(token_budget=1024, num_sink=10, lam=0.5, aggregation="query_group",
+                               centroid_dtype="fp32")
+    state, _ = _run_sequence(layer, config, steps=4, seed=100, exact_scores=True, max_communities=8)
+    assert int(state.workspace.selection.descriptor_counts.max()) <= 8
 
 
 def test_many_small_communities_and_delta_chains():
