@@ -84,6 +84,9 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--prompt-length", type=int, default=32768)
     parser.add_argument("--new-tokens", type=int, default=128)
     parser.add_argument("--model-layers", type=int, default=36)
+    parser.add_argument("--online-assignment", choices=["modularity", "nearest_centroid"], default="modularity",
+                        help="--workload model: the reference's modularity-gain rule, or the nearest-centroid "
+                             "variant (one more centroid scan per layer and token)")
     parser.add_argument("--prefill-length", type=int, default=16384)
     return parser.parse_args()
 
@@ -1032,7 +1035,8 @@ def run_model(args: argparse.Namespace) -> None:
     build_seconds = time.perf_counter() - build_begin
     generator = torch.Generator().manual_seed(args.seed)
     prompt = torch.randint(0, config.vocab_size, (1, args.prompt_length), generator=generator).to(device)
-    ckv = CommunityKVConfig(token_budget=BUDGET, num_sink=NUM_SINK, lam=0.5, aggregation="query_group")
+    ckv = CommunityKVConfig(token_budget=BUDGET, num_sink=NUM_SINK, lam=0.5, aggregation="query_group",
+                            online_assignment=args.online_assignment)
     partitioner = SyntheticPartitioner(communities=512, zipf_exponent=ZIPF, seed=args.seed)
     sampler = ClockSampler(device.index or 0)
     with CommunityKVRuntime(config=ckv, partition=PartitionConfig(), num_layers=layers,
@@ -1091,7 +1095,8 @@ def run_model(args: argparse.Namespace) -> None:
         "config": {
             "workload": f"random-init Qwen3-8B-shaped decoder ({layers} layers, hidden 4096, 32/8 heads, FFN 12288, "
                         f"vocab 151936), batch 1, prompt {args.prompt_length} random ids, {args.new_tokens} new tokens, "
-                        f"512 Zipf({ZIPF}) communities per (layer, KV head), budget {BUDGET}",
+                        f"512 Zipf({ZIPF}) communities per (layer, KV head), budget {BUDGET}, "
+                        f"online assignment: {args.online_assignment}",
             "loop": "Hugging Face generate, eager (no CUDA graph): projections, MLP, norms and sampling included",
         },
         "prefill_seconds": first_decode["t"] - begin,
