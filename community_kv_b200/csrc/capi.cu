@@ -12,6 +12,7 @@ cudaError_t launch_append_kv(void* key_cache, void* value_cache, const void* new
                              int64_t units, int64_t unit_stride, const int32_t* row_index,
                              int64_t row_index_stride, int64_t row, cudaStream_t stream);
 cudaError_t launch_wait_peers(uint32_t* flag, uint32_t expected, uint32_t* status, cudaStream_t stream);
+cudaError_t launch_nearest_centroid(const ckv_layer_args& a, int32_t* forced, cudaStream_t stream);
 bool fused_layer_supported(const ckv_layer_args& a);
 cudaError_t launch_fused_layer(const ckv_layer_args& a, cudaStream_t stream);
 int attention_smem_bytes();
@@ -202,6 +203,22 @@ int ckv_wait_peers(uint32_t* flag, uint32_t expected, uint32_t* status, void* cu
   if (expected == 0) return CKV_OK;
   return ckv::launched(
       ckv::launch_wait_peers(flag, expected, status, static_cast<cudaStream_t>(cuda_stream)));
+}
+
+int ckv_nearest_centroid(const ckv_layer_args* args, int32_t* forced_community, void* cuda_stream) {
+  const int common = ckv::check_common(args);
+  if (common != CKV_OK) return common;
+  const ckv_layer_args& a = *args;
+  if (!forced_community || !a.centroids || !a.community_sizes || !a.community_counts ||
+      !a.current_position) {
+    return CKV_ERR_NULL;
+  }
+  if (!a.current_key && !a.key) return CKV_ERR_NULL;
+  if (a.sequence_capacity <= 0) return CKV_ERR_SHAPE;
+  const int status = ckv::select_device(args);
+  if (status != CKV_OK) return status;
+  return ckv::launched(
+      ckv::launch_nearest_centroid(a, forced_community, static_cast<cudaStream_t>(cuda_stream)));
 }
 
 int ckv_decode_layer_kernels(const ckv_layer_args* args) {

@@ -140,6 +140,106 @@ cudaError_t launch_wait_peers(uint32_t* flag, uint32_t expected, uint32_t* statu
   return cudaLaunchKernelEx(&config, wait_peers_kernel, flag, expected, status);
 }
 
+// Nearest-centroid assignment variant: per leader head, the live community whose centroid
+// has the largest inner product with the key of the token being decoded (the fp16 value the
+// scoring kernel would give a query group made of that key; first maximum).  One CTA per
+// retrieval head; eight lanes share a centroid row, every product and sum rounded on its own
+// in the scoring kernels' fixed order, so a CPU reproduces the choice bit for bit.
+constexpr int kNearestThreads = 256;
+
+__global__ void __launch_bounds__(kNearestThreads) nearest_centroid_kernel(const ckv_layer_args a,
+                                                                          int32_t* forced) {
+  __shared__ unsigned long long warp_best[kNearestThreads / 32];
+  const int flat = blockIdx.x;
+  const Unit u = make_unit(a, flat);
+  if (u.head != u.graph) {
+    return;  // followers of a shared graph take the leader's choice
+  }
+  const int capacity = a.community_capacity;
+  const int64_t graph_slot = static_cast<int64_t>(u.batch) * a.graphs + u.graph;
+  const int current = min(max(a.current_position[graph_slot], 0), a.sequence_capacity - 1);
+  const __nv_bfloat16* key_row =
+      a.current_key != nullptr
+          ? reinterpret_cast<const __nv_bfloat16*>(a.current_key) + static_cast<int64_t>(flat) * kHeadDim
+          : reinterpret_cast<const __nv_bfloat16*>(a.key) + u.batch * a.key_batch_stride +
+                u.kv * a.key_head_stride + static_cast<int64_t>(current) * a.key_row_stride;
+  const int slice = threadIdx.x & 7;
+  float q[16];
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    q[k] = __bfloat162float(key_row[slice * 16 + k]);
+  }
+  const bool wide = (a.flags & CKV_FLAG_FP32_CENTROIDS) != 0;
+  const int count = min(a.community_counts[flat], capacity);
+  const int32_t* sizes = a.community_sizes + static_cast<int64_t>(flat) * capacity;
+  unsigned long long best = 0ull;  // (ordered fp16 key + 1) << 32 | ~row : the first maximum wins
+  for (int base = 0; base < count; base += kNearestThreads / 8) {
+    const int row = base + (threadIdx.x >> 3);
+    const int safe_row = min(row, capacity - 1);  // every lane takes part in the shuffles
+    float x[16];
+    if (wide) {
+      const float4* source = reinterpret_cast<const float4*>(
+          reinterpret_cast<const float*>(a.centroids) +
+          (static_cast<int64_t>(flat) * capacity + safe_row) * kHeadDim + slice * 16);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 v = source[i];
+        x[4 * i] = v.x;
+        x[4 * i + 1] = v.y;
+        x[4 * i + 2] = v.z;
+        x[4 * i + 3] = v.w;
+      }
+    } else {
+      const uint4 raw = *reinterpret_cast<const uint4*>(
+          reinterpret_cast<const uint8_t*>(a.centroids) +
+          (static_cast<int64_t>(flat) * capacity + safe_row) * kHeadDim + slice * 16);
+      const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const __half_raw half = __nv_cvt_fp8_to_halfraw(
+            static_cast<__nv_fp8_storage_t>((words[k >> 2] >> (8 * (k & 3))) & 0xffu), __NV_E4M3);
+        x[k] = __half2float(*reinterpret_cast<const __half*>(&half));
+      }
+    }
+    float acc = __fmul_rn(x[0], q[0]);
+#pragma unroll
+    for (int k = 1; k < 16; ++k) {
+      acc = __fadd_rn(acc, __fmul_rn(x[k], q[k]));
+    }
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+    if (row < count && sizes[row] > 0) {
+      uint16_t bits = __half_as_ushort(__float2half_rn(acc));
+      bits = bits == 0x8000u ? 0u : bits;  // -0 and +0 compare equal
+      const unsigned long long key = static_cast<unsigned long long>(ordered_key16(bits)) + 1ull;
+      const unsigned long long packed = (key << 32) | (0xffffffffull - static_cast<unsigned long long>(row));
+      best = packed > best ? packed : best;
+    }
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, offset);
+    best = other > best ? other : best;
+  }
+  if ((threadIdx.x & 31) == 0) {
+    warp_best[threadIdx.x >> 5] = best;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < kNearestThreads / 32; ++w) {
+      best = warp_best[w] > best ? warp_best[w] : best;
+    }
+    forced[graph_slot] =
+        best == 0ull ? -1 : static_cast<int32_t>(0xffffffffull - (best & 0xffffffffull));
+  }
+}
+
+cudaError_t launch_nearest_centroid(const ckv_layer_args& a, int32_t* forced, cudaStream_t stream) {
+  nearest_centroid_kernel<<<a.batch * a.retrieval_heads, kNearestThreads, 0, stream>>>(a, forced);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_merge_update(const ckv_layer_args& a, cudaStream_t stream) {
   cudaError_t err = launch_dependent(merge_update_kernel, dim3(a.batch * a.retrieval_heads),
                                      dim3(kMergeThreads + 32), 0, stream, a);

@@ -186,6 +186,7 @@ ENTRY_POINTS = (
     "ckv_prefill_topk",
     "ckv_online_update",
     "ckv_wait_peers",
+    "ckv_nearest_centroid",
     "ckv_append_kv",
     "ckv_merge_partials",
     "ckv_assemble_member_csr",
@@ -242,6 +243,8 @@ def library() -> ctypes.CDLL:
         getattr(lib, name).argtypes = [_l, _l, _i, ctypes.c_double]
     lib.ckv_build_adjacency.restype = ctypes.c_int
     lib.ckv_build_adjacency.argtypes = [_p, _p, _p, _i, _l, _i, _i, ctypes.c_double, _p, _p, _p, _l, _p, _p, _l, _p]
+    lib.ckv_nearest_centroid.restype = ctypes.c_int
+    lib.ckv_nearest_centroid.argtypes = [ctypes.POINTER(LayerArgs), ctypes.c_void_p, ctypes.c_void_p]
     lib.ckv_wait_peers.restype = ctypes.c_int
     lib.ckv_wait_peers.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p]
     lib.ckv_prefill_topk.restype = ctypes.c_int

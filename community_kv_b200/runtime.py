@@ -14,6 +14,8 @@ computed partitions enter through ``DecodeRuntime.prepare_layer``.
 
 from __future__ import annotations
 
+import ctypes
+
 from dataclasses import dataclass
 from types import TracebackType
 from typing import Any, Callable, Mapping, Sequence
@@ -23,7 +25,6 @@ import torch
 from community_kv_b200 import native, ops
 from community_kv_b200.config import CommunityKVConfig, GraphAggregation, PartitionConfig
 from community_kv_b200.state import (
-    CentroidSelectionWorkspace,
     ATTENTION_TILE,
     HEAD_DIM,
     DecodeDeltaChunks,
@@ -69,8 +70,7 @@ class DecodeLayerState:
     args: native.LayerArgs | None = None
     cache_key: tuple[int, ...] | None = None
     update_done: Any = None  # deferred update: event of the layer's last online assignment
-    # nearest-centroid assignment variant: scores of the new token's key, the arg-max per graph
-    nearest: Any = None
+    # nearest-centroid assignment variant: the community each graph's new token joins
     forced: torch.Tensor | None = None
 
 
@@ -367,39 +367,27 @@ class DecodeRuntime:
         """The variant of the online assignment that is not in the reference: the token joins
         the live community whose centroid has the largest inner product with its key.
 
-        The key row of the token being decoded (already in the cache at the graph's cursor) is
-        scored against the centroid table by the scoring kernel itself - as a query group whose
-        rows are all that key, in the fixed summation order, so that a CPU reproduces the fp16
-        scores bit for bit - and the first maximum per leader head is handed to the update as
-        ``forced_community``.  Everything stays on the device and on the caller's stream.
+        One small launch (``ckv_nearest_centroid``) scores the key row of the token being
+        decoded (already in the cache at the graph's cursor) against the head's centroid table -
+        the fp16 value the scoring kernel gives a query group made of that key, in the fixed
+        summation order, so that a CPU reproduces the choice bit for bit - and leaves the first
+        maximum per leader head where the update reads it (``forced_community``).
         """
 
         mutable = layer.converted.mutable
-        heads = mutable.retrieval_head_count
         device = mutable.centroids.device
-        if layer.nearest is None:
-            layer.nearest = CentroidSelectionWorkspace.allocate(
-                kv_heads=heads, community_capacity=mutable.community_capacity,
-                token_budget=layer.workspace.selection.token_budget, num_sink=self.config.num_sink,
-                device=device,
-            )
+        if layer.forced is None:
             layer.forced = torch.full((mutable.graph_count,), -1, dtype=torch.int32, device=device)
         layer.args.forced_community = layer.forced.data_ptr()  # the block is rebuilt when the cache moves
         if layer.update_done is not None:
             # the previous step's deferred update still reads `forced`
             torch.cuda.current_stream(device).wait_event(layer.update_done)
-        cursor = layer.converted.current_position.long()[mutable.retrieval_to_graph.long()]
-        rows = key[mutable.retrieval_to_kv.long(), cursor.clamp(max=key.shape[1] - 1)]  # [R, 128]
-        group = layer.converted.group_size
-        scores = ops.score_centroids(
-            query=rows.repeat_interleave(group, dim=0).contiguous(), centroids=mutable.centroids,
-            community_sizes=mutable.community_sizes, community_counts=mutable.community_counts,
-            workspace=layer.nearest, exact=True,
+        status = native.library().ckv_nearest_centroid(
+            ctypes.byref(layer.args), ctypes.c_void_p(layer.forced.data_ptr()),
+            ctypes.c_void_p(native.current_stream(device)),
         )
-        best = scores.float().max(dim=1)
-        nearest = torch.where(torch.isinf(best.values) & (best.values < 0), -1, best.indices).to(torch.int32)
-        # the leader of graph g is retrieval head g
-        layer.forced.copy_(nearest[: mutable.graph_count])
+        if status:
+            raise native.NativeError(native.library().ckv_status_string(status).decode())
 
     def assert_no_overflow(self) -> None:
         self.synchronize_updates()

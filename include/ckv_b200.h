@@ -302,6 +302,16 @@ int ckv_append_kv(void* key_cache, void* value_cache, const void* new_key, const
  * counterpart: the reference runs on one GPU. */
 int ckv_wait_peers(uint32_t* flag, uint32_t expected, uint32_t* status, void* cuda_stream);
 
+/* Nearest-centroid assignment variant (no reference counterpart: the reference assigns by
+ * modularity gain, A5).  For every graph writes forced_community[batch, graphs]: the live
+ * community (index < community_counts, size > 0) of the graph's leader head whose centroid has
+ * the largest inner product with the key of the token being decoded - the fp16 value
+ * ckv_score_centroids gives a query group made of that key, fixed summation order; the first
+ * maximum wins; -1 when the head has no live community.  The key is current_key[batch, R, 128]
+ * when set, else the cache row at current_position.  Pass the array as `forced_community` to
+ * ckv_decode_layer / ckv_online_update. */
+int ckv_nearest_centroid(const ckv_layer_args* args, int32_t* forced_community, void* cuda_stream);
+
 /* How many kernels ckv_decode_layer launches for these arguments (1, 4 or 5);
  * no reference counterpart, used for launch accounting. */
 int ckv_decode_layer_kernels(const ckv_layer_args* args);
