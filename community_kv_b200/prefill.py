@@ -112,15 +112,17 @@ def prefill_attention_topk(
     """
 
     own_status = status is None
+    rows = max(0, query.shape[1] - (num_sink + TOPK - 1)) if query.ndim == 4 else 0
+    # a prompt with no row long enough for eight eligible keys: attention only, empty edge tensors
     args, out, lse, status, keep = _pack(
-        query, key, value, softmax_scale=softmax_scale, num_sink=num_sink, mode=1, status=status
+        query, key, value, softmax_scale=softmax_scale, num_sink=num_sink, mode=1 if rows else 0, status=status
     )
     batch, length, heads, _ = out.shape
-    rows = max(0, length - (num_sink + TOPK - 1))
     topk_val = torch.zeros((batch, heads, rows, TOPK), dtype=torch.float32, device=out.device)
     topk_idx = torch.zeros((batch, heads, rows, TOPK), dtype=torch.int32, device=out.device)
-    args.topk_val = topk_val.data_ptr()
-    args.topk_idx = topk_idx.data_ptr()
+    if rows:
+        args.topk_val = topk_val.data_ptr()
+        args.topk_idx = topk_idx.data_ptr()
     native.call("ckv_prefill_topk", args, native.current_stream(out.device))
     if own_status:
         check_status(status)

@@ -39,7 +39,10 @@ def _check_attention(out, lse, q, k, v, want_out, want_lse):
     np.testing.assert_allclose(lse.cpu().numpy(), want_lse, atol=2e-3, rtol=0)
 
 
-@pytest.mark.parametrize("length,heads,kv_heads", [(256, 4, 1), (300, 8, 2), (640, 2, 2), (200, 8, 1), (512, 2, 1)])
+@pytest.mark.parametrize(
+    "length,heads,kv_heads",
+    [(256, 4, 1), (300, 8, 2), (640, 2, 2), (200, 8, 1), (512, 2, 1), (64, 4, 2), (1, 2, 1), (130, 4, 1), (129, 2, 2)],
+)
 def test_attention_output_and_lse(length, heads, kv_heads):
     q, k, v = _inputs(1, length, heads, kv_heads)
     out, lse = prefill_attention(q.cuda(), k.cuda(), v.cuda(), softmax_scale=SCALE)
@@ -98,6 +101,32 @@ def test_exact_edges_are_bit_exact(length, heads, kv_heads, edges):
     want_out, want_lse, _ = oracle.causal_attention(q[0].float().numpy(), k[0].float().numpy(), v[0].float().numpy(), SCALE)
     _check_attention(out[0], lse[0], q, k, v, want_out, want_lse)
     assert int(flags.sum()) <= flags.numel() // 20
+
+
+@pytest.mark.parametrize("length,heads,kv_heads,sinks", [(100, 4, 2, 4), (129, 8, 2, 0), (12, 2, 1, 3), (9, 4, 1, 4)])
+def test_reference_topk_rule_short_and_ragged(length, heads, kv_heads, sinks):
+    """Rows shorter than one tile, a tile of a single row, a prompt barely longer than the sinks."""
+
+    q, k, v = _inputs(6, length, heads, kv_heads)
+    out, lse, _, _, val, idx = prefill_attention_topk(q.cuda(), k.cuda(), v.cuda(), softmax_scale=SCALE, num_sink=sinks)
+    torch.cuda.synchronize()
+    rows = max(0, length - sinks - 7)
+    assert val.shape == (1, heads, rows, 8) and idx.shape == (1, heads, rows, 8)
+    want_out, want_lse, raw = oracle.causal_attention(q[0].float().numpy(), k[0].float().numpy(), v[0].float().numpy(), SCALE)
+    _check_attention(out[0], lse[0], q, k, v, want_out, want_lse)
+    for head in range(heads):
+        if rows == 0:
+            break
+        want_val, want_idx, want_key = oracle.reference_topk(raw[head], want_lse[head], SCALE, sinks)
+        keys = oracle.quantised_keys(raw[head])
+        got_idx = idx[0, head].cpu().numpy()
+        for row in range(rows):
+            position = row + sinks + 7
+            mine = got_idx[row]
+            assert mine.min() >= sinks and mine.max() <= position and len(set(mine.tolist())) == 8
+            floor_key = want_key[row].min()
+            for j in set(mine.tolist()) ^ set(want_idx[row].tolist()):
+                assert abs(int(keys[position, j]) - int(floor_key)) <= 1, (head, row, j)
 
 
 def test_exact_edges_rescan_path():
