@@ -154,28 +154,30 @@ def prefill_attention_edges(
     if not 1 <= edges_per_row <= EXACT_KEEP:
         raise ValueError("edges_per_row must be in [1, 16]")
     own_status = status is None
+    rows = max(0, query.shape[1] - (num_sink + edges_per_row - 1)) if query.ndim == 4 else 0
+    # a prompt with no row long enough for `edges_per_row` eligible keys: attention only, empty edges
     args, out, lse, status, keep = _pack(
-        query, key, value, softmax_scale=softmax_scale, num_sink=num_sink, mode=2,
+        query, key, value, softmax_scale=softmax_scale, num_sink=num_sink, mode=2 if rows else 0,
         edges_per_row=edges_per_row, exact_slack=exact_slack, status=status,
     )
     batch, length, heads, _ = out.shape
     kv_heads = keep[1].shape[2]
     group = heads // kv_heads
-    rows = max(0, length - (num_sink + edges_per_row - 1))
     device = out.device
     candidates = torch.zeros((batch, kv_heads, length, group, EXACT_KEEP + 1), dtype=torch.int64, device=device)
     edge_idx = torch.full((batch, kv_heads, rows, edges_per_row), -1, dtype=torch.int32, device=device)
     edge_score = torch.zeros((batch, kv_heads, rows, edges_per_row), dtype=torch.float32, device=device)
     flags = torch.zeros((batch, kv_heads, rows), dtype=torch.int32, device=device)
     rescan_list = torch.zeros((1 + batch * kv_heads * rows,), dtype=torch.int32, device=device)
-    native.fill(
-        args,
-        candidates=candidates.data_ptr(),
-        edge_idx=edge_idx.data_ptr(),
-        edge_score=edge_score.data_ptr(),
-        edge_flags=flags.data_ptr(),
-        rescan_list=rescan_list.data_ptr(),
-    )
+    if rows:
+        native.fill(
+            args,
+            candidates=candidates.data_ptr(),
+            edge_idx=edge_idx.data_ptr(),
+            edge_score=edge_score.data_ptr(),
+            edge_flags=flags.data_ptr(),
+            rescan_list=rescan_list.data_ptr(),
+        )
     native.call("ckv_prefill_topk", args, native.current_stream(device))
     if own_status:
         check_status(status)

@@ -129,6 +129,16 @@ def test_reference_topk_rule_short_and_ragged(length, heads, kv_heads, sinks):
                 assert abs(int(keys[position, j]) - int(floor_key)) <= 1, (head, row, j)
 
 
+def test_exact_edges_of_a_prompt_shorter_than_the_list():
+    q, k, v = _inputs(7, 12, 4, 2)
+    out, lse, edge_idx, edge_score, flags = prefill_attention_edges(
+        q.cuda(), k.cuda(), v.cuda(), softmax_scale=SCALE, num_sink=4, edges_per_row=16)
+    torch.cuda.synchronize()
+    assert edge_idx.shape == (1, 2, 0, 16) and edge_score.shape == (1, 2, 0, 16) and flags.numel() == 0
+    want_out, want_lse, _ = oracle.causal_attention(q[0].float().numpy(), k[0].float().numpy(), v[0].float().numpy(), SCALE)
+    _check_attention(out[0], lse[0], q, k, v, want_out, want_lse)
+
+
 def test_exact_edges_rescan_path():
     """A huge slack flags every row: the brute-force re-scan must give the same exact answer."""
 
