@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   const uint32_t bar_v_full = smem_u32(bars + 3);   // two stages
   const uint32_t bar_k_free = smem_u32(bars + 5);   // two stages: both tiles' S of that block done
   const uint32_t bar_s_full = smem_u32(bars + 9);   // per tile: S written
-  const uint32_t bar_p_full = smem_u32(bars + 11);  // per tile: P written by its 128 threads
+  const uint32_t bar_p_full = smem_u32(bars + 11);  // per tile: P written by its four warps
   const uint32_t bar_o_full = smem_u32(bars + 13);  // per tile: P.V folded into O
 
   // a wait already ran out somewhere in this launch: drain the grid quickly
@@ -222,8 +222,8 @@ __global__ void __launch_bounds__(kPairThreads, 1)
     for (int i = 0; i < 11; ++i) {
       mbar_init(bar_q + 8 * i, 1);
     }
-    mbar_init(bar_p_full, 128);
-    mbar_init(bar_p_full + 8, 128);
+    mbar_init(bar_p_full, 4);  // one arrival per softmax warp
+    mbar_init(bar_p_full + 8, 4);
     mbar_init(bar_o_full, 1);
     mbar_init(bar_o_full + 8, 1);
     *abort = 0u;
@@ -470,7 +470,11 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       }
       tmem_wait_store();
       tc_fence_before();
-      mbar_arrive(bar_p_full + 8 * t);
+      // one arrival per warp: 128 arrivals on one barrier word queue up behind each other
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar_p_full + 8 * t);
+      }
 
       // The candidate bookkeeping runs from the scores still in registers while the tensor
       // cores work on this tile's P.V and next S: it is off the path between two blocks.
