@@ -366,7 +366,7 @@ def run_b200(args: argparse.Namespace) -> None:
         batch = per_gpu * world
     total_steps = args.warmup + args.steps
     e2e_steps = max(3, min(args.steps, 10))
-    extra_steps = 4 + e2e_steps + 3 + 4  # e2e steps, three event-timed passes, one phase-stamped pass
+    extra_steps = 4 + e2e_steps + 2 + 3 + 4  # e2e steps, three event-timed passes, one phase-stamped pass
     max_decode = total_steps + extra_steps + 8
 
     build_begin = time.perf_counter()
@@ -407,7 +407,15 @@ def run_b200(args: argparse.Namespace) -> None:
             torch.zeros((launches, world, slots, query_local, HEAD_DIM), dtype=torch.bfloat16, device=device)
             if world > 1 else None
         )
-    q_cur = torch.zeros((launches, slots, query_local, HEAD_DIM), dtype=torch.bfloat16, device=device)
+    # One staging buffer holds a step's inputs, layer by layer: a layer's queries, then its new
+    # K rows, then its new V rows.  The end-to-end loop can so bring the first layers' inputs
+    # from the host in one copy and the remaining layers' in a second that runs beside them.
+    query_count = slots * query_local * HEAD_DIM
+    row_count = slots * heads_local * HEAD_DIM
+    staged = torch.zeros((launches, query_count + 2 * row_count), dtype=torch.bfloat16, device=device)
+    q_cur = staged[:, :query_count].view(launches, slots, query_local, HEAD_DIM)
+    new_key = staged[:, query_count:query_count + row_count].view(launches, slots, heads_local, HEAD_DIM)
+    new_value = staged[:, query_count + row_count:].view(launches, slots, heads_local, HEAD_DIM)
     generator = torch.Generator(device=device).manual_seed(args.seed + 17 + rank)
     stream = torch.cuda.Stream(device)
     packed = []
@@ -440,9 +448,9 @@ def run_b200(args: argparse.Namespace) -> None:
         update.peer_wait_flag = None
         update_args.append(update)
 
-    def enqueue_step() -> None:
+    def enqueue_step(first: int = 0, last: int = launches, after_layer=None) -> None:
         handle = stream.cuda_stream
-        for launch in range(launches):
+        for launch in range(first, last):
             if deferred:
                 native.call("ckv_decode_layer", attend_args[launch], handle)
                 attended = torch.cuda.Event()
@@ -456,6 +464,8 @@ def run_b200(args: argparse.Namespace) -> None:
                     exchange.wait(launch, handle)  # the next consumer needs every rank's heads
             elif world > 1:
                 dist.all_gather_into_tensor(out_full[launch], out_local[launch])
+            if after_layer is not None:
+                after_layer(launch)
         if deferred:
             updated = torch.cuda.Event()
             updated.record(side)
@@ -602,30 +612,104 @@ def run_b200(args: argparse.Namespace) -> None:
     clocks = sampler.stop() if rank == 0 else {}
 
     # ---- end to end: host queries and new K/V rows in, head outputs out, every step ----
-    pinned_q = torch.randn((e2e_steps, launches, slots, query_local, HEAD_DIM)).to(torch.bfloat16).pin_memory()
-    pinned_kv = (torch.randn((e2e_steps, 2, launches, slots, heads_local, HEAD_DIM)) * SCALE).to(torch.bfloat16).pin_memory()
+    # A token is two graph replays.  The first holds the leading layers, whose inputs come in a
+    # small copy; the second holds the other layers, whose inputs come in a second copy that
+    # runs on the copy stream beside the first replay.  Inside the second replay the head
+    # outputs go back to the host a few layers at a time on the copy stream, beside the layers
+    # still to run; only the last piece is read after the last layer.  The row the new K/V
+    # land in is a device cursor that the token advances itself.
+    pinned_in = torch.randn((e2e_steps, launches, query_count + 2 * row_count))
+    pinned_in[:, :, query_count:] *= SCALE
+    pinned_in = pinned_in.to(torch.bfloat16).pin_memory()
     # every rank reads back the head outputs it computed (together the ranks read the whole result once)
     pinned_out = torch.empty((launches, slots, query_local, HEAD_DIM), dtype=torch.bfloat16).pin_memory()
-    new_kv = torch.empty((2, launches, slots, heads_local, HEAD_DIM), dtype=torch.bfloat16, device=device)
-    cursor = int(work.state(0).current_position.max())
     result = exchange.gathered[:, rank] if exchange is not None else out_local
+    cursor = work.state(0).current_position.max().to(torch.int32).reshape(1).clone()
+    copies = torch.cuda.Stream(device)
+    lead = launches // 9  # a ninth of the layers: 4 of 36
+    pieces = 4 if launches >= 8 else 1
+    piece_ends = [launches * (piece + 1) // pieces for piece in range(pieces)]
+
+    def append_rows(first: int, last: int) -> None:
+        ops.append_kv(work.key[first:last], work.value[first:last], new_key[first:last],
+                      new_value[first:last], cursor)
+
+    def read_back(launch: int) -> None:
+        if launch + 1 not in piece_ends[:-1]:
+            return
+        index = piece_ends.index(launch + 1)
+        begin = piece_ends[index - 1] if index else 0
+        produced = torch.cuda.Event()
+        produced.record(stream)
+        copies.wait_event(produced)
+        with torch.cuda.stream(copies):
+            pinned_out[begin:launch + 1].copy_(result[begin:launch + 1], non_blocking=True)
+
+    def enqueue_lead() -> None:
+        append_rows(0, lead)
+        enqueue_step(0, lead)
+
+    def enqueue_rest() -> None:
+        append_rows(lead, launches)
+        cursor.add_(1)
+        enqueue_step(lead, launches, after_layer=read_back)
+        begin = piece_ends[-2] if pieces > 1 else 0
+        pinned_out[begin:].copy_(result[begin:], non_blocking=True)
+        if pieces > 1:
+            returned = torch.cuda.Event()
+            returned.record(copies)
+            stream.wait_event(returned)
+
+    lead_graph = rest_graph = None
+    if use_graph:
+        rest_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(rest_graph, stream=stream):
+            enqueue_rest()
+        if lead:
+            lead_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(lead_graph, stream=stream):
+                enqueue_lead()
+
+    def replay_or_enqueue(graph, enqueue) -> None:
+        if graph is not None:
+            graph.replay()
+        else:
+            enqueue()
+
+    def token(step: int) -> None:
+        source = pinned_in[step]
+        if lead:
+            staged[:lead].copy_(source[:lead], non_blocking=True)
+            first_arrived, all_arrived = torch.cuda.Event(), torch.cuda.Event()
+            first_arrived.record(stream)
+            copies.wait_event(first_arrived)  # one copy at a time in this direction
+            with torch.cuda.stream(copies):
+                staged[lead:].copy_(source[lead:], non_blocking=True)
+                all_arrived.record(copies)
+            replay_or_enqueue(lead_graph, enqueue_lead)
+            stream.wait_event(all_arrived)
+        else:
+            staged.copy_(source, non_blocking=True)
+        replay_or_enqueue(rest_graph, enqueue_rest)
+        stream.synchronize()  # the caller reads the token's output before the next token
+
+    with torch.cuda.stream(stream):
+        for warm in range(2):  # untimed: the first replays of a new graph also upload it
+            token(warm)
     barrier()
     e2e_begin, e2e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         e2e_begin.record()
         for step in range(e2e_steps):
-            q_cur.copy_(pinned_q[step], non_blocking=True)
-            new_kv.copy_(pinned_kv[step], non_blocking=True)
-            ops.append_kv(work.key, work.value, new_kv[0], new_kv[1], cursor + step)
-            run_step()
-            pinned_out.copy_(result, non_blocking=True)
-            stream.synchronize()  # the caller reads the step's output before the next token
+            token(step)
         e2e_end.record()
     barrier()
     e2e_ms = torch.tensor([e2e_begin.elapsed_time(e2e_end)], device=device)
     if world > 1:
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     e2e_ms_per_step = float(e2e_ms) / e2e_steps
+    if not torch.equal(pinned_out, result.cpu()):
+        raise RuntimeError("the head outputs read back piece by piece differ from the ones on the device")
     work.runtime.assert_no_overflow()
     if exchange is not None:
         exchange.check()
@@ -709,7 +793,7 @@ def run_b200(args: argparse.Namespace) -> None:
             "unit": "tokens/s",
             "ms_per_step": e2e_ms_per_step,
             "steps": e2e_steps,
-            "h2d_bytes_per_step": int(pinned_q[0].numel() * 2 + pinned_kv[0].numel() * 2),
+            "h2d_bytes_per_step": int(pinned_in[0].numel() * 2),
             "d2h_bytes_per_step": int(pinned_out.numel() * 2),
         },
         "phases_us": phases_us,
